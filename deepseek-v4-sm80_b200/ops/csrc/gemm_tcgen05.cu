@@ -1,0 +1,303 @@
+// Dense projection GEMM for sm_100a:  out[M,N] = X[M,K] * W[N,K]^T  (both operands K-major).
+//
+// One CTA computes a 128 x BN output tile.  Warp 0 streams A/B k-tiles with TMA
+// (128-byte swizzle) through a multi-stage mbarrier ring, warp 1 issues
+// tcgen05.mma with the accumulator in tensor memory, warps 2-5 read the
+// accumulator back with tcgen05.ld and write the result.
+//
+// Two operand formats:
+//   * bf16 x bf16 (kind::f16), fp32 accumulate over the whole K in one TMEM buffer.
+//   * e4m3 x e4m3 (kind::f8f6f4) with power-of-two block scales: activations carry
+//     one fp32 scale per (row, 128-wide K block), weights one per (128 x 128)
+//     block.  Each 128-wide K block is accumulated on the tensor cores into one
+//     of two TMEM buffers and promoted into fp32 registers by the epilogue warps
+//     as  acc += sa[row,kb] * sw[nb,kb] * partial  -- the exact arithmetic of the
+//     reference's "fake-quant activations x dequantised weights" path
+//     (python/minisgl/models/deepseek_v4.py:145-149, :483) up to summation order.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kRowBytes = 128;  // one swizzle span per tile row
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStages = (BN >= 128) ? 5 : 6;
+  static constexpr int kABytes = kBM * kRowBytes;
+  static constexpr int kBBytes = BN * kRowBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const float* v, int ncols_valid) {
+  if (ncols_valid >= 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+      __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+      __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+      uint4 u;
+      u.x = *reinterpret_cast<uint32_t*>(&p0);
+      u.y = *reinterpret_cast<uint32_t*>(&p1);
+      u.z = *reinterpret_cast<uint32_t*>(&p2);
+      u.w = *reinterpret_cast<uint32_t*>(&p3);
+      reinterpret_cast<uint4*>(dst)[i] = u;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols_valid) dst[i] = f2bf(v[i]);
+  }
+}
+__device__ __forceinline__ void store_row_chunk(float* dst, const float* v, int ncols_valid) {
+  if (ncols_valid >= 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols_valid) dst[i] = v[i];
+  }
+}
+
+template <int BN, bool FP8, typename OutT>
+__global__ void __launch_bounds__(192, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ out,
+               int M, int N, int K, int ldo, const float* __restrict__ sa, const float* __restrict__ sb, int accumulate_out) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  constexpr int BK = FP8 ? 128 : 64;  // elements per k-tile (= 128 bytes)
+  constexpr uint32_t kTmemCols = FP8 ? (2 * BN < 32 ? 32 : 2 * BN) : (BN < 32 ? 32 : BN);
+  constexpr uint32_t kIdesc = FP8 ? umma_idesc(kBM, BN, 0, 0) : umma_idesc(kBM, BN, 1, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint64_t* empty = full + S;
+  uint64_t* tfull = empty + S;   // [2]
+  uint64_t* tempty = tfull + 2;  // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * kBM;
+  const int k_tiles = (K + BK - 1) / BK;
+  const int kblocks = k_tiles;  // FP8: one scale block per k-tile
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 128);
+    mbar_init(&tempty[1], 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const int s = kt % S;
+        const uint32_t ph = (kt / S) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, 1)) break;
+        mbar_expect_tx(&full[s], Cfg::kStageBytes);
+        uint8_t* a = tiles + s * Cfg::kStageBytes;
+        tma_load_2d(a, &tmA, &full[s], kt * BK, m0);
+        tma_load_2d(a + Cfg::kABytes, &tmB, &full[s], kt * BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const int s = kt % S;
+        const uint32_t ph = (kt / S) & 1;
+        uint32_t d = tmem_base;
+        if (FP8) {
+          const int b = kt & 1;
+          if (!mbar_wait(&tempty[b], ((kt >> 1) & 1) ^ 1, abort_flag, 2)) break;
+          d = tmem_base + b * BN;
+        }
+        if (!mbar_wait(&full[s], ph, abort_flag, 3)) break;
+        tc_fence_after();
+        const uint8_t* a = tiles + s * Cfg::kStageBytes;
+        const uint8_t* bt = a + Cfg::kABytes;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t ad = umma_desc_k128(a, k * 32);
+          const uint64_t bd = umma_desc_k128(bt, k * 32);
+          const uint32_t acc = FP8 ? (k > 0) : (kt > 0 || k > 0);
+          if (FP8)
+            umma_f8(d, ad, bd, kIdesc, acc);
+          else
+            umma_f16(d, ad, bd, kIdesc, acc);
+        }
+        umma_commit(&empty[s]);
+        if (FP8) umma_commit(&tfull[kt & 1]);
+      }
+      if (!FP8) umma_commit(&tfull[0]);
+    }
+  } else {
+    // epilogue warps 2..5 ; TMEM lane quarter = warp % 4
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int grow = m0 + row;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    if (!FP8) {
+      bool ok = mbar_wait(&tfull[0], 0, abort_flag, 4);
+      tc_fence_after();
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(lane_addr + c * 32, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          const int col = n0 + c * 32;
+          if (grow < M && col < N) {
+            OutT* dst = out + (size_t)grow * ldo + col;
+            if (accumulate_out) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col + j < N) v[j] += (float)dst[j];
+            }
+            store_row_chunk(dst, v, N - col);
+          }
+        }
+      }
+    } else {
+      float acc[BN];
+#pragma unroll
+      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+      const int nb = n0 >> 7;
+      bool ok = true;
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const int b = kt & 1;
+        if (!mbar_wait(&tfull[b], (kt >> 1) & 1, abort_flag, 5)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float s_a = (grow < M) ? sa[(size_t)grow * kblocks + kt] : 0.f;
+        const float sc = s_a * sb[(size_t)nb * kblocks + kt];
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(lane_addr + b * BN + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(sc, __uint_as_float(r[j]), acc[c * 32 + j]);
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty[b]);
+      }
+      if (ok && grow < M) {
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = n0 + c * 32;
+          if (col < N) {
+            OutT* dst = out + (size_t)grow * ldo + col;
+            if (accumulate_out) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col + j < N) acc[c * 32 + j] += (float)dst[j];
+            }
+            store_row_chunk(dst, &acc[c * 32], N - col);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+template <int BN, bool FP8, typename OutT>
+int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, int ldx, int ldw, int ldo, const float* sa,
+                const float* sb, int accumulate_out, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int BK = FP8 ? 128 : 64;
+  const int esz = FP8 ? 1 : 2;
+  CUtensorMap tmA, tmB;
+  if (dsv4_make_tmap_2d(&tmA, x, FP8 ? 0 : 1, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * esz, BK, kBM, 3)) return 101;
+  if (dsv4_make_tmap_2d(&tmB, w, FP8 ? 0 : 1, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * esz, BK, BN, 3)) return 102;
+  auto kern = gemm_tn_kernel<BN, FP8, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return 103;
+    attr_set = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM);
+  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, M, N, K, ldo, sa, sb, accumulate_out);
+  return (int)cudaGetLastError();
+}
+
+template <bool FP8, typename OutT>
+int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, int ldx, int ldw, int ldo, const float* sa,
+                const float* sb, int acc, int bn, cudaStream_t st) {
+  if (bn == 0) {
+    const int mt = (M + kBM - 1) / kBM;
+    if (mt * ((N + 127) / 128) >= 148 && !FP8)
+      bn = 128;
+    else if (mt * ((N + 63) / 64) >= 148)
+      bn = 64;
+    else
+      bn = 32;
+  }
+  if (FP8 && bn > 64) bn = 64;
+  switch (bn) {
+    case 128:
+      if constexpr (!FP8) return launch_gemm<128, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st);
+    case 64:
+      return launch_gemm<64, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st);
+    default:
+      return launch_gemm<32, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st);
+  }
+}
+
+}  // namespace
+
+// out dtype: 0 = bf16, 1 = fp32.  ld* are row strides in elements.  bn = 0 picks the tile width.
+DSV4_API int dsv4_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo,
+                            int out_fp32, int accumulate_out, int bn, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 8) || (ldx % 8) || (ldw % 8)) return 110;
+  if (out_fp32)
+    return dispatch_bn<false, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, nullptr, nullptr, accumulate_out, bn,
+                                     stream);
+  return dispatch_bn<false, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, nullptr, nullptr,
+                                           accumulate_out, bn, stream);
+}
+
+// x: e4m3 [M,K] with sa fp32 [M, K/128];  w: e4m3 [N,K] with sb fp32 [ceil(N/128), K/128].
+DSV4_API int dsv4_gemm_fp8(const void* x, const void* w, void* out, const float* sa, const float* sb, int M, int N, int K,
+                           int ldx, int ldw, int ldo, int out_fp32, int accumulate_out, int bn, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 128) || (ldx % 16) || (ldw % 16)) return 111;
+  if (out_fp32)
+    return dispatch_bn<true, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn, stream);
+  return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn,
+                                          stream);
+}

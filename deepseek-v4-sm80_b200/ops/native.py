@@ -1,0 +1,93 @@
+"""ctypes bindings to the native libraries built by :mod:`minisgl.ops.build`.
+
+The CUDA library exports ``extern "C"`` launchers that take raw device pointers,
+sizes and a ``cudaStream_t``.  There is no Python fallback for them: when a CUDA
+tensor reaches an op and the library cannot be loaded, the call raises.  The
+reference guards its kernels the same way ("fail closed",
+python/minisgl/kernel/deepseek_v4.py:141-143,384-385).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+_CUDA_LIB = None
+_HOST_LIB = None
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def cuda_lib() -> ctypes.CDLL:
+    """Loads (building first if it is missing and nvcc exists) the sm_100a kernel library."""
+    global _CUDA_LIB
+    if _CUDA_LIB is None:
+        path = _HERE / "libdsv4_b200.so"
+        if not path.exists() or os.environ.get("MINISGL_REBUILD_KERNELS") == "1":
+            from . import build
+
+            build.build_cuda(verbose=False)
+        _CUDA_LIB = ctypes.CDLL(str(path))
+        _CUDA_LIB.dsv4_abi_version.restype = ctypes.c_int
+    return _CUDA_LIB
+
+
+def host_lib() -> ctypes.CDLL:
+    global _HOST_LIB
+    if _HOST_LIB is None:
+        path = _HERE / "libdsv4_host.so"
+        if not path.exists():
+            from . import build
+
+            build.build_host(verbose=False)
+        _HOST_LIB = ctypes.CDLL(str(path))
+        _HOST_LIB.dsv4_first_mismatch.restype = ctypes.c_int64
+        _HOST_LIB.dsv4_first_mismatch.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32]
+        _HOST_LIB.dsv4_host_last_error.restype = ctypes.c_char_p
+    return _HOST_LIB
+
+
+def ptr(t) -> ctypes.c_void_p:
+    if t is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise NativeError(f"{what} failed with code {code}")
+
+
+def call(name: str, *args) -> None:
+    """Calls ``dsv4_<name>(*args, stream)`` and raises on a non-zero return code."""
+    fn = getattr(cuda_lib(), "dsv4_" + name)
+    code = fn(*args, stream())
+    if code != 0:
+        raise NativeError(f"dsv4_{name} failed with code {code}")
+
+
+def read_status(clear: bool = True) -> list:
+    """Device status word: [code, detail_a, detail_b, count, ...]; code 0 means no kernel gave up a wait."""
+    buf = (ctypes.c_int * 8)()
+    check(cuda_lib().dsv4_read_status(buf, ctypes.c_int(1 if clear else 0)), "dsv4_read_status")
+    return list(buf)
+
+
+def assert_device_ok() -> None:
+    st = read_status()
+    if st[0] != 0:
+        raise NativeError(f"a kernel reported status {st[0]} (detail {st[1]}, {st[2]}; {st[3]} occurrences)")
+
+
+I = ctypes.c_int
+F = ctypes.c_float
+L = ctypes.c_int64

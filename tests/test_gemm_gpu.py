@@ -1,0 +1,46 @@
+"""tcgen05 GEMM kernels against the fp32 PyTorch statement of the same product."""
+import pytest
+import torch
+
+from minisgl.ops import gemm, quant
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (8, 4096, 1024), (1, 512, 4096), (300, 1536, 4096), (128, 24, 512)])
+@pytest.mark.parametrize("bn", [0, 32, 64, 128])
+def test_gemm_bf16(m, n, k, bn):
+    torch.manual_seed(0)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    y = gemm.gemm_bf16(x, w, out_dtype=torch.float32, bn=bn)
+    ref = x.float() @ w.float().t()
+    torch.cuda.synchronize()
+    assert torch.allclose(y, ref, rtol=2e-3, atol=2e-3), (y - ref).abs().max().item()
+    yb = gemm.gemm_bf16(x, w, bn=bn)
+    assert torch.allclose(yb.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_gemm_bf16_accumulate():
+    x = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(128, 256, device="cuda", dtype=torch.bfloat16) * 0.1
+    out = torch.ones(64, 128, device="cuda", dtype=torch.float32)
+    gemm.gemm_bf16(x, w, out=out, accumulate=True)
+    ref = x.float() @ w.float().t() + 1
+    assert torch.allclose(out, ref, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 512, 1024), (5, 4096, 4096), (200, 1536, 4096), (128, 64, 256)])
+@pytest.mark.parametrize("bn", [0, 32, 64])
+def test_gemm_fp8_block_scaled(m, n, k, bn):
+    torch.manual_seed(1)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda") * 0.02
+    xq, sx = quant.fp8_act_quant(x)
+    wq, swc = quant.fp8_weight_quant(w)
+    sw = quant.e8m0_decode(swc)
+    y = gemm.gemm_fp8(xq, sx, wq, sw, out_dtype=torch.float32, bn=bn)
+    xf = (xq.float().reshape(m, k // 128, 128) * sx.unsqueeze(-1)).reshape(m, k)
+    wf = quant.fp8_weight_dequant(wq, swc, dtype=torch.float32)
+    ref = xf @ wf.t()
+    assert torch.allclose(y, ref, rtol=1e-3, atol=1e-3), (y - ref).abs().max().item()
