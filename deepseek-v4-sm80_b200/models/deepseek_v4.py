@@ -1,0 +1,163 @@
+"""DeepSeek-V4 decoder: hyper-connected residual streams, MQA latent attention with a sliding window plus
+C4 (indexer-selected) / C128 compressed history, and a routed + shared MoE.
+
+The dataflow per layer follows the reference model (python/minisgl/models/deepseek_v4.py:753-922 for
+attention, :1493-1523 for the MoE, :1614-1628 for the hyper-connection wrapper) but is written against the
+operator facade :mod:`minisgl.ops.api`: on CUDA every call is a hand-written sm_100a kernel, on CPU the
+fp32 PyTorch oracle.  Differences by design:
+
+* dense FP8 weights are multiplied as FP8 on the tensor cores (activations quantised to e4m3 with the same
+  power-of-two block scales the reference uses for its fake-quant), so no BF16 weight copies exist except
+  ``wo_a``, whose input the model does not quantise;
+* attention index surfaces are not materialised: kernels walk the request's page-table row;
+* the embedding is replicated, so a forward has two reductions per layer and one all-gather at the head.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, Optional
+
+import torch
+
+from ..ops import api as O
+from ..ops.ref import RopeSpec
+from .config import ModelConfig
+
+
+@dataclass
+class ForwardBatch:
+    """Device-side description of one forward: T token rows belonging to B requests."""
+
+    input_ids: torch.Tensor      # [T] int32
+    positions: torch.Tensor      # [T] int32
+    slots: torch.Tensor          # [T] int32 request table slot per row
+    out_loc: torch.Tensor        # [T] int32 token location (page*page_size+offset); -1 = do not store
+    last_idx: torch.Tensor       # [B] int64 rows whose logits are wanted
+    page_table: torch.Tensor     # [slots+1, max_len] int32 token locations
+    is_prefill: bool
+    max_context: int             # max position + 1 over the batch (host value; bounds workspace widths)
+    num_valid: Optional[torch.Tensor] = None  # [1] int32: rows >= num_valid are padding (graph replay)
+
+
+class Comm:
+    """Collectives the model needs; the single-rank default does nothing."""
+
+    rank, size = 0, 1
+
+    def all_reduce(self, x: torch.Tensor, tag: str = "") -> torch.Tensor:
+        return x
+
+    def all_gather_last(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+
+class DSV4Model:
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], pool, comm: Optional[Comm] = None,
+                 moe_mode: str = "tp"):
+        self.cfg, self.w, self.pool = cfg, weights, pool
+        self.comm = comm or Comm()
+        self.moe_mode = moe_mode
+        tp = self.comm.size
+        assert cfg.num_heads % tp == 0 and cfg.o_groups % tp == 0, "tp must divide heads and o_groups"
+        self.h_local = cfg.num_heads // tp
+        self.g_local = cfg.o_groups // tp
+        self.ropes = []
+        for l in range(cfg.num_layers):
+            r = cfg.ratio(l)
+            base = cfg.compress_rope_theta if (r and cfg.compress_rope_theta is not None) else cfg.rope_theta
+            self.ropes.append(RopeSpec.make(cfg.rope_head_dim, base, cfg.original_seq_len if r else 0,
+                                            cfg.rope_factor, cfg.beta_fast, cfg.beta_slow))
+        e_local = weights["L0.moe.w13"].shape[0]
+        self.expert_base = self.comm.rank * e_local if (moe_mode == "ep" and tp > 1) else 0
+        self.qat = cfg.nope_head_dim % 64 == 0
+
+    # ------------------------------------------------------------------ blocks
+    def _fp8_linear(self, x, name: str, xq=None):
+        if xq is None:
+            xq = O.fp8_quant(x)
+        return O.gemm_fp8(xq[0], xq[1], self.w[name + ".weight"], self.w[name + ".scale"])
+
+    def attention(self, l: int, y: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        cfg, w, p = self.cfg, self.w, f"L{l}.attn."
+        t = y.shape[0]
+        rope = self.ropes[l]
+        ratio = cfg.ratio(l)
+        kvv = self.pool.layer_views(l)
+        ps = self.pool.page_size
+        yq = O.fp8_quant(y)
+        qkv = O.gemm_fp8(yq[0], yq[1], w[p + "wqkv_a.weight"], w[p + "wqkv_a.scale"])
+        q_lora = O.rms_norm(qkv[:, : cfg.q_lora_rank], w[p + "q_norm.weight"], cfg.rms_norm_eps)
+        kv = qkv[:, cfg.q_lora_rank:]
+        qlq = O.fp8_quant(q_lora)
+        q = O.gemm_fp8(qlq[0], qlq[1], w[p + "wq_b.weight"], w[p + "wq_b.scale"]).view(t, self.h_local, cfg.head_dim)
+        q, kv = O.q_kv_norm_rope_store(q, kv, fb.positions, w[p + "kv_norm.weight"], cfg.rms_norm_eps, rope,
+                                       kvv["swa"], fb.out_loc, self.pool.swa_map, ps, self.qat)
+        topk_idx = topk_len = None
+        if ratio == 4:
+            iq = O.gemm_fp8(qlq[0], qlq[1], w[p + "idx.wq_b.weight"], w[p + "idx.wq_b.scale"])
+            iq = iq.view(t, cfg.index_n_heads, cfg.index_head_dim)
+            iw = O.gemm_bf16(y, w[p + "idx.weights_proj"])
+            qc, wf = O.indexer_q_encode(iq, iw, fb.positions, rope, cfg.index_head_dim ** -0.5,
+                                        cfg.index_n_heads ** -0.5)
+            proj = O.gemm_bf16(y, w[p + "idx.comp.wkv_gate"], out_dtype=torch.float32)
+            pooled = O.compress(proj, fb, 4, cfg.index_head_dim, w[p + "idx.comp.ape"], kvv["idx_ring"],
+                                kvv["idx_ckpt"], ps)
+            O.indexer_kv_store(pooled, fb, w[p + "idx.comp.norm"], cfg.rms_norm_eps, rope, kvv["idx_vals"],
+                               kvv["idx_scale"], ps)
+            topk_idx, topk_len = O.indexer_select(qc, wf, kvv["idx_vals"], kvv["idx_scale"], fb, ps, cfg.index_topk)
+        if ratio:
+            proj = O.gemm_bf16(y, w[p + "comp.wkv_gate"], out_dtype=torch.float32)
+            pooled = O.compress(proj, fb, ratio, cfg.head_dim, w[p + "comp.ape"], kvv["ring"], kvv.get("ckpt"), ps)
+            O.compress_store(pooled, fb, w[p + "comp.norm"], cfg.rms_norm_eps, rope, kvv["comp"], ps, ratio)
+        o = O.attention(q, fb, kvv["swa"], self.pool.swa_map, kvv.get("comp"), ratio, topk_idx, topk_len,
+                        w[p + "sink"], cfg.head_dim ** -0.5, ps, cfg.window_size)
+        o = O.rope_tail(o, fb.positions, rope, inverse=True)
+        dg = cfg.num_heads * cfg.head_dim // cfg.o_groups
+        o = o.reshape(t, self.g_local, dg)
+        wa = w[p + "wo_a.weight_bf16"]
+        o2 = torch.empty(t, self.g_local * cfg.o_lora_rank, dtype=y.dtype, device=y.device)
+        for g in range(self.g_local):
+            O.gemm_bf16(o[:, g], wa[g * cfg.o_lora_rank:(g + 1) * cfg.o_lora_rank],
+                        out=o2[:, g * cfg.o_lora_rank:(g + 1) * cfg.o_lora_rank])
+        out = self._fp8_linear(o2, p + "wo_b")
+        return self.comm.all_reduce(out, "attn")
+
+    def moe(self, l: int, y: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        cfg, w, p = self.cfg, self.w, f"L{l}.moe."
+        idx, wt = O.moe_gate(y, w[p + "gate.weight"], w.get(p + "gate.bias"), cfg.num_experts_per_tok,
+                             cfg.routed_scaling_factor, cfg.scoring_func, w.get(p + "gate.tid2eid"), fb.input_ids,
+                             fb.num_valid)
+        routed = O.moe_experts(y, idx, wt, w[p + "w13"], w[p + "s13"], w[p + "w2"], w[p + "s2"], cfg.swiglu_limit,
+                               self.expert_base)
+        yq = O.fp8_quant(y)
+        gu = O.gemm_fp8(yq[0], yq[1], w[p + "sh_gate_up.weight"], w[p + "sh_gate_up.scale"])
+        a = O.silu_mul_clamp(gu, cfg.swiglu_limit)
+        shared = self._fp8_linear(a, p + "sh_down")
+        out = O.add_cast(routed, shared, fb.num_valid)
+        return self.comm.all_reduce(out, "moe")
+
+    def layer(self, l: int, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        cfg, w, p = self.cfg, self.w, f"L{l}."
+        for blk, fn, norm in (("hc_attn", self.attention, "attn_norm"), ("hc_ffn", self.moe, "ffn_norm")):
+            y, post, comb = O.hc_pre(x, w[p + blk + ".fn"], w[p + blk + ".scale"], w[p + blk + ".base"],
+                                     cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps)
+            y = O.rms_norm(y, w[p + norm + ".weight"], cfg.rms_norm_eps)
+            y = fn(l, y, fb)
+            x = O.hc_post(y, x, post, comb)
+        return x
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, fb: ForwardBatch) -> torch.Tensor:
+        """Returns fp32 logits [B, vocab] for the rows ``fb.last_idx``."""
+        cfg, w = self.cfg, self.w
+        x = O.embed(fb.input_ids, w["embed.weight"], cfg.hc_mult)
+        for l in range(cfg.num_layers):
+            x = self.layer(l, x, fb)
+        if fb.last_idx is not None and fb.last_idx.shape[0] != x.shape[0]:
+            x = x[fb.last_idx]
+        elif fb.last_idx is not None and fb.is_prefill:
+            x = x[fb.last_idx]
+        y = O.hc_head(x, w["hc_head.fn"], w["hc_head.scale"], w["hc_head.base"], cfg.hc_eps, cfg.rms_norm_eps)
+        y = O.rms_norm(y, w["norm.weight"], cfg.rms_norm_eps)
+        logits = O.gemm_bf16(y, w["head.weight"], out_dtype=torch.float32)
+        return self.comm.all_gather_last(logits)

@@ -1,0 +1,218 @@
+"""Operator facade used by the model.
+
+Each function has two bodies: CUDA tensors go to the hand-written sm_100a kernels (``ops/cuda.py`` ->
+``libdsv4_b200.so``), CPU tensors to the PyTorch oracle in ``ops/ref.py``.  There is no third path: a CUDA
+tensor never falls back to PyTorch silently (``cuda.py`` raises when the library is missing).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import gemm as _gemm
+from . import ref
+
+gemm_bf16 = _gemm.gemm_bf16
+gemm_fp8 = _gemm.gemm_fp8
+
+
+def _cu():
+    from . import cuda
+
+    return cuda
+
+
+# --------------------------------------------------------------------------- page-table helpers (CPU path)
+def _locs(fb, pos):
+    """Token locations of (row slot, position) pairs; pos [T,n] may be negative (-> -1)."""
+    p = pos.clamp_min(0).long()
+    loc = fb.page_table[fb.slots.long()[:, None], p]
+    return torch.where(pos >= 0, loc, torch.full_like(loc, -1))
+
+
+def swa_rows(fb, swa_map, ps: int, window: int):
+    off = torch.arange(window - 1, -1, -1, device=fb.positions.device)
+    pos = fb.positions.long()[:, None] - off[None, :]
+    loc = _locs(fb, pos).long()
+    slot = swa_map[(loc.clamp_min(0) // ps)].long()
+    row = slot * ps + loc.clamp_min(0) % ps
+    return torch.where((loc >= 0) & (slot >= 0), row, torch.full_like(row, -1))
+
+
+def comp_rows_all(fb, ps: int, ratio: int, width: int):
+    j = torch.arange(width, device=fb.positions.device)[None, :]
+    n = ((fb.positions.long() + 1) // ratio)[:, None]
+    loc = _locs(fb, torch.where(j < n, j * ratio + ratio - 1, torch.full_like(j, -1))).long()
+    return torch.where(loc >= 0, ref.comp_row(loc.clamp_min(0), ps, ratio), torch.full_like(loc, -1))
+
+
+def comp_rows_from_idx(fb, idx, ps: int, ratio: int):
+    loc = _locs(fb, torch.where(idx >= 0, idx.long() * ratio + ratio - 1, torch.full_like(idx.long(), -1))).long()
+    return torch.where(loc >= 0, ref.comp_row(loc.clamp_min(0), ps, ratio), torch.full_like(loc, -1))
+
+
+# --------------------------------------------------------------------------- elementwise
+def embed(ids, weight, m: int):
+    if ids.is_cuda:
+        return _cu().embed(ids, weight, m)
+    return weight[ids.long()].unsqueeze(1).repeat(1, m, 1)
+
+
+def rms_norm(x, weight, eps: float):
+    if x.is_cuda:
+        return _cu().rms_norm(x, weight, eps)
+    return ref.rms_norm(x, weight, eps)
+
+
+def fp8_quant(x, block: int = 128):
+    if x.is_cuda:
+        return _cu().fp8_quant(x, block)
+    from . import quant
+
+    return quant.fp8_act_quant(x.contiguous(), block)
+
+
+def silu_mul_clamp(gate_up, limit):
+    if gate_up.is_cuda:
+        return _cu().silu_mul_clamp(gate_up, limit)
+    return ref.silu_mul_clamp(gate_up, limit)
+
+
+def add_cast(routed, shared, num_valid=None):
+    if routed.is_cuda:
+        return _cu().add_cast(routed, shared, num_valid)
+    out = (routed.float() + shared.float()).to(routed.dtype)
+    if num_valid is not None:
+        out[int(num_valid):] = 0
+    return out
+
+
+def rope_tail(x, positions, spec, inverse: bool = False):
+    if x.is_cuda:
+        return _cu().rope_tail(x, positions, spec, inverse)
+    return ref.rope_tail(x, positions, spec, inverse).to(x.dtype)
+
+
+def q_kv_norm_rope_store(q, kv, positions, kv_w, eps, spec, swa_cache, out_loc, swa_map, ps: int, qat: bool):
+    if q.is_cuda:
+        return _cu().q_kv_norm_rope_store(q, kv, positions, kv_w, eps, spec, swa_cache, out_loc, swa_map, ps, qat)
+    qo, ko = ref.q_kv_norm_rope(q, kv, positions, kv_w, eps, spec, qat)
+    loc = out_loc.long()
+    slot = swa_map[loc.clamp_min(0) // ps].long()
+    ok = (loc >= 0) & (slot >= 0)
+    swa_cache[(slot * ps + loc % ps)[ok]] = ko[ok]
+    return qo, ko
+
+
+# --------------------------------------------------------------------------- hyper-connections
+def hc_pre(x, fn, scale, base, iters, eps, norm_eps):
+    if x.is_cuda:
+        return _cu().hc_pre(x, fn, scale, base, iters, eps, norm_eps)
+    return ref.hc_pre(x, fn, scale, base, iters, eps, norm_eps)
+
+
+def hc_post(y, residual, post, comb):
+    if y.is_cuda:
+        return _cu().hc_post(y, residual, post, comb)
+    return ref.hc_post(y, residual, post, comb)
+
+
+def hc_head(x, fn, scale, base, eps, norm_eps):
+    if x.is_cuda:
+        return _cu().hc_head(x, fn, scale, base, eps, norm_eps)
+    return ref.hc_head(x, fn, scale, base, eps, norm_eps)
+
+
+# --------------------------------------------------------------------------- compressors
+def compress(proj, fb, ratio: int, d: int, ape, ring, ckpt, ps: int):
+    """Pools group boundaries of this call and then carries the call's rows into the ring / checkpoint state."""
+    if proj.is_cuda:
+        return _cu().compress(proj, fb, ratio, d, ape, ring, ckpt, ps)
+    pooled = ref.compress_pool(proj, fb.positions, fb.slots, ratio, d, ape, ring, ckpt, fb.page_table, ps)
+    ref.compress_state_store(proj, fb.positions, fb.slots, ratio, d, ape, ring, ckpt, fb.page_table, ps)
+    return pooled
+
+
+def compress_store(pooled, fb, norm_w, eps, spec, cache, ps: int, ratio: int):
+    if pooled.is_cuda:
+        return _cu().compress_store(pooled, fb, norm_w, eps, spec, cache, ps, ratio)
+    ok = ((fb.positions.long() + 1) % ratio == 0) & (fb.out_loc >= 0)
+    if bool(ok.any()):
+        y = ref.compress_norm_rope(pooled[ok], fb.positions[ok].long(), norm_w, eps, spec, ratio)
+        cache[ref.comp_row(fb.out_loc[ok].long(), ps, ratio)] = y
+
+
+def indexer_q_encode(q, weights, positions, spec, softmax_scale, head_scale):
+    if q.is_cuda:
+        return _cu().indexer_q_encode(q, weights, positions, spec, softmax_scale, head_scale)
+    return ref.indexer_q_encode(q, weights, positions, spec, softmax_scale, head_scale)
+
+
+def indexer_kv_store(pooled, fb, norm_w, eps, spec, vals, scales, ps: int):
+    if pooled.is_cuda:
+        return _cu().indexer_kv_store(pooled, fb, norm_w, eps, spec, vals, scales, ps)
+    ok = ((fb.positions.long() + 1) % 4 == 0) & (fb.out_loc >= 0)
+    if bool(ok.any()):
+        codes, sc = ref.indexer_kv_encode(pooled[ok], fb.positions[ok].long(), norm_w, eps, spec)
+        rows = ref.comp_row(fb.out_loc[ok].long(), ps, 4)
+        vals[rows] = codes
+        scales[rows] = sc
+
+
+def indexer_select(qc, wf, vals, scales, fb, ps: int, k: int):
+    """Top-k compressed entries per token: (idx int32 [T,k] of compressed indices j, -1 padded; len int32 [T])."""
+    if qc.is_cuda:
+        return _cu().indexer_select(qc, wf, vals, scales, fb, ps, k)
+    width = max(fb.max_context // 4, 1)
+    rows = comp_rows_all(fb, ps, 4, width)
+    lens = ((fb.positions.long() + 1) // 4).to(torch.int32)
+    logits = ref.indexer_logits(qc, wf, vals, scales, rows, lens)
+    return ref.topk_select(logits, lens, k)
+
+
+# --------------------------------------------------------------------------- attention
+def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_len, sink, scale, ps: int,
+              window: int):
+    if q.is_cuda:
+        return _cu().attention(q, fb, swa_cache, swa_map, comp_cache, ratio, topk_idx, topk_len, sink, scale, ps,
+                               window)
+    srows = swa_rows(fb, swa_map, ps, window)
+    crows = None
+    if ratio == 4:
+        idx = torch.where((topk_len > 0)[:, None], topk_idx, torch.full_like(topk_idx, -1))
+        crows = comp_rows_from_idx(fb, idx, ps, 4)
+    elif ratio:
+        crows = comp_rows_all(fb, ps, ratio, max(fb.max_context // ratio, 1))
+    return ref.sparse_attention(q, comp_cache, crows, swa_cache, srows, sink, scale)
+
+
+# --------------------------------------------------------------------------- MoE
+def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid=None):
+    if y.is_cuda:
+        return _cu().moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid)
+    idx, w = ref.moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids)
+    if num_valid is not None:
+        idx[int(num_valid):] = -1
+        w[int(num_valid):] = 0
+    return idx, w
+
+
+def moe_experts(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
+    if y.is_cuda:
+        return _cu().moe_experts(y, idx, w, w13, s13, w2, s2, limit, expert_base)
+    e_local = w13.shape[0]
+    local = idx - expert_base
+    local = torch.where((local >= 0) & (local < e_local) & (idx >= 0), local, torch.full_like(local, -1))
+    return ref.moe_experts(y, local, w, w13, s13, w2, s2, limit)
+
+
+# --------------------------------------------------------------------------- sampling
+def sample(logits, temperature, top_k, top_p, uniform):
+    if logits.is_cuda:
+        return _cu().sample(logits, temperature, top_k, top_p, uniform)
+    return ref.sample(logits, temperature, top_k, top_p, uniform)
+
+
+def argmax(logits):
+    if logits.is_cuda:
+        return _cu().argmax(logits)
+    return logits.argmax(-1)

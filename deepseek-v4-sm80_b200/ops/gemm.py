@@ -25,8 +25,9 @@ def gemm_bf16(x, w, out=None, out_dtype=torch.bfloat16, accumulate=False, bn=0):
     if not x.is_cuda:
         y = (x2.float() @ w.float().t())
         if out is not None:
-            y = y + out.reshape(m, n).float() if accumulate else y
-            out.reshape(m, n).copy_(y.to(out.dtype))
+            y = y.reshape(out.shape)
+            y = y + out.float() if accumulate else y
+            out.copy_(y.to(out.dtype))
             return out
         return y.to(out_dtype).reshape(*x.shape[:-1], n)
     assert x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, (x2.dtype, w.dtype)
