@@ -93,6 +93,8 @@ class DSV4KVPool:
         self.free_pages: List[int] = list(range(sizes.num_pages - 1, -1, -1))
         self.free_swa: List[int] = list(range(sizes.num_swa_slots - 1, -1, -1))
         self.page_ref = [0] * P
+        self.swa_pins = [0] * P          # users of a page's window storage (running requests + the radix tree)
+        self._tree_pinned = set()
         self.swa_version = 0
         self.counters = {"swa_taken": 0, "swa_released": 0, "pages_taken": 0, "pages_released": 0}
 
@@ -132,6 +134,9 @@ class DSV4KVPool:
             if self.page_ref[p] == 0:
                 freed.append(p)
         if freed:
+            for p in freed:
+                self.swa_pins[p] = 0
+                self._tree_pinned.discard(p)
             self.release_swa(freed)
             self.free_pages.extend(freed)
             self.counters["pages_released"] += len(freed)
@@ -165,6 +170,30 @@ class DSV4KVPool:
             self.counters["swa_released"] += len(upd)
             self._push_swa_map(upd, [-1] * len(upd))
         return len(upd)
+
+    def pin_swa(self, pages, owner: str = "req") -> None:
+        """Declares a user of the pages' window storage.  The tree pins a page at most once."""
+        for p in pages:
+            if owner == "tree":
+                if p in self._tree_pinned:
+                    continue
+                self._tree_pinned.add(p)
+            self.swa_pins[p] += 1
+
+    def unpin_swa(self, pages, owner: str = "req") -> None:
+        """Drops a user; window storage of a page nobody uses any more is recycled (the page itself stays)."""
+        drop = []
+        for p in pages:
+            if owner == "tree":
+                if p not in self._tree_pinned:
+                    continue
+                self._tree_pinned.discard(p)
+            if self.swa_pins[p] > 0:
+                self.swa_pins[p] -= 1
+                if self.swa_pins[p] == 0:
+                    drop.append(p)
+        if drop:
+            self.release_swa(drop)
 
     def has_swa(self, page: int) -> bool:
         return self._swa_map_host[page] >= 0

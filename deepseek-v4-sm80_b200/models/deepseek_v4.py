@@ -140,8 +140,7 @@ class DSV4Model:
         cfg, w, p = self.cfg, self.w, f"L{l}."
         for blk, fn, norm in (("hc_attn", self.attention, "attn_norm"), ("hc_ffn", self.moe, "ffn_norm")):
             y, post, comb = O.hc_pre(x, w[p + blk + ".fn"], w[p + blk + ".scale"], w[p + blk + ".base"],
-                                     cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps)
-            y = O.rms_norm(y, w[p + norm + ".weight"], cfg.rms_norm_eps)
+                                     cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps, w[p + norm + ".weight"])
             y = fn(l, y, fb)
             x = O.hc_post(y, x, post, comb)
         return x
@@ -153,11 +152,9 @@ class DSV4Model:
         x = O.embed(fb.input_ids, w["embed.weight"], cfg.hc_mult)
         for l in range(cfg.num_layers):
             x = self.layer(l, x, fb)
-        if fb.last_idx is not None and fb.last_idx.shape[0] != x.shape[0]:
-            x = x[fb.last_idx]
-        elif fb.last_idx is not None and fb.is_prefill:
-            x = x[fb.last_idx]
-        y = O.hc_head(x, w["hc_head.fn"], w["hc_head.scale"], w["hc_head.base"], cfg.hc_eps, cfg.rms_norm_eps)
-        y = O.rms_norm(y, w["norm.weight"], cfg.rms_norm_eps)
+        if fb.last_idx is not None and (fb.is_prefill or fb.last_idx.shape[0] != x.shape[0]):
+            x = x[fb.last_idx].contiguous()
+        y = O.hc_head(x, w["hc_head.fn"], w["hc_head.scale"], w["hc_head.base"], cfg.hc_eps, cfg.rms_norm_eps,
+                      w["norm.weight"])
         logits = O.gemm_bf16(y, w["head.weight"], out_dtype=torch.float32)
         return self.comm.all_gather_last(logits)

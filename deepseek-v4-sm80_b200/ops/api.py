@@ -104,10 +104,14 @@ def q_kv_norm_rope_store(q, kv, positions, kv_w, eps, spec, swa_cache, out_loc, 
 
 
 # --------------------------------------------------------------------------- hyper-connections
-def hc_pre(x, fn, scale, base, iters, eps, norm_eps):
+def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None):
+    """Returns (y, post, comb); with ``norm_w`` y is additionally RMS-normalised (fused on CUDA)."""
     if x.is_cuda:
-        return _cu().hc_pre(x, fn, scale, base, iters, eps, norm_eps)
-    return ref.hc_pre(x, fn, scale, base, iters, eps, norm_eps)
+        return _cu().hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w)
+    y, post, comb = ref.hc_pre(x, fn, scale, base, iters, eps, norm_eps)
+    if norm_w is not None:
+        y = ref.rms_norm(y, norm_w, norm_eps)
+    return y, post, comb
 
 
 def hc_post(y, residual, post, comb):
@@ -116,10 +120,11 @@ def hc_post(y, residual, post, comb):
     return ref.hc_post(y, residual, post, comb)
 
 
-def hc_head(x, fn, scale, base, eps, norm_eps):
+def hc_head(x, fn, scale, base, eps, norm_eps, norm_w=None):
     if x.is_cuda:
-        return _cu().hc_head(x, fn, scale, base, eps, norm_eps)
-    return ref.hc_head(x, fn, scale, base, eps, norm_eps)
+        return _cu().hc_head(x, fn, scale, base, eps, norm_eps, norm_w)
+    y = ref.hc_head(x, fn, scale, base, eps, norm_eps)
+    return ref.rms_norm(y, norm_w, norm_eps) if norm_w is not None else y
 
 
 # --------------------------------------------------------------------------- compressors
@@ -206,10 +211,10 @@ def moe_experts(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
 
 
 # --------------------------------------------------------------------------- sampling
-def sample(logits, temperature, top_k, top_p, uniform):
+def sample(logits, temperature, top_k, top_p, uniform, mask_ids=None):
     if logits.is_cuda:
-        return _cu().sample(logits, temperature, top_k, top_p, uniform)
-    return ref.sample(logits, temperature, top_k, top_p, uniform)
+        return _cu().sample(logits, temperature, top_k, top_p, uniform, mask_ids)
+    return ref.sample(logits, temperature, top_k, top_p, uniform, mask_ids)
 
 
 def argmax(logits):

@@ -1,0 +1,280 @@
+"""Python wrappers around the sm_100a kernels (one function per facade op in :mod:`minisgl.ops.api`).
+
+Every function allocates its outputs with torch (caching allocator, so CUDA-graph capture sees static
+addresses on replay) and launches on the current stream.  Nothing here falls back to PyTorch math.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import native as nv
+from .native import F, I
+from .ref import RopeSpec
+
+
+class RopeParams(ctypes.Structure):
+    _fields_ = [("rotary_dim", ctypes.c_int), ("log_base", ctypes.c_float), ("use_scaling", ctypes.c_int),
+                ("factor", ctypes.c_float), ("low", ctypes.c_float), ("scale_denom", ctypes.c_float)]
+
+
+_ROPE_CACHE = {}
+
+
+def rope_params(spec: RopeSpec) -> RopeParams:
+    rp = _ROPE_CACHE.get(spec)
+    if rp is None:
+        rp = RopeParams(spec.rotary_dim, math.log(spec.base), 1 if spec.use_scaling else 0, spec.factor,
+                        float(spec.low), spec.scale_denom)
+        _ROPE_CACHE[spec] = rp
+    return rp
+
+
+_SMS = {}
+
+
+def num_sms(device) -> int:
+    i = torch.device(device).index or 0
+    if i not in _SMS:
+        _SMS[i] = torch.cuda.get_device_properties(i).multi_processor_count
+    return _SMS[i]
+
+
+def _i32(t):
+    assert t.dtype == torch.int32, t.dtype
+    return nv.ptr(t)
+
+
+# --------------------------------------------------------------------------- elementwise
+def embed(ids, weight, m: int):
+    t, h = ids.shape[0], weight.shape[1]
+    out = torch.empty(t, m, h, dtype=weight.dtype, device=weight.device)
+    nv.call("embed", _i32(ids), nv.ptr(weight), nv.ptr(out), I(t), I(m), I(h))
+    return out
+
+
+def rms_norm(x, weight, eps: float):
+    d = x.shape[-1]
+    x2 = x if x.dim() == 2 else x.reshape(-1, d)
+    assert x2.stride(-1) == 1
+    out = torch.empty(x2.shape[0], d, dtype=x.dtype, device=x.device)
+    nv.call("rms_norm", nv.ptr(x2), I(x2.stride(0)), nv.ptr(weight), nv.ptr(out), I(d), I(x2.shape[0]), I(d), F(eps))
+    return out.reshape(*x.shape[:-1], d)
+
+
+def fp8_quant(x, block: int = 128):
+    k = x.shape[-1]
+    x2 = x if x.dim() == 2 else x.reshape(-1, k)
+    assert x2.stride(-1) == 1
+    rows = x2.shape[0]
+    q = torch.empty(rows, k, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(rows, k // block, dtype=torch.float32, device=x.device)
+    nv.call("fp8_quant", nv.ptr(x2), I(x2.stride(0)), nv.ptr(q), nv.ptr(s), I(rows), I(k), I(block))
+    return q, s
+
+
+def silu_mul_clamp(gate_up, limit):
+    rows, two_i = gate_up.shape
+    out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
+    nv.call("silu_mul_clamp", nv.ptr(gate_up), nv.ptr(out), I(rows), I(two_i // 2), F(limit or 0.0))
+    return out
+
+
+def add_cast(routed, shared, num_valid=None):
+    out = torch.empty_like(routed)
+    nv.call("add_cast", nv.ptr(routed), nv.ptr(shared), nv.ptr(out), I(routed.shape[0]), I(routed.shape[1]),
+            nv.ptr(num_valid))
+    return out
+
+
+def rope_tail(x, positions, spec, inverse: bool = False, pos_offset: int = 0):
+    assert x.is_contiguous()
+    d = x.shape[-1]
+    rows = x.numel() // d
+    heads = rows // positions.shape[0]
+    nv.call("rope_tail", nv.ptr(x), _i32(positions), I(rows), I(heads), I(d), rope_params(spec),
+            I(1 if inverse else 0), I(pos_offset))
+    return x
+
+
+def q_kv_norm_rope_store(q, kv, positions, kv_w, eps, spec, swa_cache, out_loc, swa_map, ps: int, qat: bool):
+    t, h, d = q.shape
+    assert q.is_contiguous() and kv.stride(-1) == 1
+    nv.call("q_kv_norm_rope_store", nv.ptr(q), nv.ptr(kv), I(kv.stride(0)), _i32(positions), nv.ptr(kv_w), F(eps),
+            rope_params(spec), nv.ptr(swa_cache), _i32(out_loc), _i32(swa_map), I(ps), I(t), I(h), I(d),
+            I(1 if qat else 0))
+    return q, kv
+
+
+# --------------------------------------------------------------------------- hyper-connections
+def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None):
+    t, m, h = x.shape
+    assert m == 4 and x.is_contiguous()
+    y = torch.empty(t, h, dtype=x.dtype, device=x.device)
+    post = torch.empty(t, m, dtype=torch.float32, device=x.device)
+    comb = torch.empty(t, m, m, dtype=torch.float32, device=x.device)
+    nv.call("hc_pre", nv.ptr(x), nv.ptr(fn), nv.ptr(scale), nv.ptr(base), nv.ptr(norm_w), nv.ptr(y), nv.ptr(post),
+            nv.ptr(comb), I(t), I(h), I(24), I(iters), F(eps), F(norm_eps), F(norm_eps))
+    return y, post, comb
+
+
+def hc_post(y, residual, post, comb):
+    t, m, h = residual.shape
+    out = torch.empty_like(residual)
+    nv.call("hc_post", nv.ptr(y), nv.ptr(residual), nv.ptr(post), nv.ptr(comb), nv.ptr(out), I(t), I(h))
+    return out
+
+
+def hc_head(x, fn, scale, base, eps, norm_eps, norm_w=None):
+    t, m, h = x.shape
+    x = x.contiguous()
+    y = torch.empty(t, h, dtype=x.dtype, device=x.device)
+    nv.call("hc_pre", nv.ptr(x), nv.ptr(fn), nv.ptr(scale), nv.ptr(base), nv.ptr(norm_w), nv.ptr(y), nv.ptr(None),
+            nv.ptr(None), I(t), I(h), I(4), I(0), F(eps), F(norm_eps), F(norm_eps))
+    return y
+
+
+# --------------------------------------------------------------------------- compressors / indexer producers
+def compress(proj, fb, ratio: int, d: int, ape, ring, ckpt, ps: int):
+    t = proj.shape[0]
+    assert proj.is_contiguous() and proj.dtype == torch.float32
+    out = torch.empty(t, d, dtype=torch.float32, device=proj.device)
+    pt = fb.page_table
+    nv.call("compress_pool", nv.ptr(proj), _i32(fb.positions), _i32(fb.slots), _i32(pt), I(pt.stride(0)),
+            nv.ptr(ring), nv.ptr(ckpt), nv.ptr(ape), nv.ptr(out), I(t), I(d), I(ratio), I(ps))
+    nv.call("compress_state", nv.ptr(proj), _i32(fb.positions), _i32(fb.slots), _i32(pt), I(pt.stride(0)),
+            nv.ptr(ring), nv.ptr(ckpt), nv.ptr(ape), I(t), I(d), I(ratio), I(ps))
+    return out
+
+
+def compress_store(pooled, fb, norm_w, eps, spec, cache, ps: int, ratio: int):
+    t, d = pooled.shape
+    nv.call("compress_store", nv.ptr(pooled), _i32(fb.positions), _i32(fb.out_loc), nv.ptr(norm_w), F(eps),
+            rope_params(spec), nv.ptr(cache), I(t), I(d), I(ps), I(ratio))
+
+
+def indexer_q_encode(q, weights, positions, spec, softmax_scale, head_scale):
+    t, h, d = q.shape
+    assert q.is_contiguous() and weights.is_contiguous() and weights.dtype == torch.bfloat16
+    codes = torch.empty(t, h, d, dtype=torch.uint8, device=q.device)
+    wf = torch.empty(t, h, dtype=torch.float32, device=q.device)
+    nv.call("indexer_q_encode", nv.ptr(q), nv.ptr(weights), _i32(positions), rope_params(spec),
+            F(softmax_scale * head_scale), nv.ptr(codes), nv.ptr(wf), I(t), I(h), I(d))
+    return codes, wf
+
+
+def indexer_kv_store(pooled, fb, norm_w, eps, spec, vals, scales, ps: int):
+    t, d = pooled.shape
+    nv.call("indexer_kv_store", nv.ptr(pooled), _i32(fb.positions), _i32(fb.out_loc), nv.ptr(norm_w), F(eps),
+            rope_params(spec), nv.ptr(vals), nv.ptr(scales), I(t), I(d), I(ps))
+
+
+def indexer_select(qc, wf, vals, scales, fb, ps: int, k: int):
+    t, h, d = qc.shape
+    idx = torch.empty(t, k, dtype=torch.int32, device=qc.device)
+    out_len = torch.empty(t, dtype=torch.int32, device=qc.device)
+    n_max = fb.max_context // 4
+    if n_max <= k:
+        # every row keeps its whole history: the selection is the identity and no logits are needed
+        nv.call("topk", nv.ptr(None), I(k), _i32(fb.positions), nv.ptr(idx), nv.ptr(out_len), I(t), I(k))
+        return idx, out_len
+    width = (n_max + 63) // 64 * 64
+    logits = torch.empty(t, width, dtype=torch.float32, device=qc.device)
+    pt = fb.page_table
+    nv.call("indexer_logits", nv.ptr(qc), nv.ptr(wf), nv.ptr(vals), nv.ptr(scales), _i32(fb.slots),
+            _i32(fb.positions), _i32(pt), I(pt.stride(0)), I(ps), nv.ptr(logits), I(width), I(t), I(h), I(d))
+    nv.call("topk", nv.ptr(logits), I(width), _i32(fb.positions), nv.ptr(idx), nv.ptr(out_len), I(t), I(k))
+    return idx, out_len
+
+
+# --------------------------------------------------------------------------- attention
+def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_len, sink, scale, ps: int,
+              window: int):
+    t, h, d = q.shape
+    o = torch.empty_like(q)
+    mode = 1 if ratio == 4 else (2 if ratio else 0)
+    pt = fb.page_table
+    nv.call("sparse_attention", nv.ptr(q), nv.ptr(o), _i32(fb.slots), _i32(fb.positions), _i32(pt), I(pt.stride(0)),
+            nv.ptr(swa_cache), _i32(swa_map), nv.ptr(comp_cache if mode else None),
+            nv.ptr(topk_idx if mode == 1 else None), nv.ptr(topk_len if mode == 1 else None),
+            I(topk_idx.shape[1] if mode == 1 else 0), I(mode), I(ratio), nv.ptr(sink), F(scale), I(ps), I(window),
+            nv.ptr(fb.num_valid), I(t), I(h), I(d))
+    return o
+
+
+# --------------------------------------------------------------------------- MoE
+_SCORING = {"sqrtsoftplus": 0, "sigmoid": 1, "softmax": 2}
+_GATE_BF16 = {}
+
+
+def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid=None):
+    from .gemm import gemm_bf16
+
+    key = gate_w.data_ptr()
+    wb = _GATE_BF16.get(key)
+    if wb is None:  # the router weight is bf16 in the checkpoint; its fp32 copy converts back losslessly
+        wb = gate_w.to(torch.bfloat16)
+        _GATE_BF16[key] = wb
+    t, e = y.shape[0], gate_w.shape[0]
+    scores = gemm_bf16(y, wb, out_dtype=torch.float32)
+    idx = torch.empty(t, topk, dtype=torch.int32, device=y.device)
+    wts = torch.empty(t, topk, dtype=torch.float32, device=y.device)
+    nv.call("moe_topk", nv.ptr(scores), nv.ptr(bias if tid2eid is None else None), nv.ptr(tid2eid),
+            nv.ptr(token_ids), nv.ptr(num_valid), nv.ptr(idx), nv.ptr(wts), I(t), I(e), I(topk), F(scaling),
+            I(_SCORING[scoring]))
+    return idx, wts
+
+
+def moe_routed(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
+    """Returns (route_rows bf16 [T*topk, H], plan int32) for :func:`moe_finalize`."""
+    t, h = y.shape
+    topk = idx.shape[1]
+    routes = t * topk
+    e_local, two_i = w13.shape[0], w13.shape[1]
+    inter = two_i // 2
+    nt = 32 if routes <= 32 * e_local else 128
+    max_tiles = min(e_local, routes) + routes // nt + 1
+    plan = torch.empty(4 + 3 * max_tiles + 3 * routes, dtype=torch.int32, device=y.device)
+    nv.call("moe_plan", nv.ptr(idx), nv.ptr(w), I(routes), I(e_local), I(expert_base), I(nt), nv.ptr(plan),
+            I(max_tiles))
+    xs = torch.empty(routes, h, dtype=y.dtype, device=y.device)
+    nv.call("moe_permute", nv.ptr(y), nv.ptr(xs), nv.ptr(plan), I(routes), I(max_tiles), I(topk), I(h))
+    act = torch.empty(routes, inter, dtype=y.dtype, device=y.device)
+    sms = num_sms(y.device)
+    nv.call("moe_gemm", I(1), I(nt), nv.ptr(w13), nv.ptr(s13), nv.ptr(xs), I(routes), nv.ptr(plan), I(routes),
+            I(max_tiles), nv.ptr(act), I(e_local), I(h), I(inter), I(inter), F(limit or 0.0), I(sms))
+    rows = torch.empty(routes, h, dtype=y.dtype, device=y.device)
+    nv.call("moe_gemm", I(2), I(nt), nv.ptr(w2), nv.ptr(s2), nv.ptr(act), I(routes), nv.ptr(plan), I(routes),
+            I(max_tiles), nv.ptr(rows), I(e_local), I(inter), I(h), I(h), F(0.0), I(sms))
+    return rows, plan, max_tiles
+
+
+def moe_finalize(rows, plan, max_tiles, shared, num_valid, t, topk, h):
+    out = torch.empty(t, h, dtype=rows.dtype, device=rows.device)
+    nv.call("moe_finalize", nv.ptr(rows), nv.ptr(plan), I(t * topk), I(max_tiles), nv.ptr(shared), nv.ptr(out),
+            nv.ptr(num_valid), I(t), I(topk), I(h))
+    return out
+
+
+def moe_experts(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
+    rows, plan, max_tiles = moe_routed(y, idx, w, w13, s13, w2, s2, limit, expert_base)
+    return moe_finalize(rows, plan, max_tiles, None, None, y.shape[0], idx.shape[1], y.shape[1])
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax(logits):
+    b, v = logits.shape
+    out = torch.empty(b, dtype=torch.int64, device=logits.device)
+    nv.call("argmax", nv.ptr(logits), nv.ptr(out), I(b), I(v))
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, uniform, mask_ids=None):
+    b, v = logits.shape
+    out = torch.empty(b, dtype=torch.int64, device=logits.device)
+    n_mask = 0 if mask_ids is None else mask_ids.shape[1]
+    nv.call("sample", nv.ptr(logits), I(b), I(v), nv.ptr(temperature), nv.ptr(top_k), nv.ptr(top_p), nv.ptr(uniform),
+            nv.ptr(mask_ids), I(n_mask), nv.ptr(out))
+    return out

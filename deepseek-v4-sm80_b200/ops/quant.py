@@ -89,8 +89,8 @@ def fp4_quant(w: torch.Tensor, group: int = 32):
     g = w.float().reshape(*w.shape[:-1], k // group, group)
     scale = pow2_scale(g.abs().amax(dim=-1, keepdim=True), limit=6.0, floor=1e-12)
     v = (g / scale).clamp(-6.0, 6.0)
-    mags = torch.tensor(_E2M1, dtype=torch.float32, device=w.device)
-    idx = (v.abs().unsqueeze(-1) - mags).abs().argmin(dim=-1)
+    bounds = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=torch.float32, device=w.device)
+    idx = torch.bucketize(v.abs(), bounds)
     code = (idx | ((v < 0) & (idx > 0)).to(idx.dtype) * 8).to(torch.uint8).reshape(*w.shape[:-1], k)
     packed = (code[..., 0::2] | (code[..., 1::2] << 4)).view(torch.int8)
     return packed, e8m0_encode(scale.squeeze(-1))

@@ -430,3 +430,63 @@ def sample(logits, temperature, top_k, top_p, uniform):
         pick = int(torch.searchsorted(cdf, torch.tensor(u, device=cdf.device), right=True).clamp(max=v - 1))
         out[r] = ids[pick]
     return out
+
+
+def topk_select(logits, lens, k: int):  # noqa: F811  (final definition: index-ordered output)
+    """Per row: the k entries of logits[:len] that come first under (score desc, index asc), returned sorted by
+    index; rows with len <= k keep 0..len-1; a non-finite score inside the valid range invalidates the row
+    (len -1).  Returns (idx int32 [T,k] padded with -1, out_len int32 [T])  (csrc/jit/dsv4_topk_v1.cu:275-479;
+    the reference emits score order, attention does not depend on it)."""
+    t = logits.shape[0]
+    idx = torch.full((t, k), -1, dtype=torch.int32, device=logits.device)
+    out_len = torch.zeros(t, dtype=torch.int32, device=logits.device)
+    for r in range(t):
+        n = min(int(lens[r]), logits.shape[1])
+        if n <= 0:
+            continue
+        if n <= k:
+            idx[r, :n] = torch.arange(n, dtype=torch.int32, device=logits.device)
+            out_len[r] = n
+            continue
+        row = logits[r, :n].float()
+        if not bool(torch.isfinite(row).all()):
+            out_len[r] = -1
+            continue
+        vals = row.tolist()
+        order = sorted(sorted(range(n), key=lambda i: (-vals[i], i))[:k])
+        idx[r] = torch.tensor(order, dtype=torch.int32, device=logits.device)
+        out_len[r] = k
+    return idx, out_len
+
+
+def sample(logits, temperature, top_k, top_p, uniform, mask_ids=None):  # noqa: F811
+    """Greedy where temperature <= 0 or top_k == 1.  Otherwise p = softmax(logits / T); with the vocabulary ordered
+    by (p desc, id asc) rank r is kept iff (top_k <= 0 or r < top_k) and the mass before it is < top_p; the sample
+    is the first kept id, in id order, whose running kept mass exceeds u * kept_mass.  ``mask_ids`` [B, n] are ids
+    forced to -inf first.  Returns int64 [B]."""
+    b, v = logits.shape
+    lg = logits.double().clone()
+    if mask_ids is not None:
+        for r in range(b):
+            lg[r, mask_ids[r].long()] = float("-inf")
+    out = lg.argmax(-1)
+    for r in range(b):
+        tmp = float(temperature[r])
+        k = int(top_k[r])
+        if tmp <= 0 or k == 1:
+            continue
+        p = torch.softmax(lg[r] / tmp, dim=-1)
+        order = torch.sort(p, descending=True, stable=True).indices
+        ps = p[order]
+        before = ps.cumsum(0) - ps
+        keep_sorted = before < float(top_p[r]) if float(top_p[r]) < 1.0 else torch.ones(v, dtype=torch.bool)
+        if k > 0:
+            keep_sorted = keep_sorted & (torch.arange(v) < k)
+        keep = torch.zeros(v, dtype=torch.bool)
+        keep[order[keep_sorted]] = True
+        pk = torch.where(keep, p, torch.zeros_like(p))
+        cdf = pk.cumsum(0)
+        target = float(uniform[r]) * float(cdf[-1])
+        pick = int(torch.searchsorted(cdf, torch.tensor(target, dtype=cdf.dtype), right=True).clamp(max=v - 1))
+        out[r] = pick
+    return out

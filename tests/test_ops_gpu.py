@@ -1,0 +1,291 @@
+"""Each sm_100a kernel against the fp32 PyTorch oracle (minisgl.ops.ref) of the same operator, at the flagship
+per-layer shapes (hidden 4096, head dim 512, rope 64, indexer 64 x 128)."""
+import math
+import types
+
+import pytest
+import torch
+
+from minisgl.ops import api as O
+from minisgl.ops import quant, ref
+from minisgl.ops.ref import RopeSpec
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ROPE = RopeSpec.make(64, 160000.0, 65536, 16.0, 32, 1)
+ROPE0 = RopeSpec.make(64, 10000.0)
+
+
+def bf(*shape, std=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+
+
+def close(a, b, atol=2e-2, rtol=2e-2, frac=1.0):
+    a, b = a.float().cpu(), b.float().cpu()
+    ok = (a - b).abs() <= atol + rtol * b.abs()
+    assert ok.float().mean().item() >= frac, ((a - b).abs().max().item(), ok.float().mean().item())
+
+
+def test_embed_rmsnorm_silu_addcast():
+    w = bf(1000, 4096)
+    ids = torch.randint(0, 1000, (37,), dtype=torch.int32)
+    out = O.embed(ids.to(DEV), w.to(DEV), 4)
+    assert torch.equal(out.cpu(), w[ids.long()].unsqueeze(1).repeat(1, 4, 1))
+    x, g = bf(37, 1536, seed=1), bf(1024, std=0.3, seed=2) + 1
+    close(O.rms_norm(x.to(DEV)[:, :1024], g.to(DEV), 1e-6), ref.rms_norm(x[:, :1024], g, 1e-6))
+    gu = bf(19, 4096, std=3.0, seed=3)
+    close(O.silu_mul_clamp(gu.to(DEV), 7.0), ref.silu_mul_clamp(gu, 7.0))
+    a, b = bf(9, 4096, seed=4), bf(9, 4096, seed=5)
+    nvalid = torch.tensor([7], dtype=torch.int32, device=DEV)
+    o = O.add_cast(a.to(DEV), b.to(DEV), nvalid).cpu()
+    exp = (a.float() + b.float()).to(torch.bfloat16)
+    exp[7:] = 0
+    assert torch.equal(o, exp)
+
+
+@pytest.mark.parametrize("block", [128, 64])
+def test_fp8_quant_matches_oracle(block):
+    x = bf(33, 1024, std=2.0, seed=6)
+    x[0, :128] = 0
+    q, s = O.fp8_quant(x.to(DEV), block)
+    qr, sr = quant.fp8_act_quant(x, block)
+    assert torch.equal(s.cpu(), sr)
+    assert torch.equal(q.cpu().view(torch.uint8), qr.view(torch.uint8))
+
+
+def test_rope_and_qkv_norm_store():
+    t, h = 21, 8
+    pos = torch.randint(0, 200000, (t,), dtype=torch.int32)
+    x = bf(t, h, 512, seed=7)
+    y = O.rope_tail(x.to(DEV).clone(), pos.to(DEV), ROPE, inverse=True)
+    close(y, ref.rope_tail(x, pos, ROPE, True).to(torch.bfloat16), atol=3e-2)
+    q, qkv, kw = bf(t, h, 512, seed=8), bf(t, 1536, seed=9), bf(512, std=0.2, seed=10) + 1
+    ps = 256
+    swa = torch.zeros(4 * ps, 512, dtype=torch.bfloat16)
+    swa_map = torch.tensor([2, -1, 0, 3], dtype=torch.int32)
+    out_loc = torch.randperm(3 * ps)[:t].to(torch.int32)
+    out_loc[3] = -1
+    qd, kvd = q.to(DEV), qkv.to(DEV)
+    swad = swa.to(DEV)
+    O.q_kv_norm_rope_store(qd, kvd[:, 1024:], pos.to(DEV), kw.to(DEV), 1e-6, ROPE, swad, out_loc.to(DEV),
+                           swa_map.to(DEV), ps, True)
+    qo, ko = O.q_kv_norm_rope_store(q.clone(), qkv[:, 1024:].clone(), pos, kw, 1e-6, ROPE, swa, out_loc, swa_map, ps,
+                                    True)
+    close(qd, qo, atol=3e-2)
+    close(kvd[:, 1024:], ko, atol=3e-2, frac=0.995)  # an e4m3 rounding flip in the QAT moves one value by an fp8 ulp
+    close(swad, swa, atol=3e-2, frac=0.999)
+    assert torch.equal(kvd[:, :1024].cpu(), qkv[:, :1024])
+
+
+def test_hc_pre_post_head():
+    t, h = 11, 4096
+    x = bf(t, 4, h, seed=11)
+    fn, sc, base = bf(24, 4 * h, std=0.02, seed=12), torch.tensor([1.0, 0.7, 1.3]), torch.randn(24) * 0.5
+    nw = bf(h, std=0.2, seed=13) + 1
+    y, post, comb = O.hc_pre(x.to(DEV), fn.to(DEV), sc.to(DEV), base.to(DEV), 20, 1e-6, 1e-6, nw.to(DEV))
+    yr, pr, cr = O.hc_pre(x, fn, sc, base, 20, 1e-6, 1e-6, nw)
+    close(post, pr, atol=1e-3)
+    close(comb, cr, atol=1e-3)
+    close(y, yr, atol=3e-2)
+    yy = bf(t, h, seed=14)
+    close(O.hc_post(yy.to(DEV), x.to(DEV), post, comb), ref.hc_post(yy, x, pr, cr), atol=4e-2)
+    fh = bf(4, 4 * h, std=0.02, seed=15)
+    close(O.hc_head(x.to(DEV), fh.to(DEV), sc[:1].to(DEV), base[:4].to(DEV), 1e-6, 1e-6, nw.to(DEV)),
+          O.hc_head(x, fh, sc[:1], base[:4], 1e-6, 1e-6, nw), atol=3e-2)
+
+
+def _fb(pos, slots, page_table, out_loc=None, max_context=None):
+    return types.SimpleNamespace(positions=pos, slots=slots, page_table=page_table, out_loc=out_loc,
+                                 max_context=max_context or int(pos.max()) + 1, num_valid=None)
+
+
+def _mk_batch(ps=256, seed=0):
+    """Two requests: slot 0 continues at position 250 with 20 tokens (crosses a page), slot 2 is a fresh prefill."""
+    g = torch.Generator().manual_seed(seed)
+    pt = torch.zeros(4, 1024, dtype=torch.int32)
+    pages = torch.randperm(12, generator=g).tolist()
+    for s in range(4):
+        for k in range(3):
+            p = pages[s * 3 + k]
+            pt[s, k * ps:(k + 1) * ps] = torch.arange(p * ps, (p + 1) * ps, dtype=torch.int32)
+    pos = torch.cat([torch.arange(250, 270), torch.arange(0, 300)]).to(torch.int32)
+    slots = torch.cat([torch.zeros(20), torch.full((300,), 2)]).to(torch.int32)
+    out_loc = pt[slots.long(), pos.long()]
+    return pos, slots, pt, out_loc
+
+
+@pytest.mark.parametrize("ratio,d", [(4, 512), (4, 128), (128, 512)])
+def test_compress_pool_and_state(ratio, d):
+    ps = 256
+    pos, slots, pt, out_loc = _mk_batch(ps)
+    t = pos.shape[0]
+    c = 2 if ratio == 4 else 1
+    proj = torch.randn(t, 2 * c * d)
+    ape = torch.randn(ratio, c * d) * 0.5
+    ring_len = 8 if ratio == 4 else ratio
+    ring = torch.randn(4 * ring_len, 2 * c * d)
+    ckpt = torch.randn(13 * 4, 2 * d) if ratio == 4 else None
+    fb = _fb(pos, slots, pt, out_loc)
+    ring_d, ckpt_d = ring.to(DEV), (ckpt.to(DEV) if ckpt is not None else None)
+    fbd = _fb(pos.to(DEV), slots.to(DEV), pt.to(DEV), out_loc.to(DEV))
+    out = O.compress(proj.to(DEV), fbd, ratio, d, ape.to(DEV), ring_d, ckpt_d, ps)
+    exp = O.compress(proj, fb, ratio, d, ape, ring, ckpt, ps)
+    close(out, exp, atol=1e-4, rtol=1e-4)
+    close(ring_d, ring, atol=1e-5)
+    if ckpt is not None:
+        close(ckpt_d, ckpt, atol=1e-6)
+
+
+def test_compress_store_and_indexer_producers():
+    ps = 256
+    pos, slots, pt, out_loc = _mk_batch(ps)
+    t = pos.shape[0]
+    fb, fbd = _fb(pos, slots, pt, out_loc), _fb(pos.to(DEV), slots.to(DEV), pt.to(DEV), out_loc.to(DEV))
+    for ratio in (4, 128):
+        pooled = torch.randn(t, 512)
+        nw = bf(512, std=0.2, seed=20) + 1
+        rows = 13 * max(ps // ratio, 1)
+        cache = torch.zeros(rows, 512, dtype=torch.bfloat16)
+        cache_d = cache.to(DEV)
+        O.compress_store(pooled.to(DEV), fbd, nw.to(DEV), 1e-6, ROPE, cache_d, ps, ratio)
+        O.compress_store(pooled, fb, nw, 1e-6, ROPE, cache, ps, ratio)
+        close(cache_d, cache, atol=3e-2)
+    pooled = torch.randn(t, 128)
+    nwf = torch.rand(128) + 0.5
+    vals, scales = torch.zeros(13 * 64, 128, dtype=torch.uint8), torch.zeros(13 * 64)
+    vd, sd = vals.to(DEV), scales.to(DEV)
+    O.indexer_kv_store(pooled.to(DEV), fbd, nwf.to(DEV), 1e-6, ROPE, vd, sd, ps)
+    O.indexer_kv_store(pooled, fb, nwf, 1e-6, ROPE, vals, scales, ps)
+    assert torch.equal(sd.cpu(), scales)
+    dq = lambda v, s: v.view(quant.FP8).float() * s[:, None]
+    close(dq(vd.cpu(), sd.cpu()), dq(vals, scales), atol=2e-2, frac=0.995)
+    q, w = bf(t, 64, 128, seed=21), bf(t, 64, seed=22)
+    qc, wf = O.indexer_q_encode(q.to(DEV), w.to(DEV), pos.to(DEV), ROPE, 128 ** -0.5, 64 ** -0.5)
+    qr, wr = O.indexer_q_encode(q, w, pos, ROPE, 128 ** -0.5, 64 ** -0.5)
+    close(wf, wr, atol=1e-6, rtol=1e-3)
+    assert (qc.cpu() == qr).float().mean() > 0.995
+
+
+def test_indexer_logits_and_topk():
+    ps = 256
+    g = torch.Generator().manual_seed(3)
+    pt = torch.zeros(2, 4096, dtype=torch.int32)
+    pages = torch.randperm(16, generator=g).tolist()
+    for k in range(16):
+        pt[1, k * ps:(k + 1) * ps] = torch.arange(pages[k] * ps, (pages[k] + 1) * ps, dtype=torch.int32)
+    pos = torch.tensor([4000, 2100, 2047, 700, 3], dtype=torch.int32)
+    slots = torch.ones(5, dtype=torch.int32)
+    t = 5
+    qc = torch.randn(t, 64, 128, generator=g).to(quant.FP8).view(torch.uint8)
+    wf = torch.randn(t, 64, generator=g)
+    vals = torch.randn(16 * 64, 128, generator=g).to(quant.FP8).view(torch.uint8)
+    scales = torch.rand(16 * 64, generator=g) + 0.5
+    fb = _fb(pos, slots, pt, None, 4001)
+    fbd = _fb(pos.to(DEV), slots.to(DEV), pt.to(DEV), None, 4001)
+    idx, ln = O.indexer_select(qc.to(DEV), wf.to(DEV), vals.to(DEV), scales.to(DEV), fbd, ps, 512)
+    idx_r, ln_r = O.indexer_select(qc, wf, vals, scales, fb, ps, 512)
+    assert torch.equal(ln.cpu(), ln_r)
+    for r in range(t):
+        a, b = set(idx[r].cpu().tolist()), set(idx_r[r].tolist())
+        assert len(a ^ b) <= 4, (r, len(a ^ b))  # fp32 summation order may swap near-ties at the threshold
+    # determinism and the tie rule on exact inputs
+    from minisgl.ops import cuda
+
+    lg = torch.zeros(2, 2048)
+    lg[0, 100:900] = 1.0
+    lg[1] = torch.arange(2048).float()
+    p2 = torch.tensor([8191, 8191], dtype=torch.int32)
+    o1 = torch.empty(2, 512, dtype=torch.int32, device=DEV)
+    l1 = torch.empty(2, dtype=torch.int32, device=DEV)
+    cuda.nv.call("topk", cuda.nv.ptr(lg.to(DEV)), cuda.I(2048), cuda.nv.ptr(p2.to(DEV)), cuda.nv.ptr(o1),
+                 cuda.nv.ptr(l1), cuda.I(2), cuda.I(512))
+    assert o1[0].cpu().tolist() == list(range(100, 612))
+    assert o1[1].cpu().tolist() == list(range(1536, 2048))
+
+
+@pytest.mark.parametrize("heads", [8, 64])
+@pytest.mark.parametrize("ratio", [0, 4, 128])
+def test_sparse_attention(heads, ratio):
+    ps = 256
+    g = torch.Generator().manual_seed(heads + ratio)
+    pt = torch.zeros(3, 2048, dtype=torch.int32)
+    pages = torch.randperm(8, generator=g).tolist()
+    for k in range(8):
+        pt[1, k * ps:(k + 1) * ps] = torch.arange(pages[k] * ps, (pages[k] + 1) * ps, dtype=torch.int32)
+    pos = torch.tensor([0, 5, 127, 128, 1000, 2047], dtype=torch.int32)
+    t = pos.shape[0]
+    slots = torch.ones(t, dtype=torch.int32)
+    swa_map = torch.randperm(9, generator=g).to(torch.int32)
+    swa = bf(9 * ps, 512, seed=30)
+    comp = bf(9 * max(ps // max(ratio, 1), 1), 512, seed=31) if ratio else None
+    q = bf(t, heads, 512, seed=32)
+    sink = torch.randn(heads, generator=g)
+    tk_idx = tk_len = None
+    if ratio == 4:
+        tk_idx = torch.full((t, 512), -1, dtype=torch.int32)
+        tk_len = torch.zeros(t, dtype=torch.int32)
+        for r in range(t):
+            n = min((int(pos[r]) + 1) // 4, 512)
+            sel = torch.randperm(max((int(pos[r]) + 1) // 4, 1), generator=g)[:n].sort().values
+            tk_idx[r, :n] = sel.to(torch.int32)
+            tk_len[r] = n
+    fb = _fb(pos, slots, pt, None, 2048)
+    fbd = _fb(pos.to(DEV), slots.to(DEV), pt.to(DEV), None, 2048)
+    dv = lambda x: None if x is None else x.to(DEV)
+    o = O.attention(q.to(DEV), fbd, swa.to(DEV), swa_map.to(DEV), dv(comp), ratio, dv(tk_idx), dv(tk_len),
+                    sink.to(DEV), 512 ** -0.5, ps, 128)
+    o_r = O.attention(q, fb, swa, swa_map, comp, ratio, tk_idx, tk_len, sink, 512 ** -0.5, ps, 128)
+    close(o, o_r, atol=2e-2)
+
+
+def test_moe_gate_and_experts():
+    g = torch.Generator().manual_seed(5)
+    t, h, e, inter, k = 45, 4096, 16, 512, 6
+    y = bf(t, h, seed=40)
+    gw = bf(e, h, std=0.1, seed=41).float()
+    bias = torch.randn(e, generator=g) * 0.01
+    ids = torch.randint(0, 100, (t,), dtype=torch.int32)
+    idx, wt = O.moe_gate(y.to(DEV), gw.to(DEV), bias.to(DEV), k, 1.5, "sqrtsoftplus", None, ids.to(DEV))
+    idx_r, wt_r = O.moe_gate(y, gw, bias, k, 1.5, "sqrtsoftplus", None, ids)
+    same = (idx.cpu().sort(-1).values == idx_r.sort(-1).values).all(-1).float().mean()
+    assert same > 0.9, same
+    w13, s13 = quant.fp4_quant(torch.randn(e, 2 * inter, h, generator=g) * 0.02)
+    w2, s2 = quant.fp4_quant(torch.randn(e, h, inter, generator=g) * 0.02)
+    out = O.moe_experts(y.to(DEV), idx_r.to(DEV), wt_r.to(DEV), w13.to(DEV), s13.to(DEV), w2.to(DEV), s2.to(DEV),
+                        7.0, 0)
+    exp = O.moe_experts(y, idx_r, wt_r, w13, s13, w2, s2, 7.0, 0)
+    close(out, exp, atol=3e-2, rtol=3e-2, frac=0.999)
+    # expert-parallel slice: only experts [8, 16) are local
+    out2 = O.moe_experts(y.to(DEV), idx_r.to(DEV), wt_r.to(DEV), w13[8:].to(DEV), s13[8:].to(DEV), w2[8:].to(DEV),
+                         s2[8:].to(DEV), 7.0, 8)
+    exp2 = O.moe_experts(y, idx_r, wt_r, w13[8:], s13[8:], w2[8:], s2[8:], 7.0, 8)
+    close(out2, exp2, atol=3e-2, rtol=3e-2, frac=0.999)
+
+
+def test_moe_experts_many_routes_per_expert():
+    g = torch.Generator().manual_seed(6)
+    t, h, e, inter, k = 700, 4096, 4, 256, 2
+    y = bf(t, h, seed=42)
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).to(torch.int32)
+    wt = torch.rand(t, k, generator=g)
+    w13, s13 = quant.fp4_quant(torch.randn(e, 2 * inter, h, generator=g) * 0.02)
+    w2, s2 = quant.fp4_quant(torch.randn(e, h, inter, generator=g) * 0.02)
+    out = O.moe_experts(y.to(DEV), idx.to(DEV), wt.to(DEV), w13.to(DEV), s13.to(DEV), w2.to(DEV), s2.to(DEV), 7.0, 0)
+    exp = O.moe_experts(y, idx, wt, w13, s13, w2, s2, 7.0, 0)
+    close(out, exp, atol=3e-2, rtol=3e-2, frac=0.999)
+
+
+def test_sampling():
+    g = torch.Generator().manual_seed(7)
+    b, v = 6, 129280
+    lg = torch.randn(b, v, generator=g) * 3
+    temp = torch.tensor([0.0, 1.0, 0.7, 1.0, 1.3, 0.5])
+    tk = torch.tensor([-1, 1, -1, 40, 5, -1], dtype=torch.int32)
+    tp = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.9, 0.8])
+    u = torch.rand(b, generator=g)
+    mask = torch.stack([lg.argmax(-1), torch.zeros(b, dtype=torch.long)], 1).to(torch.int32)
+    out = O.sample(lg.to(DEV), temp.to(DEV), tk.to(DEV), tp.to(DEV), u.to(DEV), mask.to(DEV))
+    exp = O.sample(lg, temp, tk, tp, u, mask)
+    assert torch.equal(out.cpu(), exp), (out.cpu(), exp)
+    assert torch.equal(O.argmax(lg.to(DEV)).cpu(), lg.argmax(-1))
