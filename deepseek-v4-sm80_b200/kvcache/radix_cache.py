@@ -178,18 +178,24 @@ class RadixPrefixCache:
             node = child
         return canon, node
 
+    def _tail_pages(self, node: RadixNode) -> List[int]:
+        """Pages whose window storage a hit at the path's last aligned boundary (or at its end) would need."""
+        n = node.path_len()
+        pages = self._path_pages(node, n)
+        boundary = n // self.align * self.align
+        first = max(boundary - self.window, 0) // self.ps
+        return pages[first:]
+
     def _retire_tail(self, node: RadixNode) -> None:
         if node is self.root or not node.pages:
             return
-        n_tail = (self.window + self.ps - 1) // self.ps
-        self.pool.unpin_swa(node.pages[-n_tail:], owner="tree")
+        self.pool.unpin_swa(self._tail_pages(node), owner="tree")
 
     def pin_tail(self, node: RadixNode) -> None:
-        """Keeps window storage alive for the last ``window`` tokens of a cached path."""
+        """Keeps window storage alive for the tail of a cached path so that a later hit can resume there."""
         if node is self.root or not node.pages:
             return
-        n_tail = (self.window + self.ps - 1) // self.ps
-        self.pool.pin_swa(node.pages[-n_tail:], owner="tree")
+        self.pool.pin_swa(self._tail_pages(node), owner="tree")
 
     def evictable_pages(self) -> int:
         total, stack = 0, [self.root]

@@ -1,0 +1,1 @@
+from .llm import LLM, RequestOutput  # noqa: F401

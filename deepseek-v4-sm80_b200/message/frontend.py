@@ -1,0 +1,20 @@
+"""Messages consumed by the API frontend (python/minisgl/message/frontend.py:9-33)."""
+from __future__ import annotations
+
+from typing import Any, List, Optional
+
+from .utils import message
+
+
+@message
+class UserReply:
+    uid: int
+    incremental_output: str
+    finished: bool
+    finish_reason: Optional[str] = None
+    num_tokens: int = 0
+
+
+@message
+class BatchFrontendMsg:
+    data: List[Any]

@@ -30,12 +30,12 @@ def test_gpu_forward_matches_cpu_oracle():
         lc = cpu.step([(0, chunk)])
         lg = gpu.step([(0, chunk)])
     torch.cuda.synchronize()
-    scale = lc.std().item()
-    assert (lg.cpu() - lc).abs().max().item() < 0.15 * scale + 0.05, ((lg.cpu() - lc).abs().max().item(), scale)
+    rel = lambda a, b: ((a.cpu() - b).norm() / b.norm()).item()
+    assert rel(lg, lc) < 0.08, rel(lg, lc)  # e4m3 rounding flips (activation quant, QAT) decorrelate a few percent
     for t in toks[290:]:
         lc = cpu.step([(0, [t])])
         lg = gpu.step([(0, [t])])
-    assert (lg.cpu() - lc).abs().max().item() < 0.15 * scale + 0.05
+    assert rel(lg, lc) < 0.08, rel(lg, lc)
     n4 = 300 // 4
     a, b = gpu.pool.c4[0][:n4 + 64].float().cpu(), cpu.pool.c4[0][:n4 + 64].float()
     assert ((a - b).abs() < 0.1).float().mean() > 0.98
