@@ -119,6 +119,9 @@ class DSV4Model:
         for g in range(self.g_local):
             O.gemm_bf16(o[:, g], wa[g * cfg.o_lora_rank:(g + 1) * cfg.o_lora_rank],
                         out=o2[:, g * cfg.o_lora_rank:(g + 1) * cfg.o_lora_rank])
+        if getattr(self.comm, "fused", False):
+            oq = O.fp8_quant(o2)
+            return self.comm.gemm_fp8_allreduce(oq[0], oq[1], w[p + "wo_b.weight"], w[p + "wo_b.scale"])
         out = self._fp8_linear(o2, p + "wo_b")
         return self.comm.all_reduce(out, "attn")
 
@@ -127,12 +130,24 @@ class DSV4Model:
         idx, wt = O.moe_gate(y, w[p + "gate.weight"], w.get(p + "gate.bias"), cfg.num_experts_per_tok,
                              cfg.routed_scaling_factor, cfg.scoring_func, w.get(p + "gate.tid2eid"), fb.input_ids,
                              fb.num_valid)
-        routed = O.moe_experts(y, idx, wt, w[p + "w13"], w[p + "s13"], w[p + "w2"], w[p + "s2"], cfg.swiglu_limit,
-                               self.expert_base)
         yq = O.fp8_quant(y)
         gu = O.gemm_fp8(yq[0], yq[1], w[p + "sh_gate_up.weight"], w[p + "sh_gate_up.scale"])
         a = O.silu_mul_clamp(gu, cfg.swiglu_limit)
         shared = self._fp8_linear(a, p + "sh_down")
+        if y.is_cuda:
+            # routed rows stay per route; the combine kernel sums them with the shared expert (and, with fused
+            # communication, all-reduces the result in the same kernel)
+            from ..ops import cuda as C
+
+            rows, plan, mt = C.moe_routed(y, idx, wt, w[p + "w13"], w[p + "s13"], w[p + "w2"], w[p + "s2"],
+                                          cfg.swiglu_limit, self.expert_base)
+            t, k, h = y.shape[0], idx.shape[1], y.shape[1]
+            if getattr(self.comm, "fused", False):
+                return self.comm.moe_finalize_allreduce(rows, plan, mt, shared, fb.num_valid, t, k, h)
+            out = C.moe_finalize(rows, plan, mt, shared, fb.num_valid, t, k, h)
+            return self.comm.all_reduce(out, "moe")
+        routed = O.moe_experts(y, idx, wt, w[p + "w13"], w[p + "s13"], w[p + "w2"], w[p + "s2"], cfg.swiglu_limit,
+                               self.expert_base)
         out = O.add_cast(routed, shared, fb.num_valid)
         return self.comm.all_reduce(out, "moe")
 

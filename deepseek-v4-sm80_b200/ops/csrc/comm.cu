@@ -1,0 +1,73 @@
+// Stand-alone in-kernel all-reduce over NVLink peer memory (bf16 [rows, cols], sum), using the protocol in comm.cuh.
+// It is the unfused form of the two fused call sites (projection GEMM epilogue in gemm_tcgen05.cu, MoE combine in
+// moe.cu), used for the embedding-free generic reductions, for tests and as the microbenchmark baseline against
+// NCCL.  Each CTA owns rows b, b + grid, ...: copy to the symmetric buffer, publish, wait, reduce in rank order.
+#include "comm.cuh"
+
+namespace {
+
+__global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                                        int rows, int cols, const CommCtx comm) {
+  __shared__ int ok;
+  const uint32_t epoch = comm_epoch(comm);
+  const int parity = epoch & 1;
+  __nv_bfloat16* mine = comm_data(comm, comm.rank, parity);
+  const int c8 = cols / 8;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x)
+    for (int i = threadIdx.x; i < c8; i += blockDim.x)
+      reinterpret_cast<uint4*>(mine + (size_t)r * cols)[i] = reinterpret_cast<const uint4*>(x + (size_t)r * cols)[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    comm_publish(comm, blockIdx.x, epoch);
+    ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
+  }
+  __syncthreads();
+  if (ok) {
+    for (int r = blockIdx.x; r < rows; r += gridDim.x)
+      for (int i = threadIdx.x; i < c8; i += blockDim.x)
+        reinterpret_cast<uint4*>(out + (size_t)r * cols)[i] = comm_reduce16(comm, parity, (size_t)r * cols + i * 8);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) comm_finish(comm, gridDim.x);
+}
+
+// A wait that nothing satisfies: used by the failure-detection test to show that a missing peer ends in an error
+// status (DSV4_ERR_PEER_TIMEOUT) within `limit_ns`, with the context still usable.  It polls a LOCAL flag.
+__global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, unsigned long long limit_ns, int* result) {
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    if (ld_acquire_sys(flag) == want) {
+      *result = 1;
+      return;
+    }
+    if (globaltimer_ns() - t0 > limit_ns) {
+      dsv4_set_error(DSV4_ERR_PEER_TIMEOUT, -1, 0);
+      *result = 0;
+      return;
+    }
+  }
+}
+
+}  // namespace
+
+DSV4_API int dsv4_comm_layout(long long* flags_bytes, int* channels, int* slots, int* max_ranks) {
+  *flags_bytes = (long long)comm_flags_bytes();
+  *channels = kCommChannels;
+  *slots = kCommSlots;
+  *max_ranks = kMaxRanks;
+  return 0;
+}
+
+DSV4_API int dsv4_allreduce(const void* x, void* out, int rows, int cols, const CommCtx* comm, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (cols % 8) return 500;
+  if ((long long)rows * cols * 2 > comm->data_bytes) return 501;
+  int grid = rows < 1024 ? rows : 1024;
+  allreduce_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, cols, *comm);
+  return (int)cudaGetLastError();
+}
+
+DSV4_API int dsv4_wait_flag(const void* flag, unsigned want, long long limit_ns, int* result, cudaStream_t st) {
+  wait_flag_kernel<<<1, 1, 0, st>>>((const uint32_t*)flag, want, (unsigned long long)limit_ns, result);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,105 @@
+// In-kernel collectives over NVLink peer memory (plain P2P loads/stores through NVSwitch).
+//
+// Every rank owns one symmetric allocation with the same layout; `CommCtx` carries all ranks' base pointers:
+//   flags  [channel][writer rank][slot]  uint32, written remotely by `writer rank`, polled locally
+//   data   [channel][parity][row][col]   bf16 partial results of this rank, read remotely by every peer
+// A *channel* is one call site (attention output projection, MoE combine, generic).  A call uses the channel's
+// device-resident epoch E: partials go to data[E & 1], flags carry E.  Each CTA owns a set of tiles: it writes its
+// partial tile locally, publishes flag[E] to every peer, waits for the same tile's flag from every peer and reduces
+// the 'world' copies in rank order (so all ranks produce bit-identical sums).  A CTA only ever waits on other GPUs,
+// never on a CTA of its own grid, so no co-residency of the grid is required.  Reuse of data[E & 1] two calls later is
+// safe because a rank can only finish call E+1 after every peer has entered call E+1, i.e. finished call E.
+// The last CTA of the grid to finish bumps the epoch, which keeps the protocol valid under CUDA-graph replay.
+// All waits are bounded: on expiry the kernel records DSV4_ERR_PEER_TIMEOUT and returns without reducing.
+#pragma once
+#include "common.cuh"
+
+constexpr int kMaxRanks = 8;
+constexpr int kCommChannels = 3;
+constexpr int kCommSlots = 8192;
+
+struct CommCtx {
+  uint8_t* peer[kMaxRanks];   // symmetric base of every rank (peer[rank] is local)
+  int rank, world;
+  int channel;
+  long long data_bytes;       // bytes of one parity buffer of one channel
+  int* epoch;                 // local [kCommChannels] device ints
+  int* done;                  // local [kCommChannels] device ints
+};
+
+__host__ __device__ inline size_t comm_flags_bytes() { return (size_t)kCommChannels * kMaxRanks * kCommSlots * 4; }
+__device__ __forceinline__ uint32_t* comm_flag(const CommCtx& c, int on_rank, int writer, int slot) {
+  return reinterpret_cast<uint32_t*>(c.peer[on_rank]) + ((size_t)c.channel * kMaxRanks + writer) * kCommSlots + slot;
+}
+__device__ __forceinline__ __nv_bfloat16* comm_data(const CommCtx& c, int on_rank, int parity) {
+  return reinterpret_cast<__nv_bfloat16*>(c.peer[on_rank] + comm_flags_bytes() +
+                                          ((size_t)c.channel * 2 + parity) * (size_t)c.data_bytes);
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Called by ONE thread after the CTA's partial tile is written and the writers have synchronised.
+__device__ __forceinline__ void comm_publish(const CommCtx& c, int slot, uint32_t epoch) {
+  __threadfence_system();
+  for (int p = 0; p < c.world; ++p)
+    if (p != c.rank) st_release_sys(comm_flag(c, p, c.rank, slot), epoch);
+}
+// Called by ONE thread; returns false when a peer's flag did not arrive in time.
+__device__ __forceinline__ bool comm_wait(const CommCtx& c, int slot, uint32_t epoch) {
+  for (int p = 0; p < c.world; ++p) {
+    if (p == c.rank) continue;
+    const uint32_t* f = comm_flag(c, c.rank, p, slot);
+    if ((int)(ld_acquire_sys(f) - epoch) >= 0) continue;
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+      if ((int)(ld_acquire_sys(f) - epoch) >= 0) break;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        dsv4_set_error(DSV4_ERR_PEER_TIMEOUT, p, slot);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+// Sum `world` bf16x8 vectors (one per rank, same offset) in rank order, fp32 accumulate, round once.
+__device__ __forceinline__ uint4 comm_reduce16(const CommCtx& c, int parity, size_t elem_offset) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int p = 0; p < c.world; ++p) {
+    const uint4 u = ld_peer16(comm_data(c, p, parity) + elem_offset);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      acc[2 * k] += f.x;
+      acc[2 * k + 1] += f.y;
+    }
+  }
+  uint4 o;
+  __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) ho[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+  return o;
+}
+// Last CTA of the grid advances the channel epoch (call once per CTA, by one thread, at the very end).
+__device__ __forceinline__ void comm_finish(const CommCtx& c, int total_ctas) {
+  __threadfence();
+  if (atomicAdd(&c.done[c.channel], 1) == total_ctas - 1) {
+    c.done[c.channel] = 0;
+    __threadfence();
+    atomicAdd(&c.epoch[c.channel], 1);
+  }
+}
+__device__ __forceinline__ uint32_t comm_epoch(const CommCtx& c) {
+  return (uint32_t)(*reinterpret_cast<volatile int*>(&c.epoch[c.channel])) + 1u;
+}

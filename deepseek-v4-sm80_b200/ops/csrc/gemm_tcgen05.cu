@@ -14,7 +14,7 @@
 //     as  acc += sa[row,kb] * sw[nb,kb] * partial  -- the exact arithmetic of the
 //     reference's "fake-quant activations x dequantised weights" path
 //     (python/minisgl/models/deepseek_v4.py:145-149, :483) up to summation order.
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace {
 
@@ -66,7 +66,8 @@ __device__ __forceinline__ void store_row_chunk(float* dst, const float* v, int 
 template <int BN, bool FP8, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ out,
-               int M, int N, int K, int ldo, const float* __restrict__ sa, const float* __restrict__ sb, int accumulate_out) {
+               int M, int N, int K, int ldo, const float* __restrict__ sa, const float* __restrict__ sb, int accumulate_out,
+               const CommCtx comm) {
   using Cfg = GemmCfg<BN>;
   constexpr int S = Cfg::kStages;
   constexpr int BK = FP8 ? 128 : 64;  // elements per k-tile (= 128 bytes)
@@ -161,6 +162,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int row = q * 32 + lane;
     const int grow = m0 + row;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    // fused all-reduce: the partial tile goes to this rank's symmetric buffer, the reduced tile to `out`
+    const bool fused = comm.world > 1;
+    uint32_t epoch = 0;
+    OutT* part = out;
+    int ld_part = ldo;
+    if (fused) {
+      epoch = comm_epoch(comm);
+      part = reinterpret_cast<OutT*>(comm_data(comm, comm.rank, epoch & 1));
+      ld_part = N;
+    }
     if (!FP8) {
       bool ok = mbar_wait(&tfull[0], 0, abort_flag, 4);
       tc_fence_after();
@@ -175,7 +186,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           const int col = n0 + c * 32;
           if (grow < M && col < N) {
-            OutT* dst = out + (size_t)grow * ldo + col;
+            OutT* dst = part + (size_t)grow * ld_part + col;
             if (accumulate_out) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
@@ -216,7 +227,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int c = 0; c < BN / 32; ++c) {
           const int col = n0 + c * 32;
           if (col < N) {
-            OutT* dst = out + (size_t)grow * ldo + col;
+            OutT* dst = part + (size_t)grow * ld_part + col;
             if (accumulate_out) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
@@ -227,6 +238,29 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
     }
+    if (fused) {
+      if constexpr (sizeof(OutT) == 2) {
+        __shared__ int comm_ok;
+        const int slot = blockIdx.y * gridDim.x + blockIdx.x;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          comm_publish(comm, slot, epoch);
+          comm_ok = comm_wait(comm, slot, epoch) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (comm_ok && grow < M) {
+#pragma unroll 1
+          for (int c8 = 0; c8 < BN; c8 += 8) {
+            const int col = n0 + c8;
+            if (col < N)
+              *reinterpret_cast<uint4*>(out + (size_t)grow * ldo + col) =
+                  comm_reduce16(comm, epoch & 1, (size_t)grow * N + col);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) comm_finish(comm, gridDim.x * gridDim.y);
+      }
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -235,7 +269,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 template <int BN, bool FP8, typename OutT>
 int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, int ldx, int ldw, int ldo, const float* sa,
-                const float* sb, int accumulate_out, cudaStream_t stream) {
+                const float* sb, int accumulate_out, cudaStream_t stream, const CommCtx& comm) {
   using Cfg = GemmCfg<BN>;
   constexpr int BK = FP8 ? 128 : 64;
   const int esz = FP8 ? 1 : 2;
@@ -250,13 +284,14 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
     attr_set = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM);
-  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, M, N, K, ldo, sa, sb, accumulate_out);
+  if (comm.world > 1 && (long long)grid.x * grid.y > kCommSlots) return 104;
+  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, M, N, K, ldo, sa, sb, accumulate_out, comm);
   return (int)cudaGetLastError();
 }
 
 template <bool FP8, typename OutT>
 int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, int ldx, int ldw, int ldo, const float* sa,
-                const float* sb, int acc, int bn, cudaStream_t st) {
+                const float* sb, int acc, int bn, cudaStream_t st, const CommCtx& comm = CommCtx{}) {
   if (bn == 0) {
     const int mt = (M + kBM - 1) / kBM;
     if (mt * ((N + 127) / 128) >= 148 && !FP8)
@@ -269,11 +304,11 @@ int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, in
   if (FP8 && bn > 64) bn = 64;
   switch (bn) {
     case 128:
-      if constexpr (!FP8) return launch_gemm<128, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st);
+      if constexpr (!FP8) return launch_gemm<128, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, comm);
     case 64:
-      return launch_gemm<64, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st);
+      return launch_gemm<64, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, comm);
     default:
-      return launch_gemm<32, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st);
+      return launch_gemm<32, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, comm);
   }
 }
 
@@ -300,4 +335,22 @@ DSV4_API int dsv4_gemm_fp8(const void* x, const void* w, void* out, const float*
     return dispatch_bn<true, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn, stream);
   return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn,
                                           stream);
+}
+
+// Fused projection + all-reduce: every rank multiplies its K-shard, the epilogue publishes the partial tile to the
+// rank's symmetric buffer and reduces the peers' tiles over NVLink (see comm.cuh).  out is bf16 [M,N], dense.
+DSV4_API int dsv4_gemm_fp8_allreduce(const void* x, const void* w, void* out, const float* sa, const float* sb, int M,
+                                     int N, int K, int ldx, int ldw, const CommCtx* comm, int bn, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 128) || (ldx % 16) || (ldw % 16) || (N % 8)) return 112;
+  if ((long long)M * N * 2 > comm->data_bytes) return 113;
+  return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, N, sa, sb, 0, bn, stream, *comm);
+}
+DSV4_API int dsv4_gemm_bf16_allreduce(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw,
+                                      const CommCtx* comm, int bn, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 8) || (ldx % 8) || (ldw % 8) || (N % 8)) return 114;
+  if ((long long)M * N * 2 > comm->data_bytes) return 115;
+  return dispatch_bn<false, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, N, nullptr, nullptr, 0, bn,
+                                           stream, *comm);
 }

@@ -13,7 +13,7 @@
 // Numerics match the reference's Marlin path (python/minisgl/kernel/marlin_wna16.py:288-356): bf16 activations,
 // exact FP4 dequantisation, fp32 accumulation, GEMM1 output rounded to bf16 before the fp32 SwiGLU, GEMM2
 // output rounded to bf16 and multiplied by the bf16 route weight, routes summed afterwards.
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace {
 
@@ -465,6 +465,63 @@ __global__ void moe_finalize_kernel(const __nv_bfloat16* __restrict__ yr, const 
   }
 }
 
+// Fused combine: the per-token sum of the local routes (+ the shared expert) is this rank's partial of the layer
+// output; it goes to the symmetric buffer and is reduced across ranks in the same kernel (protocol in comm.cuh).
+__global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat16* __restrict__ yr,
+                                                              const int* __restrict__ route_pos,
+                                                              const __nv_bfloat16* __restrict__ shared,
+                                                              __nv_bfloat16* __restrict__ out,
+                                                              const int* __restrict__ num_valid, int topk, int h,
+                                                              int t_rows, const CommCtx comm) {
+  __shared__ int ok;
+  const uint32_t epoch = comm_epoch(comm);
+  const int parity = epoch & 1;
+  __nv_bfloat16* mine = comm_data(comm, comm.rank, parity);
+  const int nv = num_valid ? *num_valid : t_rows;
+  for (int t = blockIdx.x; t < t_rows; t += gridDim.x) {
+    const bool valid = t < nv;
+    for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      uint4 o = make_uint4(0, 0, 0, 0);
+      if (valid) {
+        for (int k = 0; k < topk; ++k) {
+          if (route_pos[t * topk + k] < 0) continue;
+          const uint4 u = *reinterpret_cast<const uint4*>(yr + ((size_t)t * topk + k) * h + i);
+          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(p[j]);
+            acc[2 * j] += f.x, acc[2 * j + 1] += f.y;
+          }
+        }
+        const uint4 su = *reinterpret_cast<const uint4*>(shared + (size_t)t * h + i);
+        const __nv_bfloat162* sp = reinterpret_cast<const __nv_bfloat162*>(&su);
+        __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 r2 = __bfloat1622float2(__floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]));
+          const float2 s2 = __bfloat1622float2(sp[j]);
+          po[j] = __floats2bfloat162_rn(r2.x + s2.x, r2.y + s2.y);
+        }
+      }
+      *reinterpret_cast<uint4*>(mine + (size_t)t * h + i) = o;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    comm_publish(comm, blockIdx.x, epoch);
+    ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
+  }
+  __syncthreads();
+  if (ok) {
+    for (int t = blockIdx.x; t < t_rows; t += gridDim.x)
+      for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8)
+        *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = comm_reduce16(comm, parity, (size_t)t * h + i);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) comm_finish(comm, gridDim.x);
+}
+
 template <int MODE, int NT>
 int launch_moe_gemm(const void* w, const uint8_t* scales, const void* x, int x_rows, const PlanHeader* hdr,
                     const int* tiles, const int* sorted_route, const float* sorted_w, void* out, int e_local, int K,
@@ -547,5 +604,17 @@ DSV4_API int dsv4_moe_finalize(const void* yr, const int* plan, int routes, int 
   const int* route_pos = plan + 4 + 3 * max_tiles + routes;
   moe_finalize_kernel<<<t, 256, 0, st>>>((const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
                                          (__nv_bfloat16*)out, num_valid, topk, h);
+  return (int)cudaGetLastError();
+}
+
+DSV4_API int dsv4_moe_finalize_allreduce(const void* yr, const int* plan, int routes, int max_tiles, const void* shared,
+                                         void* out, const int* num_valid, int t, int topk, int h, const CommCtx* comm,
+                                         cudaStream_t st) {
+  if (t <= 0) return 0;
+  if (h % 8 || (long long)t * h * 2 > comm->data_bytes) return 230;
+  const int* route_pos = plan + 4 + 3 * max_tiles + routes;
+  const int grid = t < 1024 ? t : 1024;
+  moe_finalize_ar_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
+                                               (__nv_bfloat16*)out, num_valid, topk, h, t, *comm);
   return (int)cudaGetLastError();
 }

@@ -67,9 +67,22 @@ def check(code: int, what: str) -> None:
         raise NativeError(f"{what} failed with code {code}")
 
 
+_LAUNCHES = [0]
+
+
+def launch_count() -> int:
+    """Kernel launches issued through this module so far (graph replays add their captured launches)."""
+    return _LAUNCHES[0]
+
+
+def add_launches(n: int) -> None:
+    _LAUNCHES[0] += n
+
+
 def call(name: str, *args) -> None:
     """Calls ``dsv4_<name>(*args, stream)`` and raises on a non-zero return code."""
     fn = getattr(cuda_lib(), "dsv4_" + name)
+    _LAUNCHES[0] += 1
     code = fn(*args, stream())
     if code != 0:
         raise NativeError(f"dsv4_{name} failed with code {code}")

@@ -45,9 +45,9 @@ class TorchDistComm(Comm):
         """[B, V/size] per rank -> [B, V] (rank-major along the last dim)."""
         self.counters["all_gather"] += 1
         b, vl = x.shape
-        out = torch.empty(self.size, b, vl, dtype=x.dtype, device=x.device)
+        out = torch.empty(self.size * b, vl, dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
-        full = out.permute(1, 0, 2).reshape(b, self.size * vl)
+        full = out.view(self.size, b, vl).permute(1, 0, 2).reshape(b, self.size * vl)
         return full[:, : self.vocab_size] if self.vocab_size else full
 
     def barrier(self) -> None:

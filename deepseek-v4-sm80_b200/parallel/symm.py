@@ -1,0 +1,119 @@
+"""Communicator whose collectives run *inside* this library's kernels over NVLink peer memory.
+
+One symmetric allocation per rank (``torch.distributed._symmetric_memory``: CUDA VMM + handle exchange, every peer's
+base pointer visible to every rank) holds flag words and double-buffered partial-result areas for three channels:
+
+  channel 0  attention output projection: ``wo_b`` FP8 GEMM whose epilogue all-reduces (csrc/gemm_tcgen05.cu)
+  channel 1  MoE combine: per-token route sum + shared expert, all-reduced in the same kernel (csrc/moe.cu)
+  channel 2  generic stand-alone all-reduce (csrc/comm.cu)
+
+The protocol (epochs, parity buffers, bounded waits) is documented in csrc/comm.cuh.  The logits all-gather, which
+runs once per forward, stays on NCCL.  This replaces the reference's PyNCCL object
+(python/minisgl/kernel/csrc/src/pynccl.cu:73-176: copy-in, ncclAllReduce on a registered window, copy-out).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.deepseek_v4 import Comm
+from ..ops import native as nv
+from ..ops.native import I
+from .info import DistributedInfo
+
+MAX_RANKS = 8
+
+
+class CommCtx(ctypes.Structure):
+    _fields_ = [("peer", ctypes.c_void_p * MAX_RANKS), ("rank", ctypes.c_int), ("world", ctypes.c_int),
+                ("channel", ctypes.c_int), ("data_bytes", ctypes.c_longlong), ("epoch", ctypes.c_void_p),
+                ("done", ctypes.c_void_p)]
+
+
+class SymmComm(Comm):
+    fused = True
+    CH_ATTN, CH_MOE, CH_GENERIC = 0, 1, 2
+
+    def __init__(self, info: DistributedInfo, device, vocab_size: Optional[int] = None, max_rows: int = 8192,
+                 hidden: int = 4096, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if info.size > MAX_RANKS:
+            raise ValueError(f"at most {MAX_RANKS} ranks are supported")
+        self.rank, self.size, self.vocab_size = info.rank, info.size, vocab_size
+        self.device = torch.device(device)
+        self.group = group or dist.group.WORLD
+        lib = nv.cuda_lib()
+        fb, ch, sl, mr = ctypes.c_longlong(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        nv.check(lib.dsv4_comm_layout(ctypes.byref(fb), ctypes.byref(ch), ctypes.byref(sl), ctypes.byref(mr)),
+                 "dsv4_comm_layout")
+        assert mr.value == MAX_RANKS
+        self.flags_bytes, self.channels, self.slots = fb.value, ch.value, sl.value
+        self.data_bytes = (max_rows * hidden * 2 + 255) // 256 * 256
+        total = self.flags_bytes + self.channels * 2 * self.data_bytes
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.buf.zero_()
+        self.state = torch.zeros(2 * self.channels, dtype=torch.int32, device=self.device)  # epochs, done counters
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        ptrs = list(self.handle.buffer_ptrs)
+        self.has_multicast = bool(getattr(self.handle, "multicast_ptr", 0))
+        self.ctx = []
+        for c in range(self.channels):
+            x = CommCtx()
+            for r in range(self.size):
+                x.peer[r] = ptrs[r]
+            x.rank, x.world, x.channel, x.data_bytes = self.rank, self.size, c, self.data_bytes
+            x.epoch = self.state.data_ptr()
+            x.done = self.state.data_ptr() + 4 * self.channels
+            self.ctx.append(x)
+        self.counters = {"all_reduce": 0, "gemm_allreduce": 0, "moe_allreduce": 0, "all_gather": 0}
+
+    # ------------------------------------------------------------------ collectives
+    def all_reduce(self, x: torch.Tensor, tag: str = "") -> torch.Tensor:
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 2
+        self.counters["all_reduce"] += 1
+        out = torch.empty_like(x)
+        nv.call("allreduce", nv.ptr(x), nv.ptr(out), I(x.shape[0]), I(x.shape[1]),
+                ctypes.byref(self.ctx[self.CH_GENERIC]))
+        return out
+
+    def gemm_fp8_allreduce(self, xq, sx, w, ws, bn: int = 0) -> torch.Tensor:
+        """out = all_reduce(xq @ w^T) with the reduction done by the GEMM's epilogue."""
+        m, k = xq.shape
+        n = w.shape[0]
+        self.counters["gemm_allreduce"] += 1
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=xq.device)
+        nv.call("gemm_fp8_allreduce", nv.ptr(xq), nv.ptr(w), nv.ptr(out), nv.ptr(sx), nv.ptr(ws), I(m), I(n), I(k),
+                I(xq.stride(0)), I(w.stride(0)), ctypes.byref(self.ctx[self.CH_ATTN]), I(bn))
+        return out
+
+    def gemm_bf16_allreduce(self, x, w, bn: int = 0, channel: Optional[int] = None) -> torch.Tensor:
+        m, k = x.shape
+        n = w.shape[0]
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+        nv.call("gemm_bf16_allreduce", nv.ptr(x), nv.ptr(w), nv.ptr(out), I(m), I(n), I(k), I(x.stride(0)),
+                I(w.stride(0)), ctypes.byref(self.ctx[self.CH_ATTN if channel is None else channel]), I(bn))
+        return out
+
+    def moe_finalize_allreduce(self, rows, plan, max_tiles, shared, num_valid, t, topk, h) -> torch.Tensor:
+        self.counters["moe_allreduce"] += 1
+        out = torch.empty(t, h, dtype=rows.dtype, device=rows.device)
+        nv.call("moe_finalize_allreduce", nv.ptr(rows), nv.ptr(plan), I(t * topk), I(max_tiles), nv.ptr(shared),
+                nv.ptr(out), nv.ptr(num_valid), I(t), I(topk), I(h), ctypes.byref(self.ctx[self.CH_MOE]))
+        return out
+
+    def all_gather_last(self, x: torch.Tensor) -> torch.Tensor:
+        self.counters["all_gather"] += 1
+        b, vl = x.shape
+        out = torch.empty(self.size * b, vl, dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        full = out.view(self.size, b, vl).permute(1, 0, 2).reshape(b, self.size * vl)
+        return full[:, : self.vocab_size] if self.vocab_size else full
+
+    def barrier(self) -> None:
+        dist.barrier(group=self.group)

@@ -1,0 +1,109 @@
+"""Worker for the multi-rank tests (one process per rank, launched by torch.distributed.run).
+
+cpu:  tiny model, gloo, TorchDistComm: rank logits must match the single-rank model.
+cuda: flagship-shaped small model over the fused NVLink communicator, plus the collectives themselves against NCCL.
+Writes 'OK' lines; any assertion failure exits non-zero.
+"""
+import argparse
+import dataclasses
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from helpers import MiniRunner  # noqa: E402
+from minisgl.models import synth  # noqa: E402
+from minisgl.models.config import ModelConfig  # noqa: E402
+from minisgl.parallel.comm import TorchDistComm, init_distributed  # noqa: E402
+from minisgl.parallel.info import DistributedInfo  # noqa: E402
+
+
+def rel(a, b):
+    return ((a.float().cpu() - b.float().cpu()).norm() / b.float().cpu().norm()).item()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--device", default="cpu")
+    ap.add_argument("--moe-mode", default="ep")
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    info = DistributedInfo(rank, world)
+    g = torch.Generator().manual_seed(0)
+    if args.device == "cpu":
+        cfg = ModelConfig.tiny()
+        dev = torch.device("cpu")
+        _, comm = init_distributed(info, dev, vocab_size=cfg.vocab_size)
+        assert isinstance(comm, TorchDistComm)
+        toks = torch.randint(0, cfg.vocab_size, (90,), generator=g).tolist()
+        tp = MiniRunner(cfg, "cpu", comm=comm, moe_mode=args.moe_mode, rank=rank, size=world, seed=1)
+        l_tp = tp.step([(0, toks)])
+        single = MiniRunner(cfg, "cpu", seed=1)
+        l_1 = single.step([(0, toks)])
+        assert rel(l_tp, l_1) < 0.08, rel(l_tp, l_1)  # bf16 partial sums + e4m3 rounding flips
+        assert torch.equal(l_tp.argmax(-1), l_1.argmax(-1))
+        print(f"OK cpu rank {rank} rel {rel(l_tp, l_1):.4f}", flush=True)
+    else:
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        cfg = dataclasses.replace(ModelConfig.flash().with_layers(4), n_routed_experts=16, vocab_size=4096,
+                                  n_hash_layers=1)
+        _, comm = init_distributed(info, dev, vocab_size=cfg.vocab_size, max_rows=1024, hidden=cfg.hidden_size)
+        from minisgl.ops import native, quant
+        from minisgl.parallel.symm import SymmComm
+
+        assert isinstance(comm, SymmComm), type(comm)
+        # 1) stand-alone all-reduce vs NCCL, several sizes, repeated (epochs / parity buffers)
+        for rows in (1, 8, 128, 1000):
+            for it in range(3):
+                x = (torch.randn(rows, 4096, device=dev, generator=None) * (rank + 1)).to(torch.bfloat16)
+                ref = x.float().clone()
+                dist.all_reduce(ref)
+                out = comm.all_reduce(x)
+                torch.cuda.synchronize()
+                assert rel(out, ref) < 1e-2, (rows, it, rel(out, ref))
+        # 2) fused FP8 GEMM + all-reduce vs separate GEMM + NCCL
+        from minisgl.ops import api as O
+
+        for m in (1, 8, 128, 300):
+            xx = torch.randn(m, 1024, device=dev).to(torch.bfloat16)
+            ww = torch.randn(4096, 1024, device=dev) * 0.02
+            wq, wsc = quant.fp8_weight_quant(ww)
+            ws = quant.e8m0_decode(wsc)
+            xq, sx = O.fp8_quant(xx)
+            sep = O.gemm_fp8(xq, sx, wq, ws, out_dtype=torch.float32)
+            dist.all_reduce(sep)
+            fused = comm.gemm_fp8_allreduce(xq, sx, wq, ws)
+            torch.cuda.synchronize()
+            assert rel(fused, sep) < 1e-2, (m, rel(fused, sep))
+        # every rank must hold bit-identical results
+        chk = fused.float().sum().reshape(1).clone()
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert float(lo) == float(hi)
+        # 3) whole model: tensor/expert parallel vs single rank
+        toks = torch.randint(0, cfg.vocab_size, (200,), generator=g).tolist()
+        kw = dict(page_size=256, num_pages=8, num_slots=2, max_len=1024)
+        tp = MiniRunner(cfg, dev, comm=comm, moe_mode=args.moe_mode, rank=rank, size=world, seed=2, **kw)
+        l_tp = tp.step([(0, toks)])
+        for t in toks[:3]:
+            l_tp = tp.step([(0, [t])])
+        single = MiniRunner(cfg, dev, seed=2, **kw)
+        l_1 = single.step([(0, toks)])
+        for t in toks[:3]:
+            l_1 = single.step([(0, [t])])
+        torch.cuda.synchronize()
+        native.assert_device_ok()
+        assert rel(l_tp, l_1) < 0.08, rel(l_tp, l_1)
+        print(f"OK cuda rank {rank} rel {rel(l_tp, l_1):.4f} counters {comm.counters}", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
