@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--output-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0, help="0 = as many of the 43 layers as fit in memory")
     ap.add_argument("--experts", type=int, default=256)
     ap.add_argument("--moe-mode", default="ep", choices=["ep", "tp"])
@@ -163,7 +164,13 @@ def main():
     cfg = ModelConfig.flash().with_layers(layers)
     if args.experts != 256:
         cfg = dataclasses.replace(cfg, n_routed_experts=args.experts)
-    n_out = args.warmup + args.steps + 1
+    # every sequence is asked for 1 024 output tokens, like the reference's wave.  Under mixed load the scheduler
+    # runs 4 decode forwards per 2 048-token prefill forward, so the first sequences are a few hundred tokens into
+    # their output when the last prompt finishes; the timed steps start there, with all sequences decoding.
+    n_out = args.output_len
+    mixed_fwd = (args.batch * args.prompt_len + 2047) // 2048
+    if 4 * mixed_fwd + args.warmup + args.steps + 2 > n_out:
+        raise SystemExit(f"--output-len {n_out} is too short for {args.warmup}+{args.steps} steps after the prefill wave")
     ctx = args.prompt_len + n_out + 256
     llm = LLM(model_config=cfg, tp_info=DistributedInfo(rank, world), use_dummy_weight=True, recipe="default_m128",
               max_running_req=args.batch, context_length=max(ctx, 4096), moe_mode=args.moe_mode,
@@ -229,13 +236,9 @@ def main():
     dev_s, span_s, wall = [float(x) for x in stats]
     tokens = args.batch * args.steps
     launches = native.launch_count() - launches0
-    # drain the remaining token so that every request retires cleanly
-    try:
-        while True:
-            last = llm.overlap_loop(last)
-    except Exception:
-        pass
     outs = list(llm._results.values())
+    for uid in range(args.batch):  # the wave is measured; retire what is still running
+        llm._abort(uid)
     ttft = sorted(o.t_first - t_submit for o in outs if o.t_first)
     tpot = sorted((o.t_tokens[-1] - o.t_tokens[0]) / (len(o.t_tokens) - 1) for o in outs if len(o.t_tokens) > 1)
     if rank == 0:

@@ -1,27 +1,49 @@
 // Sparse MQA attention over the paged caches: per token, all local heads attend
 //   {sink} U {selected C4 rows | all C128 rows | nothing} U {sliding window rows},
 // keys and values being the same 512-d latent row (K = V), softmax scale 512^-1/2.
-// One CTA per token: every gathered row is fetched once (cp.async, double buffered, 32 rows per tile) and
-// shared by all local heads.  The kernel walks the request's page-table row itself, so no index surface is
-// materialised: compressed entry j of ratio r lives at row comp_row(page_table[slot, j*r + r-1]); window position
-// p lives at swa_map[loc / ps] * ps + loc % ps.  (m, l) start at (sink, 1), which adds exp(sink - m) to the
-// denominator only -- the reference's two-source kernel semantics
+//
+// One CTA per token.  Every gathered row is fetched once (cp.async into 128B-swizzled shared memory, double
+// buffered) and shared by all local heads; both contractions run on the tensor cores with warp-level
+// mma.sync.m16n8k16 (bf16 in, fp32 accumulate): with 8..64 heads per token the M extent is 16..64, far below the
+// 128-row tiles tcgen05 wants, and the kernel is bound by the row gather, so the warp-level shape is the better fit.
+//   S phase : warp (mt, g) computes the 16 x 8 score tile of head tile mt and key group g (32 k-steps)
+//   softmax : online (m, l) per head, probabilities to shared memory as bf16
+//   PV phase: warp (mt, g) owns head tile mt and a 512/G slice of the output dims in registers
+// The kernel walks the request's page-table row itself, so no index surface is materialised: compressed entry j of
+// ratio r lives at row comp_row(page_table[slot, j*r + r-1]); window position p lives at
+// swa_map[loc / ps] * ps + loc % ps.  (m, l) start at (sink, 1), which adds exp(sink - m) to the denominator only --
+// the reference's two-source kernel semantics
 // (python/minisgl/kernel/csrc/jit/dsv4_sparse_attention_two_source_bf16.cu:77-168).
 #include "common.cuh"
 
 namespace {
 
 constexpr int D = 512;
-constexpr int KT = 32;  // keys per tile
-constexpr int NTHR = 256;
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* g) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(g) : "memory");
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* g, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(g), "r"(sz) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 struct AttnArgs {
@@ -46,20 +68,42 @@ struct AttnArgs {
   const int* num_valid;
 };
 
+// row of 512 bf16 = 64 chunks of 16 B; chunk c of row r is stored at chunk (c ^ (r & 7))
+__device__ __forceinline__ int swz_row(int r, int c) { return (c & ~7) | ((c ^ r) & 7); }
+
 template <int HL>
-__global__ void __launch_bounds__(NTHR) sparse_attn_kernel(AttnArgs a) {
-  extern __shared__ __align__(16) uint8_t attn_smem[];
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(attn_smem);            // [HL][D]
-  __nv_bfloat16* kvs = qs + HL * D;                                           // [2][KT][D]
-  float* ps_ = reinterpret_cast<float*>(kvs + 2 * KT * D);                    // [HL][KT] probabilities
-  float* alpha = ps_ + HL * KT;                                               // [HL]
-  float* ms = alpha + HL;                                                     // [HL]
-  float* ls = ms + HL;                                                        // [HL]
-  int* valid = reinterpret_cast<int*>(ls + HL);                               // [2][KT]
+struct AttnCfg {
+  static constexpr int HP = HL < 16 ? 16 : HL;          // padded head rows
+  static constexpr int MT = HP / 16;                     // 16-row head tiles
+  static constexpr int NW = MT >= 4 ? 16 : 8;            // warps
+  static constexpr int G = NW / MT;                      // warps per head tile
+  static constexpr int KT = 8 * G;                       // keys per tile: one 16x8 score tile per warp
+  static constexpr int DW = D / G;                       // output dims per warp
+  static constexpr int NT = DW / 8;                      // output n-tiles per warp
+  static constexpr int TPR = NW * 32 / HP;               // softmax threads per head row
+  static constexpr int PCH = KT / 8;                     // 16-byte chunks per probability row
+  static constexpr int SMEM = HP * D * 2 + 2 * KT * D * 2 + HP * KT * 4 + HP * KT * 2 + 3 * HP * 4 + 2 * KT * 4;
+};
+
+template <int HL>
+__global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnArgs a) {
+  using C = AttnCfg<HL>;
+  constexpr int HP = C::HP, MT = C::MT, G = C::G, KT = C::KT, NT = C::NT, TPR = C::TPR, PCH = C::PCH;
+  constexpr int NTHR = C::NW * 32;
+  extern __shared__ __align__(128) uint8_t attn_smem[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(attn_smem);   // [HP][D] swizzled
+  __nv_bfloat16* kvs = qs + HP * D;                                  // [2][KT][D] swizzled
+  float* ss = reinterpret_cast<float*>(kvs + 2 * KT * D);            // [HP][KT] scores
+  __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(ss + HP * KT);  // [HP][KT] probabilities, swizzled
+  float* alpha = reinterpret_cast<float*>(pb + HP * KT);             // [HP]
+  float* ms = alpha + HP;                                            // [HP]
+  float* ls = ms + HP;                                               // [HP]
+  int* valid = reinterpret_cast<int*>(ls + HP);                      // [2][KT]
 
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (a.num_valid && t >= *a.num_valid) {
-    for (int i = tid; i < HL * D / 8; i += NTHR) reinterpret_cast<uint4*>(a.o + (size_t)t * HL * D)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < HL * D / 8; i += NTHR)
+      reinterpret_cast<uint4*>(a.o + (size_t)t * HL * D)[i] = make_uint4(0, 0, 0, 0);
     return;
   }
   const int p = a.pos[t], slot = a.slots[t];
@@ -72,12 +116,20 @@ __global__ void __launch_bounds__(NTHR) sparse_attn_kernel(AttnArgs a) {
   const int ntiles = (ntot + KT - 1) / KT;
   const int rpp = a.ratio > 0 ? max(a.ps / a.ratio, 1) : 1;
 
-  for (int i = tid; i < HL * D / 8; i += NTHR)
-    reinterpret_cast<uint4*>(qs)[i] = reinterpret_cast<const uint4*>(a.q + (size_t)t * HL * D)[i];
-  if (tid < HL) ms[tid] = a.sink[tid], ls[tid] = 1.f;
+  // Q -> shared (rows >= HL are zero)
+  for (int i = tid; i < HP * 64; i += NTHR) {
+    const int r = i >> 6, c = i & 63;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < HL) v = reinterpret_cast<const uint4*>(a.q + ((size_t)t * HL + r) * D)[c];
+    reinterpret_cast<uint4*>(qs + r * D)[swz_row(r, c)] = v;
+  }
+  if (tid < HP) ms[tid] = tid < HL ? a.sink[tid] : 0.f, ls[tid] = 1.f;
 
+  constexpr int TPK = NTHR / KT;       // threads cooperating on one key row
+  constexpr int CPT = 64 / TPK;        // 16-byte chunks per thread
   auto issue_tile = [&](int tile, int buf) {
-    const int key = tile * KT + (tid >> 3);
+    const int kk = tid / TPK, part = tid % TPK;
+    const int key = tile * KT + kk;
     const __nv_bfloat16* src = nullptr;
     if (key < ntot) {
       if (key < nc) {
@@ -89,25 +141,25 @@ __global__ void __launch_bounds__(NTHR) sparse_attn_kernel(AttnArgs a) {
       } else {
         const int pp = p - ns + 1 + (key - nc);
         const int loc = pt[pp];
-        const int ss = a.swa_map[loc / a.ps];
-        if (ss >= 0) src = a.swa + ((size_t)ss * a.ps + loc % a.ps) * D;
+        const int sl = a.swa_map[loc / a.ps];
+        if (sl >= 0) src = a.swa + ((size_t)sl * a.ps + loc % a.ps) * D;
       }
     }
-    __nv_bfloat16* dst = kvs + ((size_t)buf * KT + (tid >> 3)) * D;
-    if (src) {
+    __nv_bfloat16* dst = kvs + ((size_t)buf * KT + kk) * D;
+    const __nv_bfloat16* s0 = src ? src : a.swa;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int ch = (tid & 7) + 8 * c;
-        cp_async16(dst + ch * 8, src + ch * 8);
-      }
+    for (int c = 0; c < CPT; ++c) {
+      const int ch = part + TPK * c;
+      cp_async16_zfill(dst + swz_row(kk, ch) * 8, s0 + ch * 8, src != nullptr);
     }
-    if ((tid & 7) == 0) valid[buf * KT + (tid >> 3)] = src != nullptr;
+    if (part == 0) valid[buf * KT + kk] = src != nullptr;
     cp_async_commit();
   };
 
-  float acc[HL][2];
+  const int mt = warp % MT, g = warp / MT;
+  float acc[NT][4];
 #pragma unroll
-  for (int h = 0; h < HL; ++h) acc[h][0] = acc[h][1] = 0.f;
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
   if (ntiles > 0) issue_tile(0, 0);
   for (int tile = 0; tile < ntiles; ++tile) {
@@ -120,100 +172,120 @@ __global__ void __launch_bounds__(NTHR) sparse_attn_kernel(AttnArgs a) {
     }
     __syncthreads();
     const __nv_bfloat16* kt = kvs + (size_t)buf * KT * D;
-    // scores: warp w handles keys w, w+8, w+16, w+24; lane holds 16 dims of the key in registers
-#pragma unroll 1
-    for (int kk = warp; kk < KT; kk += 8) {
-      const bool ok = valid[buf * KT + kk] != 0;
-      float kf[16];
-      if (ok) {
-        const uint4 u0 = *reinterpret_cast<const uint4*>(kt + kk * D + lane * 16);
-        const uint4 u1 = *reinterpret_cast<const uint4*>(kt + kk * D + lane * 16 + 8);
-        const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&u0);
-        const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&u1);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f0 = __bfloat1622float2(p0[i]), f1 = __bfloat1622float2(p1[i]);
-          kf[2 * i] = f0.x, kf[2 * i + 1] = f0.y, kf[8 + 2 * i] = f1.x, kf[8 + 2 * i + 1] = f1.y;
-        }
-      }
-      for (int h = 0; h < HL; ++h) {
-        float s = 0.f;
-        if (ok) {
-          const uint4 u0 = *reinterpret_cast<const uint4*>(qs + h * D + lane * 16);
-          const uint4 u1 = *reinterpret_cast<const uint4*>(qs + h * D + lane * 16 + 8);
-          const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&u0);
-          const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&u1);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f0 = __bfloat1622float2(p0[i]), f1 = __bfloat1622float2(p1[i]);
-            s = fmaf(f0.x, kf[2 * i], s);
-            s = fmaf(f0.y, kf[2 * i + 1], s);
-            s = fmaf(f1.x, kf[8 + 2 * i], s);
-            s = fmaf(f1.y, kf[8 + 2 * i + 1], s);
-          }
-          s = warp_sum(s);
-        }
-        if (lane == 0) ps_[h * KT + kk] = ok ? s * a.scale : -INFINITY;
-      }
-    }
-    __syncthreads();
-    // online softmax bookkeeping: one thread per head
-    if (tid < HL) {
-      float m_old = ms[tid], mx = m_old;
-#pragma unroll
-      for (int k = 0; k < KT; ++k) mx = fmaxf(mx, ps_[tid * KT + k]);
-      float sum = 0.f;
-#pragma unroll
-      for (int k = 0; k < KT; ++k) {
-        const float e = __expf(ps_[tid * KT + k] - mx);
-        ps_[tid * KT + k] = e;
-        sum += e;
-      }
-      const float al = __expf(m_old - mx);
-      alpha[tid] = al;
-      ms[tid] = mx;
-      ls[tid] = ls[tid] * al + sum;
-    }
-    __syncthreads();
-    // O += P V ; thread owns dims {2*tid, 2*tid+1} of every head
-#pragma unroll
-    for (int h = 0; h < HL; ++h) {
-      const float al = alpha[h];
-      acc[h][0] *= al;
-      acc[h][1] *= al;
-    }
+    // ---- S = Q K^T : one 16 x 8 tile per warp (head tile mt, keys g*8 .. g*8+7)
+    {
+      float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};
+      const int arow = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int brow = g * 8 + (lane & 7);
 #pragma unroll 4
-    for (int k = 0; k < KT; ++k) {
-      if (!valid[buf * KT + k]) continue;
-      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kt + k * D + 2 * tid));
+      for (int ks = 0; ks < 32; ks += 2) {
+        uint32_t af[4], af2[4], bf[4];
+        ldsm_x4(af, qs + arow * D + swz_row(arow, ks * 2 + (lane >> 4)) * 8);
+        ldsm_x4(af2, qs + arow * D + swz_row(arow, ks * 2 + 2 + (lane >> 4)) * 8);
+        ldsm_x4(bf, kt + brow * D + swz_row(brow, ks * 2 + (lane >> 3)) * 8);
+        mma_bf16(s0, af, bf[0], bf[1]);
+        mma_bf16(s1, af2, bf[2], bf[3]);
+      }
+      const int r0 = mt * 16 + (lane >> 2), c0 = g * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(ss + r0 * KT + c0) = make_float2((s0[0] + s1[0]) * a.scale, (s0[1] + s1[1]) * a.scale);
+      *reinterpret_cast<float2*>(ss + (r0 + 8) * KT + c0) =
+          make_float2((s0[2] + s1[2]) * a.scale, (s0[3] + s1[3]) * a.scale);
+    }
+    __syncthreads();
+    // ---- online softmax: TPR threads per head row, 4 keys each
+    {
+      const int row = tid / TPR, seg = tid % TPR;
+      float v[4];
+      float mx = -INFINITY;
 #pragma unroll
-      for (int h = 0; h < HL; ++h) {
-        const float pv = ps_[h * KT + k];
-        acc[h][0] = fmaf(pv, v.x, acc[h][0]);
-        acc[h][1] = fmaf(pv, v.y, acc[h][1]);
+      for (int i = 0; i < 4; ++i) {
+        const int k = seg * 4 + i;
+        v[i] = valid[buf * KT + k] ? ss[row * KT + k] : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+      }
+#pragma unroll
+      for (int o = TPR / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_old = ms[row];
+      const float m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+      __nv_bfloat16 pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float e = __expf(v[i] - m_new);
+        pv[i] = f2bf(e);
+        sum += bf2f(pv[i]);
+      }
+#pragma unroll
+      for (int o = TPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      // 4 keys = 8 bytes = half a 16-byte chunk
+      const int ch = seg >> 1, half = seg & 1;
+      constexpr int RP = 8 / PCH;  // rows per 128 bytes
+      const int pch = ch ^ ((row / RP) % PCH);
+      *reinterpret_cast<uint2*>(pb + row * KT + pch * 8 + half * 4) = *reinterpret_cast<uint2*>(pv);
+      __syncwarp();
+      if (seg == 0) {
+        const float al = __expf(m_old - m_new);
+        alpha[row] = al;
+        ms[row] = m_new;
+        ls[row] = ls[row] * al + sum;
+      }
+    }
+    __syncthreads();
+    // ---- O += P V : head tile mt, output dims [g*DW, (g+1)*DW)
+    {
+      const float al0 = alpha[mt * 16 + (lane >> 2)], al1 = alpha[mt * 16 + (lane >> 2) + 8];
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        acc[i][0] *= al0, acc[i][1] *= al0, acc[i][2] *= al1, acc[i][3] *= al1;
+      }
+      constexpr int RP = 8 / PCH;
+      const int prow = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int kk = 0; kk < KT / 16; ++kk) {
+        uint32_t pf[4];
+        const int pch = (kk * 2 + (lane >> 4)) ^ ((prow / RP) % PCH);
+        ldsm_x4(pf, pb + prow * KT + pch * 8);
+        const int vrow = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt += 2) {
+          uint32_t vf[4];
+          const int dch = g * (C::DW / 8) + nt + (lane >> 4);
+          ldsm_x4_trans(vf, kt + vrow * D + swz_row(vrow, dch) * 8);
+          mma_bf16(acc[nt], pf, vf[0], vf[1]);
+          mma_bf16(acc[nt + 1], pf, vf[2], vf[3]);
+        }
       }
     }
     __syncthreads();
   }
   __syncthreads();
+  {
+    const int r0 = mt * 16 + (lane >> 2);
+    const float i0 = 1.f / ls[r0], i1 = 1.f / ls[r0 + 8];
 #pragma unroll
-  for (int h = 0; h < HL; ++h) {
-    const float inv = 1.f / ls[h];
-    *reinterpret_cast<__nv_bfloat162*>(a.o + ((size_t)t * HL + h) * D + 2 * tid) =
-        __floats2bfloat162_rn(acc[h][0] * inv, acc[h][1] * inv);
+    for (int nt = 0; nt < NT; ++nt) {
+      const int d0 = g * C::DW + nt * 8 + (lane & 3) * 2;
+      if (r0 < HL)
+        *reinterpret_cast<__nv_bfloat162*>(a.o + ((size_t)t * HL + r0) * D + d0) =
+            __floats2bfloat162_rn(acc[nt][0] * i0, acc[nt][1] * i0);
+      if (r0 + 8 < HL)
+        *reinterpret_cast<__nv_bfloat162*>(a.o + ((size_t)t * HL + r0 + 8) * D + d0) =
+            __floats2bfloat162_rn(acc[nt][2] * i1, acc[nt][3] * i1);
+    }
   }
 }
 
 template <int HL>
 int launch_attn(const AttnArgs& a, int t, cudaStream_t st) {
-  const int smem = HL * D * 2 + 2 * KT * D * 2 + (HL * KT + 3 * HL) * 4 + 2 * KT * 4;
+  using C = AttnCfg<HL>;
   static bool set = false;
   if (!set) {
-    if (cudaFuncSetAttribute(sparse_attn_kernel<HL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(sparse_attn_kernel<HL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) !=
+        cudaSuccess)
       return 301;
     set = true;
   }
-  sparse_attn_kernel<HL><<<t, NTHR, smem, st>>>(a);
+  sparse_attn_kernel<HL><<<t, C::NW * 32, C::SMEM, st>>>(a);
   return (int)cudaGetLastError();
 }
 

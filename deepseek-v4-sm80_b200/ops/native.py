@@ -79,11 +79,38 @@ def add_launches(n: int) -> None:
     _LAUNCHES[0] += n
 
 
+_PROFILE = {"on": False, "events": []}
+
+
+def enable_profile(on: bool = True) -> None:
+    """Per-launcher device timing (CUDA events around every call); for kernel-share breakdowns, not for benchmarks."""
+    _PROFILE["on"] = on
+    _PROFILE["events"] = []
+
+
+def profile_report() -> dict:
+    """{launcher: (calls, total ms)} since enable_profile(); synchronises the device."""
+    torch.cuda.synchronize()
+    out = {}
+    for name, a, b in _PROFILE["events"]:
+        c, t = out.get(name, (0, 0.0))
+        out[name] = (c + 1, t + a.elapsed_time(b))
+    _PROFILE["events"] = []
+    return dict(sorted(out.items(), key=lambda kv: -kv[1][1]))
+
+
 def call(name: str, *args) -> None:
     """Calls ``dsv4_<name>(*args, stream)`` and raises on a non-zero return code."""
     fn = getattr(cuda_lib(), "dsv4_" + name)
     _LAUNCHES[0] += 1
-    code = fn(*args, stream())
+    if _PROFILE["on"]:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        code = fn(*args, stream())
+        b.record()
+        _PROFILE["events"].append((name, a, b))
+    else:
+        code = fn(*args, stream())
     if code != 0:
         raise NativeError(f"dsv4_{name} failed with code {code}")
 
