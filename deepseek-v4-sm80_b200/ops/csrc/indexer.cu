@@ -197,3 +197,56 @@ DSV4_API int dsv4_topk(const float* logits, int width, const int* pos, int* idx,
   topk_kernel<<<t, 1024, 0, st>>>(logits, width, pos, idx, out_len, k);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------ allocation-free entry point (see noalloc.h)
+#include "noalloc.h"
+
+#include <stdio.h>
+
+namespace {
+// The logits workspace of the allocation-free entry point.  In host code this name is only a handle for the runtime
+// (taking its address on the host does NOT give a device pointer); kernels get the address from cudaGetSymbolAddress.
+static __device__ __align__(256) float g_noalloc_logits[DSV4_NOALLOC_MAX_ELEMS];
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+thread_local char g_noalloc_err[256] = "";
+}  // namespace
+
+DSV4_API const char* dsv4_noalloc_last_error(void) { return g_noalloc_err; }
+
+DSV4_API int dsv4_indexer_select_noalloc(const void* qc, const float* wf, const void* kvals, const float* kscale,
+                                         const int* slots, const int* pos, const int* page_table, int ld_pt, int ps,
+                                         int width, int t, int heads, int d, int* idx, int* out_len, int k,
+                                         cudaStream_t stream) {
+  g_noalloc_err[0] = 0;
+  if (t <= 0) return 0;
+  if (width <= 0 || (unsigned long long)t * (unsigned long long)width > DSV4_NOALLOC_MAX_ELEMS) {
+    snprintf(g_noalloc_err, sizeof g_noalloc_err,
+             "dsv4_indexer_select_noalloc: t * width = %d * %d exceeds the built-in workspace of %u floats; "
+             "split the batch or use dsv4_indexer_logits + dsv4_topk with your own buffer",
+             t, width, DSV4_NOALLOC_MAX_ELEMS);
+    return 460;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(g_noalloc_err, sizeof g_noalloc_err, "dsv4_indexer_select_noalloc: cannot identify the current device");
+    return 461;
+  }
+  if (!g_noalloc_ptr[dev]) {  // once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_logits);
+    if (e != cudaSuccess || !p) {
+      snprintf(g_noalloc_err, sizeof g_noalloc_err, "dsv4_indexer_select_noalloc: cudaGetSymbolAddress failed: %s",
+               cudaGetErrorString(e));
+      return 461;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  float* logits = g_noalloc_ptr[dev];
+  int rc = dsv4_indexer_logits(qc, wf, kvals, kscale, slots, pos, page_table, ld_pt, ps, logits, width, t, heads, d,
+                               stream);
+  if (rc == 0) rc = dsv4_topk(logits, width, pos, idx, out_len, t, k, stream);
+  if (rc != 0) snprintf(g_noalloc_err, sizeof g_noalloc_err, "dsv4_indexer_select_noalloc: launch failed with code %d", rc);
+  return rc;
+}
