@@ -133,8 +133,9 @@ def pick_layers(args, world: int) -> int:
     expert_bytes = e_local * (3 * inter * cfg.hidden_size // 2 + 3 * inter * cfg.hidden_size // 32)
     dense = (170 << 20) // world + (60 << 20)
     per_layer = expert_bytes + dense
-    reserve = (22 << 30) + 2 * cfg.vocab_size * cfg.hidden_size * 2 // max(world // 2, 1)
-    return max(min(int((free * 0.94 - reserve) // per_layer), 43), 1)
+    # embedding + head shard, KV pools and rings, prefill activations, CUDA context, 4 % head-room
+    reserve = int(0.04 * total) + cfg.vocab_size * cfg.hidden_size * 2 * (1 + 1 / world) + (12 << 30)
+    return max(min(int((free - reserve) // per_layer), 43), 1)
 
 
 def main():
@@ -174,7 +175,7 @@ def main():
     ctx = args.prompt_len + n_out + 256
     llm = LLM(model_config=cfg, tp_info=DistributedInfo(rank, world), use_dummy_weight=True, recipe="default_m128",
               max_running_req=args.batch, context_length=max(ctx, 4096), moe_mode=args.moe_mode,
-              use_pynccl=not args.no_fused_comm, disable_log_stats=True,
+              use_pynccl=not args.no_fused_comm, disable_log_stats=True, memory_ratio=0.97,
               cuda_graph_max_bs=0 if args.no_graph else args.batch,
               cuda_graph_bs=None if args.no_graph else [args.batch])
     eng = llm.engine
@@ -253,6 +254,7 @@ def main():
                        "global_batch": args.batch, "seq_len": args.prompt_len, "output_len": n_out,
                        "parallelism": f"tp{world}" + (f"+{args.moe_mode}{world}" if world > 1 else ""),
                        "page_size": eng.page_size, "cuda_graph": eng.graph_runner is not None,
+                       "kv_pages": eng.num_pages, "swa_slots": eng.kv_plan["swa_slots"],
                        "l2": "inputs larger than L2 (weights read per step: %.1f GiB per GPU)" % (eng.weight_bytes / 2**30)},
             "clocks": clk,
             "e2e": {"value": round(tokens / wall, 2), "unit": "tok/s",

@@ -42,12 +42,12 @@ class ForwardOutput:
 
 
 def swa_slot_plan(max_running_req: int, prefill_budget: int, page_size: int, window: int) -> int:
-    """SWA slots to reserve: the pages of one full prefill forward, a window tail (+1 page being written) per running
-    request, one spare; never fewer than 8 per request for 16 or more requests (python/minisgl/engine/engine.py:569-584)."""
-    n = div_ceil(prefill_budget, page_size) + max_running_req * (div_ceil(window, page_size) + 1) + 1
-    if max_running_req >= 16:
-        n = max(n, 8 * max_running_req)
-    return n
+    """Sliding-window slots to reserve.  A page holds a slot from allocation until it lies wholly behind its request's
+    window, so the live set is: the pages of one full prefill forward, a window tail plus the page being written per
+    running request, one more per request for the step that overlap scheduling keeps in flight, and one spare.
+    (The reference reserves at least 8 per request, python/minisgl/engine/engine.py:569-584; its pages keep their
+    window storage longer because release there is tied to the radix tree.)"""
+    return div_ceil(prefill_budget, page_size) + max_running_req * (div_ceil(window, page_size) + 2) + 1
 
 
 class Engine:

@@ -112,13 +112,7 @@ class DSV4Model:
         o = O.attention(q, fb, kvv["swa"], self.pool.swa_map, kvv.get("comp"), ratio, topk_idx, topk_len,
                         w[p + "sink"], cfg.head_dim ** -0.5, ps, cfg.window_size)
         o = O.rope_tail(o, fb.positions, rope, inverse=True)
-        dg = cfg.num_heads * cfg.head_dim // cfg.o_groups
-        o = o.reshape(t, self.g_local, dg)
-        wa = w[p + "wo_a.weight_bf16"]
-        o2 = torch.empty(t, self.g_local * cfg.o_lora_rank, dtype=y.dtype, device=y.device)
-        for g in range(self.g_local):
-            O.gemm_bf16(o[:, g], wa[g * cfg.o_lora_rank:(g + 1) * cfg.o_lora_rank],
-                        out=o2[:, g * cfg.o_lora_rank:(g + 1) * cfg.o_lora_rank])
+        o2 = O.gemm_bf16_grouped(o.reshape(t, self.h_local * cfg.head_dim), w[p + "wo_a.weight_bf16"], self.g_local)
         if getattr(self.comm, "fused", False):
             oq = O.fp8_quant(o2)
             return self.comm.gemm_fp8_allreduce(oq[0], oq[1], w[p + "wo_b.weight"], w[p + "wo_b.scale"])

@@ -13,6 +13,7 @@ from . import ref
 
 gemm_bf16 = _gemm.gemm_bf16
 gemm_fp8 = _gemm.gemm_fp8
+gemm_bf16_grouped = _gemm.gemm_bf16_grouped
 
 
 def _cu():

@@ -1,19 +1,24 @@
 // Dense projection GEMM for sm_100a:  out[M,N] = X[M,K] * W[N,K]^T  (both operands K-major).
 //
-// One CTA computes a 128 x BN output tile.  Warp 0 streams A/B k-tiles with TMA
-// (128-byte swizzle) through a multi-stage mbarrier ring, warp 1 issues
-// tcgen05.mma with the accumulator in tensor memory, warps 2-5 read the
-// accumulator back with tcgen05.ld and write the result.
+// One CTA computes a 128 x BN output tile (or, with split-K, its share of the K range).  Warp 0 streams A/B k-tiles
+// with TMA (128-byte swizzle) through a multi-stage mbarrier ring, warp 1 issues tcgen05.mma with the accumulator in
+// tensor memory, warps 2-5 read the accumulator back with tcgen05.ld and write the result.
 //
 // Two operand formats:
-//   * bf16 x bf16 (kind::f16), fp32 accumulate over the whole K in one TMEM buffer.
-//   * e4m3 x e4m3 (kind::f8f6f4) with power-of-two block scales: activations carry
-//     one fp32 scale per (row, 128-wide K block), weights one per (128 x 128)
-//     block.  Each 128-wide K block is accumulated on the tensor cores into one
-//     of two TMEM buffers and promoted into fp32 registers by the epilogue warps
-//     as  acc += sa[row,kb] * sw[nb,kb] * partial  -- the exact arithmetic of the
-//     reference's "fake-quant activations x dequantised weights" path
-//     (python/minisgl/models/deepseek_v4.py:145-149, :483) up to summation order.
+//   * bf16 x bf16 (kind::f16), fp32 accumulate over the CTA's K range in one TMEM buffer.
+//   * e4m3 x e4m3 (kind::f8f6f4) with power-of-two block scales: activations carry one fp32 scale per (row, 128-wide
+//     K block), weights one per (128 x 128) block.  Each 128-wide K block is accumulated on the tensor cores into one
+//     of two TMEM buffers and promoted into fp32 registers by the epilogue warps as
+//     acc += sa[row,kb] * sw[nb,kb] * partial  -- the exact arithmetic of the reference's "fake-quant activations x
+//     dequantised weights" path (python/minisgl/models/deepseek_v4.py:145-149, :483) up to summation order.
+//
+// Three launch extensions, all through blockIdx.z = batch * splits + split:
+//   * batched: batch b reads A columns [b*a_col_pb, +K), B rows [b*b_row_pb, +N) and writes output columns
+//     [b*out_col_pb, +N) -- the grouped low-rank output projection (wo_a) in one launch;
+//   * split-K for skinny problems: every split writes its fp32 partial tile to a workspace, the last split to arrive
+//     (per-tile counter) sums the partials in split order, so the result does not depend on arrival order;
+//   * fused all-reduce: the epilogue publishes the partial tile to the rank's symmetric buffer and reduces the peers'
+//     tiles over NVLink (comm.cuh).
 #include "comm.cuh"
 
 namespace {
@@ -28,6 +33,18 @@ struct GemmCfg {
   static constexpr int kBBytes = BN * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmArgs {
+  int M, N, K, ldo;
+  const float* sa;     // [M, K/128] (fp8)
+  const float* sb;     // [rows/128, K/128] (fp8), indexed with the batch's row offset
+  int sb_ld;           // scale blocks per weight row block (= K/128 of the full weight)
+  int accumulate_out;
+  int a_col_pb, b_row_pb, out_col_pb;
+  int splits;
+  float* ws;           // [tiles][splits][128][BN] fp32 partials
+  int* counters;       // [tiles], zero between launches
 };
 
 __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const float* v, int ncols_valid) {
@@ -66,8 +83,7 @@ __device__ __forceinline__ void store_row_chunk(float* dst, const float* v, int 
 template <int BN, bool FP8, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ out,
-               int M, int N, int K, int ldo, const float* __restrict__ sa, const float* __restrict__ sb, int accumulate_out,
-               const CommCtx comm) {
+               const GemmArgs g, const CommCtx comm) {
   using Cfg = GemmCfg<BN>;
   constexpr int S = Cfg::kStages;
   constexpr int BK = FP8 ? 128 : 64;  // elements per k-tile (= 128 bytes)
@@ -83,13 +99,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* tempty = tfull + 2;  // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  volatile int* sh_flag = reinterpret_cast<volatile int*>(tmem_holder + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int M = g.M, N = g.N;
+  const int batch = blockIdx.z / g.splits, split = blockIdx.z % g.splits;
   const int n0 = blockIdx.x * BN;
   const int m0 = blockIdx.y * kBM;
-  const int k_tiles = (K + BK - 1) / BK;
-  const int kblocks = k_tiles;  // FP8: one scale block per k-tile
+  const int k_tiles = (g.K + BK - 1) / BK;
+  const int kt_per = (k_tiles + g.splits - 1) / g.splits;
+  const int kt0 = split * kt_per;
+  const int nkt = max(min(kt0 + kt_per, k_tiles) - kt0, 0);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -116,25 +137,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        const int s = kt % S;
-        const uint32_t ph = (kt / S) & 1;
+      const int ax = batch * g.a_col_pb, by = batch * g.b_row_pb + n0;
+      for (int i = 0; i < nkt; ++i) {
+        const int s = i % S;
+        const uint32_t ph = (i / S) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, 1)) break;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
         uint8_t* a = tiles + s * Cfg::kStageBytes;
-        tma_load_2d(a, &tmA, &full[s], kt * BK, m0);
-        tma_load_2d(a + Cfg::kABytes, &tmB, &full[s], kt * BK, n0);
+        tma_load_2d(a, &tmA, &full[s], ax + (kt0 + i) * BK, m0);
+        tma_load_2d(a + Cfg::kABytes, &tmB, &full[s], (kt0 + i) * BK, by);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        const int s = kt % S;
-        const uint32_t ph = (kt / S) & 1;
+      for (int i = 0; i < nkt; ++i) {
+        const int s = i % S;
+        const uint32_t ph = (i / S) & 1;
         uint32_t d = tmem_base;
         if (FP8) {
-          const int b = kt & 1;
-          if (!mbar_wait(&tempty[b], ((kt >> 1) & 1) ^ 1, abort_flag, 2)) break;
+          const int b = i & 1;
+          if (!mbar_wait(&tempty[b], ((i >> 1) & 1) ^ 1, abort_flag, 2)) break;
           d = tmem_base + b * BN;
         }
         if (!mbar_wait(&full[s], ph, abort_flag, 3)) break;
@@ -145,16 +167,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int k = 0; k < 4; ++k) {
           const uint64_t ad = umma_desc_k128(a, k * 32);
           const uint64_t bd = umma_desc_k128(bt, k * 32);
-          const uint32_t acc = FP8 ? (k > 0) : (kt > 0 || k > 0);
+          const uint32_t acc = FP8 ? (k > 0) : (i > 0 || k > 0);
           if (FP8)
             umma_f8(d, ad, bd, kIdesc, acc);
           else
             umma_f16(d, ad, bd, kIdesc, acc);
         }
         umma_commit(&empty[s]);
-        if (FP8) umma_commit(&tfull[kt & 1]);
+        if (FP8) umma_commit(&tfull[i & 1]);
       }
-      if (!FP8) umma_commit(&tfull[0]);
+      if (!FP8 && nkt > 0) umma_commit(&tfull[0]);
     }
   } else {
     // epilogue warps 2..5 ; TMEM lane quarter = warp % 4
@@ -162,55 +184,46 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int row = q * 32 + lane;
     const int grow = m0 + row;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    // fused all-reduce: the partial tile goes to this rank's symmetric buffer, the reduced tile to `out`
     const bool fused = comm.world > 1;
     uint32_t epoch = 0;
-    OutT* part = out;
-    int ld_part = ldo;
+    OutT* part = out + (size_t)batch * g.out_col_pb;
+    int ld_part = g.ldo;
     if (fused) {
       epoch = comm_epoch(comm);
       part = reinterpret_cast<OutT*>(comm_data(comm, comm.rank, epoch & 1));
       ld_part = N;
     }
+    float acc[BN];
+#pragma unroll
+    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+    bool ok = true;
     if (!FP8) {
-      bool ok = mbar_wait(&tfull[0], 0, abort_flag, 4);
-      tc_fence_after();
-      if (ok) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(lane_addr + c * 32, r);
-          tmem_ld_wait();
-          float v[32];
+      if (nkt > 0) {
+        ok = mbar_wait(&tfull[0], 0, abort_flag, 4);
+        tc_fence_after();
+        if (ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          const int col = n0 + c * 32;
-          if (grow < M && col < N) {
-            OutT* dst = part + (size_t)grow * ld_part + col;
-            if (accumulate_out) {
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(lane_addr + c * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col + j < N) v[j] += (float)dst[j];
-            }
-            store_row_chunk(dst, v, N - col);
+            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(r[j]);
           }
         }
       }
     } else {
-      float acc[BN];
-#pragma unroll
-      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
-      const int nb = n0 >> 7;
-      bool ok = true;
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        const int b = kt & 1;
-        if (!mbar_wait(&tfull[b], (kt >> 1) & 1, abort_flag, 5)) {
+      const size_t sb_row = (size_t)((batch * g.b_row_pb + n0) >> 7) * g.sb_ld;
+      const int kblocks = k_tiles;
+      for (int i = 0; i < nkt; ++i) {
+        const int b = i & 1;
+        if (!mbar_wait(&tfull[b], (i >> 1) & 1, abort_flag, 5)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const float s_a = (grow < M) ? sa[(size_t)grow * kblocks + kt] : 0.f;
-        const float sc = s_a * sb[(size_t)nb * kblocks + kt];
+        const float s_a = (grow < M) ? g.sa[(size_t)grow * kblocks + kt0 + i] : 0.f;
+        const float sc = s_a * g.sb[sb_row + kt0 + i];
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -222,38 +235,65 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_before();
         mbar_arrive(&tempty[b]);
       }
-      if (ok && grow < M) {
+    }
+    bool write_out = ok;
+    if (g.splits > 1) {
+      // publish this split's fp32 partial, the last split to arrive reduces all of them in split order
+      const int tile = (batch * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+      float* wsp = g.ws + (((size_t)tile * g.splits + split) * kBM + row) * BN;
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col < N) {
-            OutT* dst = part + (size_t)grow * ld_part + col;
-            if (accumulate_out) {
+      for (int j = 0; j < BN; j += 4)
+        *reinterpret_cast<float4*>(wsp + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) *sh_flag = (atomicAdd(&g.counters[tile], 1) == g.splits - 1) ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      write_out = write_out && (*sh_flag != 0);
+      if (write_out) {
+        __threadfence();
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col + j < N) acc[c * 32 + j] += (float)dst[j];
-            }
-            store_row_chunk(dst, &acc[c * 32], N - col);
+        for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+        for (int s = 0; s < g.splits; ++s) {
+          const float* p = g.ws + (((size_t)tile * g.splits + s) * kBM + row) * BN;
+#pragma unroll
+          for (int j = 0; j < BN; j += 4) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(p + j));
+            acc[j] += v.x, acc[j + 1] += v.y, acc[j + 2] += v.z, acc[j + 3] += v.w;
           }
+        }
+        if (warp == 2 && lane == 0) g.counters[tile] = 0;
+      }
+    }
+    if (write_out && grow < M) {
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col = n0 + c * 32;
+        if (col < N) {
+          OutT* dst = part + (size_t)grow * ld_part + col;
+          if (g.accumulate_out) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < N) acc[c * 32 + j] += (float)dst[j];
+          }
+          store_row_chunk(dst, &acc[c * 32], N - col);
         }
       }
     }
     if (fused) {
       if constexpr (sizeof(OutT) == 2) {
-        __shared__ int comm_ok;
         const int slot = blockIdx.y * gridDim.x + blockIdx.x;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
           comm_publish(comm, slot, epoch);
-          comm_ok = comm_wait(comm, slot, epoch) ? 1 : 0;
+          *sh_flag = comm_wait(comm, slot, epoch) ? 1 : 0;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (comm_ok && grow < M) {
+        if (*sh_flag && grow < M) {
 #pragma unroll 1
           for (int c8 = 0; c8 < BN; c8 += 8) {
             const int col = n0 + c8;
             if (col < N)
-              *reinterpret_cast<uint4*>(out + (size_t)grow * ldo + col) =
+              *reinterpret_cast<uint4*>(out + (size_t)grow * g.ldo + col) =
                   comm_reduce16(comm, epoch & 1, (size_t)grow * N + col);
           }
         }
@@ -267,15 +307,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+struct LaunchOpts {
+  int batches = 1, a_col_pb = 0, b_row_pb = 0, out_col_pb = 0;
+  int splits = 1;
+  float* ws = nullptr;
+  int* counters = nullptr;
+  int a_cols = 0, b_rows = 0;  // full extents of the operands (0 = K / N)
+  int sb_ld = 0;
+  const CommCtx* comm = nullptr;
+};
+
 template <int BN, bool FP8, typename OutT>
 int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, int ldx, int ldw, int ldo, const float* sa,
-                const float* sb, int accumulate_out, cudaStream_t stream, const CommCtx& comm) {
+                const float* sb, int accumulate_out, cudaStream_t stream, const LaunchOpts& o) {
   using Cfg = GemmCfg<BN>;
   constexpr int BK = FP8 ? 128 : 64;
   const int esz = FP8 ? 1 : 2;
   CUtensorMap tmA, tmB;
-  if (dsv4_make_tmap_2d(&tmA, x, FP8 ? 0 : 1, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * esz, BK, kBM, 3)) return 101;
-  if (dsv4_make_tmap_2d(&tmB, w, FP8 ? 0 : 1, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * esz, BK, BN, 3)) return 102;
+  const uint64_t a_cols = o.a_cols ? o.a_cols : K, b_rows = o.b_rows ? o.b_rows : N;
+  if (dsv4_make_tmap_2d(&tmA, x, FP8 ? 0 : 1, a_cols, (uint64_t)M, (uint64_t)ldx * esz, BK, kBM, 3)) return 101;
+  if (dsv4_make_tmap_2d(&tmB, w, FP8 ? 0 : 1, (uint64_t)K, b_rows, (uint64_t)ldw * esz, BK, BN, 3)) return 102;
   auto kern = gemm_tn_kernel<BN, FP8, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -283,17 +334,23 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
     if (e != cudaSuccess) return 103;
     attr_set = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM);
-  if (comm.world > 1 && (long long)grid.x * grid.y > kCommSlots) return 104;
-  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, M, N, K, ldo, sa, sb, accumulate_out, comm);
+  dim3 grid((N + BN - 1) / BN, (M + kBM - 1) / kBM, o.batches * o.splits);
+  CommCtx comm{};
+  if (o.comm) {
+    comm = *o.comm;
+    if ((long long)grid.x * grid.y > kCommSlots || o.splits != 1 || o.batches != 1) return 104;
+  }
+  GemmArgs g{M, N, K, ldo, sa, sb, o.sb_ld ? o.sb_ld : (K + 127) / 128, accumulate_out, o.a_col_pb, o.b_row_pb,
+             o.out_col_pb, o.splits, o.ws, o.counters};
+  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, g, comm);
   return (int)cudaGetLastError();
 }
 
 template <bool FP8, typename OutT>
 int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, int ldx, int ldw, int ldo, const float* sa,
-                const float* sb, int acc, int bn, cudaStream_t st, const CommCtx& comm = CommCtx{}) {
+                const float* sb, int acc, int bn, cudaStream_t st, const LaunchOpts& o = LaunchOpts{}) {
   if (bn == 0) {
-    const int mt = (M + kBM - 1) / kBM;
+    const int mt = (M + kBM - 1) / kBM * o.batches;
     if (mt * ((N + 127) / 128) >= 148 && !FP8)
       bn = 128;
     else if (mt * ((N + 63) / 64) >= 148)
@@ -304,37 +361,57 @@ int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, in
   if (FP8 && bn > 64) bn = 64;
   switch (bn) {
     case 128:
-      if constexpr (!FP8) return launch_gemm<128, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, comm);
+      if constexpr (!FP8) return launch_gemm<128, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, o);
     case 64:
-      return launch_gemm<64, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, comm);
+      return launch_gemm<64, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, o);
     default:
-      return launch_gemm<32, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, comm);
+      return launch_gemm<32, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, o);
   }
 }
 
 }  // namespace
 
+// Workspace floats needed for a split-K launch: tiles * splits * 128 * bn.
+DSV4_API long long dsv4_gemm_splitk_ws_elems(int M, int N, int bn, int batches, int splits) {
+  const long long tiles = (long long)((N + bn - 1) / bn) * ((M + kBM - 1) / kBM) * batches;
+  return tiles * splits * kBM * bn;
+}
+
 // out dtype: 0 = bf16, 1 = fp32.  ld* are row strides in elements.  bn = 0 picks the tile width.
+// batches > 1: batch b uses A columns [b*K, (b+1)*K) of x (ldx covers all batches), W rows [b*N, (b+1)*N) and output
+// columns [b*N, (b+1)*N).  splits > 1 needs ws (dsv4_gemm_splitk_ws_elems floats) and counters (>= tiles ints, zero).
 DSV4_API int dsv4_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo,
-                            int out_fp32, int accumulate_out, int bn, cudaStream_t stream) {
+                            int out_fp32, int accumulate_out, int bn, int batches, int splits, float* ws, int* counters,
+                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((K % 8) || (ldx % 8) || (ldw % 8)) return 110;
+  LaunchOpts o;
+  o.batches = batches < 1 ? 1 : batches;
+  o.splits = splits < 1 ? 1 : splits;
+  o.ws = ws, o.counters = counters;
+  if (o.batches > 1) o.a_col_pb = K, o.b_row_pb = N, o.out_col_pb = N, o.a_cols = K * o.batches, o.b_rows = N * o.batches;
+  if (o.splits > 1 && (bn == 0 || !ws || !counters)) return 116;
   if (out_fp32)
     return dispatch_bn<false, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, nullptr, nullptr, accumulate_out, bn,
-                                     stream);
+                                     stream, o);
   return dispatch_bn<false, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, nullptr, nullptr,
-                                           accumulate_out, bn, stream);
+                                           accumulate_out, bn, stream, o);
 }
 
 // x: e4m3 [M,K] with sa fp32 [M, K/128];  w: e4m3 [N,K] with sb fp32 [ceil(N/128), K/128].
 DSV4_API int dsv4_gemm_fp8(const void* x, const void* w, void* out, const float* sa, const float* sb, int M, int N, int K,
-                           int ldx, int ldw, int ldo, int out_fp32, int accumulate_out, int bn, cudaStream_t stream) {
+                           int ldx, int ldw, int ldo, int out_fp32, int accumulate_out, int bn, int splits, float* ws,
+                           int* counters, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((K % 128) || (ldx % 16) || (ldw % 16)) return 111;
+  LaunchOpts o;
+  o.splits = splits < 1 ? 1 : splits;
+  o.ws = ws, o.counters = counters;
+  if (o.splits > 1 && (bn == 0 || !ws || !counters)) return 117;
   if (out_fp32)
-    return dispatch_bn<true, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn, stream);
+    return dispatch_bn<true, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn, stream, o);
   return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn,
-                                          stream);
+                                          stream, o);
 }
 
 // Fused projection + all-reduce: every rank multiplies its K-shard, the epilogue publishes the partial tile to the
@@ -344,13 +421,17 @@ DSV4_API int dsv4_gemm_fp8_allreduce(const void* x, const void* w, void* out, co
   if (M <= 0 || N <= 0) return 0;
   if ((K % 128) || (ldx % 16) || (ldw % 16) || (N % 8)) return 112;
   if ((long long)M * N * 2 > comm->data_bytes) return 113;
-  return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, N, sa, sb, 0, bn, stream, *comm);
+  LaunchOpts o;
+  o.comm = comm;
+  return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, N, sa, sb, 0, bn, stream, o);
 }
 DSV4_API int dsv4_gemm_bf16_allreduce(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw,
                                       const CommCtx* comm, int bn, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((K % 8) || (ldx % 8) || (ldw % 8) || (N % 8)) return 114;
   if ((long long)M * N * 2 > comm->data_bytes) return 115;
+  LaunchOpts o;
+  o.comm = comm;
   return dispatch_bn<false, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, N, nullptr, nullptr, 0, bn,
-                                           stream, *comm);
+                                           stream, o);
 }

@@ -4,20 +4,68 @@ CUDA tensors run the hand-written tcgen05/TMEM kernels in ``csrc/gemm_tcgen05.cu
 CPU tensors run the fp32 PyTorch statement of the same arithmetic, which is also the
 oracle the GPU tests compare against.  These replace the reference's cuBLAS calls on
 dequantised BF16 weight caches (python/minisgl/models/deepseek_v4.py:145-149).
+
+Skinny problems (few output tiles, long K) are split along K so that the whole GPU streams the weight; the
+partials meet in an fp32 workspace and the last split per tile reduces them in a fixed order.
 """
 from __future__ import annotations
+
+import ctypes
 
 import torch
 
 from . import native as nv
 from .native import I
 
+_COUNTERS = {}
+NUM_SMS_HINT = 148
+
 
 def _as2d(x):
     return x.reshape(-1, x.shape[-1])
 
 
-def gemm_bf16(x, w, out=None, out_dtype=torch.bfloat16, accumulate=False, bn=0):
+def _counters(device) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    c = _COUNTERS.get(key)
+    if c is None:
+        c = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        _COUNTERS[key] = c
+    return c
+
+
+def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int = 0, splits: int = 0):
+    """(tile width, K splits) that put roughly one CTA on every SM."""
+    mt = (m + 127) // 128 * batches
+    if bn == 0:
+        if mt * ((n + 127) // 128) >= NUM_SMS_HINT and not fp8:
+            bn = 128
+        elif mt * ((n + 63) // 64) >= NUM_SMS_HINT:
+            bn = 64
+        else:
+            bn = 32
+    if fp8 and bn > 64:
+        bn = 64
+    if splits == 0:
+        ctas = mt * ((n + bn - 1) // bn)
+        splits = 1
+        if ctas <= NUM_SMS_HINT // 2 and k_tiles >= 8:
+            splits = max(min(NUM_SMS_HINT // ctas, k_tiles // 4, 16), 1)
+    if mt * ((n + bn - 1) // bn) > (1 << 16):
+        splits = 1
+    return bn, splits
+
+
+def _ws(m, n, bn, batches, splits, device):
+    if splits <= 1:
+        return None, None
+    elems = nv.cuda_lib().dsv4_gemm_splitk_ws_elems
+    elems.restype = ctypes.c_longlong
+    return (torch.empty(elems(I(m), I(n), I(bn), I(batches), I(splits)), dtype=torch.float32, device=device),
+            _counters(device))
+
+
+def gemm_bf16(x, w, out=None, out_dtype=torch.bfloat16, accumulate=False, bn=0, splits=0):
     """bf16 x bf16 -> bf16 / fp32 with fp32 accumulation."""
     x2 = _as2d(x)
     m, k = x2.shape
@@ -36,12 +84,39 @@ def gemm_bf16(x, w, out=None, out_dtype=torch.bfloat16, accumulate=False, bn=0):
         out = torch.empty(*x.shape[:-1], n, dtype=out_dtype, device=x.device)
     o2 = out.reshape(-1, n) if out.is_contiguous() else out
     assert o2.stride(-1) == 1
+    bn, splits = pick_tiling(m, n, (k + 63) // 64, 1, False, bn, splits)
+    ws, cnt = _ws(m, n, bn, 1, splits, x.device)
     nv.call("gemm_bf16", nv.ptr(x2), nv.ptr(w), nv.ptr(o2), I(m), I(n), I(k), I(x2.stride(0)), I(w.stride(0)),
-            I(o2.stride(0)), I(1 if out.dtype == torch.float32 else 0), I(1 if accumulate else 0), I(bn))
+            I(o2.stride(0)), I(1 if out.dtype == torch.float32 else 0), I(1 if accumulate else 0), I(bn), I(1),
+            I(splits), nv.ptr(ws), nv.ptr(cnt))
     return out
 
 
-def gemm_fp8(xq, sx, wq, sw, out=None, out_dtype=torch.bfloat16, accumulate=False, bn=0):
+def gemm_bf16_grouped(x, w, groups: int, out=None):
+    """Per-group projection in one launch: x [T, G*K], w [G*N, K] -> out [T, G*N] with
+    out[:, g*N:(g+1)*N] = x[:, g*K:(g+1)*K] @ w[g*N:(g+1)*N]^T  (the low-rank output projection wo_a; the reference
+    runs it as torch.bmm, python/minisgl/models/deepseek_v4.py:235-263)."""
+    t = x.shape[0]
+    k = x.shape[1] // groups
+    n = w.shape[0] // groups
+    if not x.is_cuda:
+        y = torch.einsum("tgk,gnk->tgn", x.reshape(t, groups, k).float(), w.reshape(groups, n, k).float())
+        y = y.reshape(t, groups * n).to(x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    assert x.is_contiguous() and w.is_contiguous() and x.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty(t, groups * n, dtype=x.dtype, device=x.device)
+    bn, splits = pick_tiling(t, n, (k + 63) // 64, groups, False, 0, 0)
+    ws, cnt = _ws(t, n, bn, groups, splits, x.device)
+    nv.call("gemm_bf16", nv.ptr(x), nv.ptr(w), nv.ptr(out), I(t), I(n), I(k), I(x.stride(0)), I(w.stride(0)),
+            I(out.stride(0)), I(0), I(0), I(bn), I(groups), I(splits), nv.ptr(ws), nv.ptr(cnt))
+    return out
+
+
+def gemm_fp8(xq, sx, wq, sw, out=None, out_dtype=torch.bfloat16, accumulate=False, bn=0, splits=0):
     """e4m3 x e4m3 with block scales: xq [M,K] + sx fp32 [M,K/128]; wq [N,K] + sw fp32 [ceil(N/128), K/128]."""
     x2 = _as2d(xq)
     m, k = x2.shape
@@ -56,7 +131,9 @@ def gemm_fp8(xq, sx, wq, sw, out=None, out_dtype=torch.bfloat16, accumulate=Fals
     if out is None:
         out = torch.empty(*xq.shape[:-1], n, dtype=out_dtype, device=xq.device)
     o2 = out.reshape(-1, n)
+    bn, splits = pick_tiling(m, n, k // 128, 1, True, bn, splits)
+    ws, cnt = _ws(m, n, bn, 1, splits, xq.device)
     nv.call("gemm_fp8", nv.ptr(x2), nv.ptr(wq), nv.ptr(o2), nv.ptr(s2), nv.ptr(sw), I(m), I(n), I(k),
             I(x2.stride(0)), I(wq.stride(0)), I(o2.stride(0)), I(1 if out.dtype == torch.float32 else 0),
-            I(1 if accumulate else 0), I(bn))
+            I(1 if accumulate else 0), I(bn), I(splits), nv.ptr(ws), nv.ptr(cnt))
     return out

@@ -44,3 +44,42 @@ def test_gemm_fp8_block_scaled(m, n, k, bn):
     wf = quant.fp8_weight_dequant(wq, swc, dtype=torch.float32)
     ref = xf @ wf.t()
     assert torch.allclose(y, ref, rtol=1e-3, atol=1e-3), (y - ref).abs().max().item()
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(128, 64, 4096, 16), (128, 1536, 4096, 3), (40, 256, 4096, 0), (128, 2048, 4096, 2)])
+def test_gemm_bf16_split_k(m, n, k, splits):
+    torch.manual_seed(2)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    for _ in range(2):  # the per-tile counters must reset themselves
+        y = gemm.gemm_bf16(x, w, out_dtype=torch.float32, bn=32, splits=splits)
+        assert torch.allclose(y, ref, rtol=2e-3, atol=2e-3), (y - ref).abs().max().item()
+    y1 = gemm.gemm_bf16(x, w, out_dtype=torch.float32, bn=32, splits=splits)
+    assert torch.equal(y, y1)  # fixed reduction order: bitwise repeatable
+
+
+@pytest.mark.parametrize("splits", [0, 4])
+def test_gemm_fp8_split_k(splits):
+    torch.manual_seed(3)
+    m, n, k = 128, 1536, 4096
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda") * 0.02
+    xq, sx = quant.fp8_act_quant(x)
+    wq, swc = quant.fp8_weight_quant(w)
+    sw = quant.e8m0_decode(swc)
+    y = gemm.gemm_fp8(xq, sx, wq, sw, out_dtype=torch.float32, bn=32, splits=splits)
+    xf = (xq.float().reshape(m, k // 128, 128) * sx.unsqueeze(-1)).reshape(m, k)
+    ref = xf @ quant.fp8_weight_dequant(wq, swc, dtype=torch.float32).t()
+    assert torch.allclose(y, ref, rtol=1e-3, atol=1e-3), (y - ref).abs().max().item()
+
+
+@pytest.mark.parametrize("t,groups", [(128, 8), (5, 1), (300, 2)])
+def test_gemm_bf16_grouped(t, groups):
+    torch.manual_seed(4)
+    k, n = 4096, 1024
+    x = torch.randn(t, groups * k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(groups * n, k, device="cuda") * 0.03).to(torch.bfloat16)
+    y = gemm.gemm_bf16_grouped(x, w, groups)
+    ref = gemm.gemm_bf16_grouped(x.cpu(), w.cpu(), groups)
+    assert torch.allclose(y.float().cpu(), ref.float(), rtol=2e-2, atol=2e-2)
