@@ -1,0 +1,1 @@
+from .args import ServerArgs, parse_args  # noqa: F401
