@@ -21,9 +21,10 @@ from .table import TableManager
 
 def allocate_fair_prefill_chunks(*, token_budget: int, alignment_quantum: int, scheduled_tokens: Sequence[int],
                                  remaining_tokens: Sequence[int]) -> List[int]:
-    """Splits one forward's token budget.  Every request first gets one quantum (or its final tail); further quanta
-    go, one at a time, to the request with the least granted progress (FIFO index breaks ties).  A grant smaller
-    than a quantum is only ever a request's final tail -- except when the whole budget is below one quantum."""
+    """Splits one forward's token budget.  Every request first gets one quantum (or its final tail); then, in rounds,
+    every unfinished request gets another quantum, visited in order of least granted progress (FIFO index breaks
+    ties), until the budget is spent.  A grant smaller than a quantum is only ever a request's final tail -- except
+    when the whole budget is below one quantum."""
     if token_budget <= 0 or alignment_quantum <= 0:
         raise ValueError("token_budget and alignment_quantum must be positive")
     if len(scheduled_tokens) != len(remaining_tokens):
