@@ -1,0 +1,144 @@
+"""Microbenchmark of the fused compute+collective kernels against "NCCL all-reduce + separate kernel".
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m minisgl.benchmark.collectives
+
+For M in {1, 8, 32, 128, 256, 8192} rows of hidden size 4096 (bf16 activations, N(0,1) inputs), per-rank shards of the
+full model's shapes:
+  * all_reduce        : the stand-alone in-kernel all-reduce vs ``dist.all_reduce`` (NCCL)
+  * wo_b              : FP8 output projection [M, 8192/N] x [4096, 8192/N]^T with the all-reduce fused into the GEMM
+                        epilogue vs the same GEMM followed by NCCL
+  * moe_combine       : expert-parallel routed experts (256/N experts per rank, uniform-random top-6 routing), with the
+                        per-token route sum + shared expert + all-reduce in one kernel vs unfused finalize + NCCL
+Times are CUDA-event medians with an L2 flush before every timed call, reduced with MAX over ranks.  The roofline of a
+fused call is the slower of FLOPs / measured GEMM peak and NVLink bytes / 770 GB/s (one-shot all-reduce: each GPU
+pulls (N-1) * M * 4096 * 2 bytes).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+import torch.distributed as dist
+
+NVLINK_GBS = 770.0
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    try:
+        j = json.load(open(path))
+        return j["bf16_tflops"], j["hbm_gbs"], "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+def _time(fn, iters, flush):
+    from minisgl.benchmark.perf import flush_l2
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b) * 1e3)
+    t = torch.tensor([statistics.median(ts)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, nargs="+", default=[1, 8, 32, 128, 256, 8192])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--out", default="")
+    a = ap.parse_args(argv)
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    from minisgl.ops import api as O
+    from minisgl.ops import cuda as C
+    from minisgl.ops import native, quant
+    from minisgl.parallel.comm import init_distributed
+    from minisgl.parallel.info import DistributedInfo
+
+    _, comm = init_distributed(DistributedInfo(rank, world), dev, max_rows=max(a.rows), hidden=4096)
+    tflops, hbm, src = _peaks()
+    H, KO = 4096, 8192 // world
+    e_local, inter, topk = 256 // world, 2048, 6
+    g = torch.Generator(device=dev).manual_seed(rank)
+    w = torch.randn(H, KO, device=dev, generator=g) * 0.02
+    wq, wsc = quant.fp8_weight_quant(w)
+    ws = quant.e8m0_decode(wsc)
+    w13 = torch.randint(0, 256, (e_local, 2 * inter, H // 2), device=dev, dtype=torch.uint8).view(torch.int8)
+    s13 = torch.randint(119, 122, (e_local, 2 * inter, H // 32), device=dev, dtype=torch.uint8)
+    w2 = torch.randint(0, 256, (e_local, H, inter // 2), device=dev, dtype=torch.uint8).view(torch.int8)
+    s2 = torch.randint(119, 122, (e_local, H, inter // 32), device=dev, dtype=torch.uint8)
+    rows_out = []
+    for m in a.rows:
+        x = torch.randn(m, H, device=dev, generator=g).to(torch.bfloat16)
+        xo = torch.randn(m, KO, device=dev, generator=g).to(torch.bfloat16)
+        xq, sx = O.fp8_quant(xo)
+        gi = torch.Generator(device=dev).manual_seed(1234)  # identical routing on every rank
+        idx = torch.stack([torch.randperm(256, device=dev, generator=gi)[:topk] for _ in range(min(m, 512))])
+        idx = idx.repeat((m + idx.shape[0] - 1) // idx.shape[0], 1)[:m].to(torch.int32).contiguous()
+        wt = torch.rand(m, topk, device=dev, generator=gi)
+        shared = torch.randn(m, H, device=dev, generator=g).to(torch.bfloat16)
+        nccl_buf = x.clone()
+        link_bytes = (world - 1) * m * H * 2
+        t_link = link_bytes / (NVLINK_GBS * 1e3)  # us
+        res = {"rows": m, "world": world}
+        res["allreduce_nccl_us"] = _time(lambda: dist.all_reduce(nccl_buf), a.iters, True)
+        res["allreduce_ours_us"] = _time(lambda: comm.all_reduce(x), a.iters, True)
+
+        def unfused_wo_b():
+            y = O.gemm_fp8(xq, sx, wq, ws)
+            dist.all_reduce(y)
+
+        res["wo_b_gemm_plus_nccl_us"] = _time(unfused_wo_b, a.iters, True)
+        res["wo_b_fused_us"] = _time(lambda: comm.gemm_fp8_allreduce(xq, sx, wq, ws), a.iters, True)
+        flops = 2.0 * m * H * KO
+        res["wo_b_roofline_us"] = max(flops / (tflops * 1e6), t_link)
+        res["wo_b_roofline_frac"] = res["wo_b_roofline_us"] / res["wo_b_fused_us"]
+        base = rank * e_local
+
+        def moe(fused):
+            rows, plan, mt = C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, base)
+            if fused:
+                return comm.moe_finalize_allreduce(rows, plan, mt, shared, None, m, topk, H)
+            y = C.moe_finalize(rows, plan, mt, shared, None, m, topk, H)
+            dist.all_reduce(y)
+            return y
+
+        res["moe_unfused_us"] = _time(lambda: moe(False), max(a.iters // 2, 3), True)
+        res["moe_fused_us"] = _time(lambda: moe(True), max(a.iters // 2, 3), True)
+        routes_local = m * topk / world
+        moe_flops = routes_local * (2.0 * H * 2 * inter + 2.0 * inter * H)
+        touched = e_local * (1 - (1 - 1 / 256) ** (m * topk)) if m * topk < 4096 else e_local
+        moe_bytes = touched * (3 * inter * H // 2 + 3 * inter * H // 32)
+        res["moe_roofline_us"] = max(moe_flops / (tflops * 1e6), moe_bytes / (hbm * 1e3), t_link)
+        res["moe_roofline_frac"] = res["moe_roofline_us"] / res["moe_fused_us"]
+        rows_out.append(res)
+        if rank == 0:
+            print(json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in res.items()}), flush=True)
+    native.assert_device_ok()
+    if rank == 0 and a.out:
+        json.dump({"peaks": {"bf16_tflops": tflops, "hbm_gbs": hbm, "source": src, "nvlink_gbs": NVLINK_GBS},
+                   "results": rows_out}, open(a.out, "w"), indent=1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,50 @@
+"""Offline benchmark over chat-style prompts of mixed lengths with temperature sampling
+(benchmark/offline/bench_wildchat.py of the reference: 256 WildChat prompts, temperature 0.6).  Without network
+access the prompts come from a jsonl file (``--data``, one {"prompt": ...} or {"conversation": [...]} per line) or,
+by default, from a synthetic length distribution with the same median."""
+from __future__ import annotations
+
+import argparse
+import json
+import random
+import time
+
+
+def load_prompts(path, n, vocab, seed=0):
+    import torch
+
+    rng = random.Random(seed)
+    if path:
+        rows = [json.loads(l) for l in open(path)][:n]
+        return [r.get("prompt") or r["conversation"] for r in rows]
+    g = torch.Generator().manual_seed(seed)
+    lens = [int(min(max(rng.lognormvariate(5.5, 1.0), 8), 4096)) for _ in range(n)]
+    return [torch.randint(0, vocab, (l,), generator=g, dtype=torch.int32) for l in lens]
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="")
+    ap.add_argument("--data", default="")
+    ap.add_argument("-n", type=int, default=256)
+    ap.add_argument("--max-tokens", type=int, default=512)
+    ap.add_argument("--temperature", type=float, default=0.6)
+    ap.add_argument("--layers", type=int, default=4)
+    a = ap.parse_args(argv)
+    from minisgl.core import SamplingParams
+    from minisgl.llm import LLM
+    from minisgl.models.config import ModelConfig
+
+    kw = {} if a.model else dict(model_config=ModelConfig.flash().with_layers(a.layers), use_dummy_weight=True)
+    llm = LLM(a.model, recipe="default_m128", **kw)
+    prompts = load_prompts(a.data, a.n, llm.engine.model_config.vocab_size)
+    t0 = time.perf_counter()
+    outs = llm.generate(prompts, SamplingParams(temperature=a.temperature, max_tokens=a.max_tokens))
+    dt = time.perf_counter() - t0
+    if llm.tp.is_primary():
+        print({"requests": len(outs), "wall_s": dt, "output_tok_s": sum(len(o.token_ids) for o in outs) / dt})
+    llm.shutdown()
+
+
+if __name__ == "__main__":
+    main()
