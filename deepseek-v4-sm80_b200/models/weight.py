@@ -152,6 +152,12 @@ def build_layer(cfg: ModelConfig, l: int, raw: Dict[str, torch.Tensor], rank: in
     out[p + "moe.s13"] = torch.stack(s13, 0).contiguous()
     out[p + "moe.w2"] = torch.stack([g(f"ffn.experts.{e}.w2.weight") for e in experts], 0).contiguous()
     out[p + "moe.s2"] = torch.stack([_u8(g(f"ffn.experts.{e}.w2.scale")) for e in experts], 0).contiguous()
+    for key in ("moe.s13", "moe.s2"):
+        sc = out[p + key]
+        # the grouped GEMM applies a group scale as an fp16 power of two: exact for e8m0 bytes 103..142 (2^-24..2^15)
+        if sc.numel() and (int(sc.min()) < 103 or int(sc.max()) > 142):
+            raise ValueError(f"{p + key}: expert scale bytes outside [103, 142] are not representable on the fp16 "
+                             f"operand path (found {int(sc.min())}..{int(sc.max())})")
     out[p + "moe.sh_gate_up.weight"] = torch.cat(
         [g("ffn.shared_experts.w1.weight"), g("ffn.shared_experts.w3.weight")], 0).contiguous()
     out[p + "moe.sh_gate_up.scale"] = torch.cat(

@@ -6,7 +6,7 @@
 // and a stream, and are loaded from Python through ctypes.
 //
 // Every wait in this file is bounded: a wait that does not complete within
-// `kWaitLimitNs` records where it gave up in `g_dsv4_status` and returns
+// its limit (about two seconds) records where it gave up in `g_dsv4_status` and returns
 // false, and the calling kernel then unwinds (frees TMEM, returns) instead of
 // spinning forever.  The host reads the status word with dsv4_read_status().
 #pragma once
@@ -37,7 +37,8 @@ __device__ __forceinline__ void dsv4_set_error(int code, int a, int b) {
   atomicAdd(&g_dsv4_status[3], 1);
 }
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s (waits on other GPUs)
+constexpr long long kWaitLimitCycles = 4000000000ll;         // 2-3 s of SM clock (waits inside one CTA)
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
@@ -78,14 +79,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and records an error) if the phase did not
 // complete within the limit or if another thread of the CTA already gave up.
+// kSleepNs > 0 puts the warp to sleep between polls.  A polling warp is always ready to issue, so it takes issue
+// slots from the warps that share its scheduler; only a wait whose wake-up latency is on the critical path (the MMA
+// issuer's) should poll without sleeping.
+template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int where) {
   if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
   for (;;) {
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 128; ++i) {
+      if (kSleepNs > 0) __nanosleep(kSleepNs);
       if (mbar_try_wait(bar, parity)) return true;
+    }
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;
       dsv4_set_error(DSV4_ERR_WAIT_TIMEOUT, where, (int)blockIdx.x);
       return false;
@@ -147,6 +154,16 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand sits in tensor memory, row i of the 128-row tile on lane i and the
+// K elements packed two per 32-bit column (16-bit types), so K = 16 of one instruction spans 8 columns.
+__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
   asm volatile(
@@ -199,6 +216,16 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "r"(taddr)
       : "memory");
 }
+// registers -> TMEM: thread (lane) i of the warp writes 16 consecutive 32-bit columns of TMEM lane (warp % 4) * 32 + i
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- misc math

@@ -5,23 +5,23 @@
 // ("swap-AB": the weight rows sit on the 128 TMEM lanes, routes are the UMMA N dimension, so an expert with a
 // handful of routes costs an N=16..NT instruction instead of a padded M=128 one).  Warp roles per CTA:
 //   warp 0      TMA producer: packed FP4 weight k-stages (128 rows x 128 B, 128-byte swizzle) and, per 64-wide
-//               k sub-tile, the bf16 route rows (already permuted into expert order) straight into the UMMA operand
+//               k sub-tile, the fp16 route rows (already permuted into expert order) straight into the UMMA operand
 //   warp 1      tcgen05.mma issuer (kind::f16), accumulators double-buffered in TMEM across tiles
 //   warps 2-5   epilogue: tcgen05.ld, then SwiGLU-with-clamp (GEMM1) or route-weight scaling (GEMM2)
-//   warps 6-13  operand builders: E2M1 nibbles -> bf16 * 2^(e8m0-127) written as the K-major 128B-swizzled
-//               UMMA A tile (generic-proxy stores + fence.proxy.async)
-// Numerics match the reference's Marlin path (python/minisgl/kernel/marlin_wna16.py:288-356): bf16 activations,
-// exact FP4 dequantisation, fp32 accumulation, GEMM1 output rounded to bf16 before the fp32 SwiGLU, GEMM2
+//   warps 6-21  operand builders: E2M1 nibbles -> fp16 * 2^(e8m0-127), stored with tcgen05.st as the UMMA A operand
+//               in tensor memory (a dequantised tile never touches shared memory, whose bandwidth it would exhaust)
+//   warp 22     TMA producer of the route rows
+//   warp 23     second tcgen05.mma issuer
+// Numerics match the reference's Marlin path (python/minisgl/kernel/marlin_wna16.py:288-356): bf16 activations
+// (held as fp16 for the tensor core: exact for |x| in [2^-14, 65504]), exact FP4 dequantisation, fp32 accumulation, GEMM1 output rounded to bf16 before the fp32 SwiGLU, GEMM2
 // output rounded to bf16 and multiplied by the bf16 route weight, routes summed afterwards.
 #include "comm.cuh"
 
 namespace {
 
 constexpr int kRowsTile = 128;
-constexpr int kPStages = 3;     // packed-weight stages (256 K elements each)
-constexpr int kOBufs = 2;       // bf16 operand buffers (64 K elements each)
-constexpr int kBuilders = 256;  // builder threads
-constexpr int kThreads = 64 + 128 + kBuilders;
+constexpr int kBuilders = 512;  // builder threads (two teams of 256)
+constexpr int kThreads = 64 + 128 + kBuilders + 64;  // + the route-row producer warp and the second MMA issuer
 
 struct PlanHeader {
   int num_tiles;
@@ -184,54 +184,99 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   }
 }
 
-// xs[pos] = x[route / topk]
+// xs[pos] = fp16(x[route / topk]): the grouped GEMMs run fp16 x fp16 (FP4 weights convert to fp16 in one instruction)
 __global__ void moe_permute_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs,
                                    const int* __restrict__ sorted_route, const PlanHeader* __restrict__ hdr, int topk,
                                    int h8) {
   const int pos = blockIdx.x;
   if (pos >= hdr->num_routes_local) return;
   const int tok = sorted_route[pos] / topk;
-  for (int i = threadIdx.x; i < h8; i += blockDim.x) xs[(size_t)pos * h8 + i] = x[(size_t)tok * h8 + i];
+  for (int i = threadIdx.x; i < h8; i += blockDim.x) {
+    const uint4 v = x[(size_t)tok * h8 + i];
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+    uint4 o;
+    __half2* hp = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) hp[j] = __float22half2_rn(__bfloat1622float2(b[j]));
+    xs[(size_t)pos * h8 + i] = o;
+  }
 }
 
-// ------------------------------------------------------------------ FP4 -> bf16 operand builder
-// 8 packed nibbles (one 32-bit word = elements 8c..8c+7, low nibble first) -> 8 bf16 scaled by 2^(sc-127).
-// A nibble s.e1e0.m placed at bf16 bits [8:6] (sign at 15) reads as value * 2^-126, so one packed multiply by
-// 2^(sc-1) yields the exact dequantised weight (sc is the e8m0 byte; sc <= 128 is required and checked on load).
+// ------------------------------------------------------------------ FP4 -> fp16 operand builder
+// 8 packed nibbles (one 32-bit word = elements 8c..8c+7, low nibble first) -> 8 fp16 scaled by 2^(sc-127), where sc
+// is the e8m0 scale byte of the 32-element group.  Scales in [103, 142] are exact; the loader rejects others.
 __device__ __forceinline__ uint4 dequant8(uint32_t w, uint32_t mul2) {
-  uint32_t r[4];
-  const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
-#pragma unroll
-  for (int p = 0; p < 4; ++p) {
-    // byte p of lo -> low half, byte p of hi -> high half
-    const uint32_t x = __byte_perm(lo, hi, 0x4040 + p + ((4 + p) << 8)) & 0x000F000Fu;  // [lo.bp, 0, hi.bp, 0]
-    const uint32_t bits = ((x & 0x00070007u) << 6) | ((x & 0x00080008u) << 12);
-    __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&bits);
-    const __nv_bfloat162 m = *reinterpret_cast<const __nv_bfloat162*>(&mul2);
-    v = __hmul2(v, m);
-    r[p] = *reinterpret_cast<uint32_t*>(&v);
-  }
-  return make_uint4(r[0], r[1], r[2], r[3]);
+  // Blackwell converts a byte holding two E2M1 values straight to an fp16 pair (low nibble -> low half); one packed
+  // multiply applies the group scale.  Both steps are exact.
+  uint32_t r0, r1, r2, r3;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+      : "r"(w));
+  const __half2 m = *reinterpret_cast<const __half2*>(&mul2);
+  __half2 v0 = __hmul2(*reinterpret_cast<__half2*>(&r0), m), v1 = __hmul2(*reinterpret_cast<__half2*>(&r1), m);
+  __half2 v2 = __hmul2(*reinterpret_cast<__half2*>(&r2), m), v3 = __hmul2(*reinterpret_cast<__half2*>(&r3), m);
+  return make_uint4(*reinterpret_cast<uint32_t*>(&v0), *reinterpret_cast<uint32_t*>(&v1),
+                    *reinterpret_cast<uint32_t*>(&v2), *reinterpret_cast<uint32_t*>(&v3));
+}
+// 32 packed nibbles (one 16-byte chunk) -> 32 fp16 in 16 registers, K order
+__device__ __forceinline__ void dequant8x4(const uint4& p, uint32_t mul2, uint32_t (&v)[16]) {
+  const uint4 a = dequant8(p.x, mul2), b = dequant8(p.y, mul2), c = dequant8(p.z, mul2), d = dequant8(p.w, mul2);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+  v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+  v[8] = c.x, v[9] = c.y, v[10] = c.z, v[11] = c.w;
+  v[12] = d.x, v[13] = d.y, v[14] = d.z, v[15] = d.w;
 }
 __device__ __forceinline__ uint32_t scale_mul2(uint32_t sc) {
-  // bf16 2^(sc-1): exponent field sc+126 (sc in [1,128]); sc == 0 -> 0
-  const uint32_t f = sc == 0 ? 0u : min(sc + 126u, 254u);
-  const uint32_t h = f << 7;
+  // fp16 pair holding 2^(sc-127): normal for sc in [113, 142], subnormal down to sc = 103, zero below
+  const int f = (int)sc - 112;
+  uint32_t h;
+  if (f >= 1)
+    h = (uint32_t)min(f, 30) << 10;
+  else
+    h = sc >= 103 ? (1u << (sc - 103)) : 0u;
   return h | (h << 16);
 }
+
 
 template <int MODE, int NT>
 struct MoeSmem {
   static constexpr int kMats = MODE == 1 ? 2 : 1;
-  static constexpr int kPackedBytes = kMats * kRowsTile * 128;  // per packed stage
-  static constexpr int kABytes = kRowsTile * 128;               // one bf16 operand sub-tile
-  static constexpr int kBBytes = NT * 128;
-  static constexpr int kOBytes = kMats * kABytes + kBBytes;
-  static constexpr int kTotal = kPStages * kPackedBytes + kOBufs * kOBytes + 1024 + 512;
+  static constexpr int kPackedBytes = kMats * kRowsTile * 128;  // per packed stage (256 K elements)
+  static constexpr int kBBytes = 2 * NT * 128;                  // route rows of one 128-wide K chunk (two swizzle atoms)
+  // A chunk (128 K elements, half a packed stage) is the unit handed from the builders to the MMA issuers.  Its
+  // dequantised weights live in tensor memory ([128 lanes x 128 fp16] = 64 columns per matrix); only the packed
+  // stages and the route rows use shared memory.  The packed ring keeps >= 64 KiB per SM in flight (HBM latency).
+  static constexpr int kPStages = MODE == 1 ? 4 : 8;
+  static constexpr int kOBufs = MODE == 1 ? (NT == 64 ? 2 : 3) : 4;
+  static constexpr int kTotal = kPStages * kPackedBytes + kOBufs * kBBytes + 1024 + 512;
+  static_assert(kTotal <= 227 * 1024, "shared memory budget");
+  // Two accumulators per tile in both modes (gate/up, or the even/odd chunks of GEMM2), one per MMA issuer, and
+  // two such pairs so that the epilogue of one tile overlaps the MMAs of the next.  NT = 64 is the widest tile for
+  // which this and the operand buffers fit the 512 columns.
+  static constexpr int kAccBufs = 2;
+  static_assert(NT == 32 || NT == 64, "route tile");
+  static constexpr int kAccCols = kAccBufs * 2 * NT;
+  static constexpr int kACols = kMats * 64;
+  static constexpr int kUsedCols = kAccCols + kOBufs * kACols;
+  static constexpr uint32_t kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128
+                                        : kUsedCols <= 256 ? 256 : 512;
+  static_assert(kUsedCols <= 512, "tensor memory budget");
 };
 
-// MODE 1: D_gate, D_up -> act[pos, j] = bf16(silu(min(g,L)) * clamp(u,+-L)), weights w13 [E, 2I, K/2].
+// MODE 1: D_gate, D_up -> act[pos, j] = fp16(bf16(silu(min(g,L)) * clamp(u,+-L))), weights w13 [E, 2I, K/2].
 // MODE 2: D -> out[route, h] = bf16(bf16(acc) * bf16(w_route)), weights w2 [E, H, K/2].
+//
+// Why this shape.  A tcgen05.mma with M = 128, K = 16 costs about 64 cycles whatever N <= 128 is (it streams the
+// 4 KiB A operand), so with a handful of routes per expert the tensor pipe, not HBM, bounds the kernel at 32 weight
+// elements per cycle per SM, and everything else has to hide behind it:
+//   * hand-offs happen in 128-element chunks, one tcgen05.commit per 8 MMAs of an issuer;
+//   * two issuer threads feed the pipe (GEMM1: gate and up matrix; GEMM2: even and odd chunks into two accumulators
+//     that the epilogue adds), so the per-chunk bookkeeping of one overlaps the MMAs of the other, and each polls the
+//     barrier of its next chunk while its last MMAs of the current one are still queueing;
+//   * every other waiting warp sleeps between polls (a polling warp takes issue slots from the issuers), and a warp
+//     makes one mbarrier arrival, not 32.
 template <int MODE, int NT>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -240,140 +285,159 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 __nv_bfloat16* __restrict__ out, int K, int rows_per_expert /*I (mode1) or H (mode2)*/,
                 int ld_out, float limit) {
   using S = MoeSmem<MODE, NT>;
-  constexpr int kMats = S::kMats;
-  constexpr uint32_t kTmemCols = 2 * kMats * NT < 32 ? 32 : 2 * kMats * NT;  // double-buffered accumulators
-  constexpr uint32_t kIdesc = umma_idesc(128, NT, 1, 1);
+  constexpr int kOBufs = S::kOBufs, kPStages = S::kPStages, kAccBufs = S::kAccBufs;
+  constexpr uint32_t kIdesc = umma_idesc(128, NT, 0, 0);  // fp16 x fp16 -> fp32
+  constexpr int kSleep = 64;                              // ns between polls of the non-critical waits
+  constexpr int kIssuerWarp1 = kThreads / 32 - 1, kRowProducerWarp = kThreads / 32 - 2;
+  constexpr bool kDual = true;  // two MMA issuer threads
   extern __shared__ uint8_t moe_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(moe_smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* packed = smem;
-  uint8_t* obuf = smem + kPStages * S::kPackedBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(obuf + kOBufs * S::kOBytes);
-  uint64_t* pfull = bars;               // [kPStages]
-  uint64_t* pempty = pfull + kPStages;  // [kPStages]
-  uint64_t* ofull = pempty + kPStages;  // [kOBufs]
-  uint64_t* oempty = ofull + kOBufs;    // [kOBufs]
-  uint64_t* tfull = oempty + kOBufs;    // [2]
-  uint64_t* tempty = tfull + 2;         // [2]
+  uint8_t* bbuf = smem + kPStages * S::kPackedBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bbuf + kOBufs * S::kBBytes);
+  uint64_t* pfull = bars;               // [kPStages]  packed stage landed
+  uint64_t* pempty = pfull + kPStages;  // [kPStages]  packed stage read by every builder warp
+  uint64_t* ofull = pempty + kPStages;  // [kOBufs]    chunk operands ready: weights in tensor memory + route rows landed
+  uint64_t* oempty = ofull + kOBufs;    // [kOBufs]    the chunk's MMAs retired
+  uint64_t* tfull = oempty + kOBufs;    // [2]         accumulators complete (one commit per issuer)
+  uint64_t* tempty = tfull + 2;         // [2]         accumulators drained by the epilogue
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_tiles = rows_per_expert / kRowsTile;
   const int kstages = K / 256;
+  const int nchunks = kstages * 2;
   const int scale_ld = K / 32;  // scale bytes per weight row
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kPStages; ++i) mbar_init(&pfull[i], 1), mbar_init(&pempty[i], kBuilders);
-    for (int i = 0; i < kOBufs; ++i) mbar_init(&ofull[i], kBuilders + 1), mbar_init(&oempty[i], 1);
-    for (int i = 0; i < 2; ++i) mbar_init(&tfull[i], 1), mbar_init(&tempty[i], 128);
+    for (int i = 0; i < kPStages; ++i) mbar_init(&pfull[i], 1), mbar_init(&pempty[i], kBuilders / 32);
+    for (int i = 0; i < kOBufs; ++i)
+      mbar_init(&ofull[i], kBuilders / 64 + 1), mbar_init(&oempty[i], (MODE == 1 && kDual) ? 2 : 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&tfull[i], kDual ? 2 : 1), mbar_init(&tempty[i], 4);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_alloc(tmem_holder, S::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  const uint32_t a_base = tmem_base + S::kAccCols;  // operand buffer b starts at column a_base + b * kACols
   const int total_work = hdr->num_tiles * row_tiles;
 
   if (warp == 0) {
-    if (lane == 0) {
-      int ps = 0, ob = 0;  // running packed-stage / operand-buffer counters
+    if (lane == 0) {  // packed weight stages
+      int ps = 0;
       for (int wk = blockIdx.x; wk < total_work; wk += gridDim.x) {
         const int ct = wk / row_tiles, rt = wk % row_tiles;
-        const int e = tiles[ct * 3], tok0 = tiles[ct * 3 + 1];
+        const int e = tiles[ct * 3];
         const int wrow = e * (MODE == 1 ? 2 * rows_per_expert : rows_per_expert) + rt * kRowsTile;
         bool ok = true;
-        for (int ks = 0; ks < kstages && ok; ++ks, ++ps) {
+        for (int ks = 0; ks < kstages; ++ks, ++ps) {
           const int s = ps % kPStages;
-          if (!mbar_wait(&pempty[s], ((ps / kPStages) & 1) ^ 1, abort_flag, 11)) { ok = false; break; }
+          if (!mbar_wait<kSleep>(&pempty[s], ((ps / kPStages) & 1) ^ 1, abort_flag, 11)) { ok = false; break; }
           mbar_expect_tx(&pfull[s], S::kPackedBytes);
           uint8_t* dst = packed + s * S::kPackedBytes;
           tma_load_2d(dst, &tmW, &pfull[s], ks * 128, wrow);
           if (MODE == 1) tma_load_2d(dst + kRowsTile * 128, &tmW, &pfull[s], ks * 128, wrow + rows_per_expert);
-          for (int q = 0; q < 4; ++q, ++ob) {
-            const int b = ob % kOBufs;
-            if (!mbar_wait(&oempty[b], ((ob / kOBufs) & 1) ^ 1, abort_flag, 12)) { ok = false; break; }
-            mbar_expect_tx(&ofull[b], S::kBBytes);
-            tma_load_2d(obuf + b * S::kOBytes + kMats * S::kABytes, &tmX, &ofull[b], ks * 256 + q * 64, tok0);
-          }
         }
         if (!ok) break;
       }
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      int ob = 0, it = 0;
-      for (int wk = blockIdx.x; wk < total_work; wk += gridDim.x, ++it) {
-        const int acc = it & 1;
-        if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag, 13)) break;
-        tc_fence_after();
-        const uint32_t d0 = tmem_base + acc * kMats * NT;
+  } else if (warp == kRowProducerWarp) {
+    if (lane == 0) {  // route rows (B operand) of one chunk: two 64-wide swizzle atoms
+      int ob = 0;
+      for (int wk = blockIdx.x; wk < total_work; wk += gridDim.x) {
+        const int tok0 = tiles[(wk / row_tiles) * 3 + 1];
         bool ok = true;
-        for (int sub = 0; sub < kstages * 4; ++sub, ++ob) {
+        for (int ch = 0; ch < nchunks; ++ch, ++ob) {
           const int b = ob % kOBufs;
-          if (!mbar_wait(&ofull[b], (ob / kOBufs) & 1, abort_flag, 14)) { ok = false; break; }
+          if (!mbar_wait<kSleep>(&oempty[b], ((ob / kOBufs) & 1) ^ 1, abort_flag, 12)) { ok = false; break; }
+          mbar_expect_tx(&ofull[b], S::kBBytes);
+          tma_load_2d(bbuf + b * S::kBBytes, &tmX, &ofull[b], ch * 128, tok0);
+          tma_load_2d(bbuf + b * S::kBBytes + NT * 128, &tmX, &ofull[b], ch * 128 + 64, tok0);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1 || (kDual && warp == kIssuerWarp1)) {
+    if (lane == 0) {
+      // MMA issuer `iss`.  GEMM1: every chunk, matrix iss.  GEMM2: the chunks of parity iss, accumulator iss.
+      const int iss = warp == 1 ? 0 : 1;
+      const int step = (MODE == 1 || !kDual) ? 1 : 2;
+      int it = 0;
+      long long ob0 = 0;  // global index of the work item's first chunk
+      bool ok = true;
+      for (int wk = blockIdx.x; wk < total_work && ok; wk += gridDim.x, ++it, ob0 += nchunks) {
+        const int acc = it % kAccBufs;
+        if (!mbar_wait(&tempty[acc], ((it / kAccBufs) & 1) ^ 1, abort_flag, 13)) break;
+        const uint32_t d = tmem_base + acc * 2 * NT + iss * NT;
+        const int ch0 = (MODE == 1 || !kDual) ? 0 : iss;
+        bool ready = false;
+        for (int ch = ch0; ch < nchunks; ch += step) {
+          const long long ob = ob0 + ch;
+          const int b = (int)(ob % kOBufs);
+          if (!ready && !mbar_wait(&ofull[b], (uint32_t)(ob / kOBufs) & 1, abort_flag, 14)) { ok = false; break; }
           tc_fence_after();
-          const uint8_t* a = obuf + b * S::kOBytes;
-          const uint8_t* bt = a + kMats * S::kABytes;
+          const uint32_t a = a_base + b * S::kACols + (MODE == 1 ? iss * 64 : 0);
+          const uint8_t* bt = bbuf + b * S::kBBytes;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t bd = umma_desc_k128(bt, k * 32);
-            umma_f16(d0, umma_desc_k128(a, k * 32), bd, kIdesc, (sub > 0 || k > 0));
-            if (MODE == 1) umma_f16(d0 + NT, umma_desc_k128(a + S::kABytes, k * 32), bd, kIdesc, (sub > 0 || k > 0));
+          for (int k = 0; k < 8; ++k) {
+            if (k == 6) {  // poll the next chunk's barrier while the last MMAs are still queueing
+              const long long obn = ob + step;
+              ready = ch + step < nchunks && mbar_try_wait(&ofull[obn % kOBufs], (uint32_t)(obn / kOBufs) & 1);
+            }
+            const uint64_t bd = umma_desc_k128(bt + (k >> 2) * (NT * 128), (k & 3) * 32);
+            umma_f16_ta(d, a + k * 8, bd, kIdesc, (ch > ch0 || k > 0));
+            if (MODE == 1 && !kDual) umma_f16_ta(d + NT, a + 64 + k * 8, bd, kIdesc, (ch > ch0 || k > 0));
           }
           umma_commit(&oempty[b]);
         }
-        if (!ok) break;
-        umma_commit(&tfull[acc]);
+        if (ok) umma_commit(&tfull[acc]);
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 6) {  // epilogue
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     int it = 0;
     for (int wk = blockIdx.x; wk < total_work; wk += gridDim.x, ++it) {
-      const int acc = it & 1;
+      const int acc = it % kAccBufs;
       const int ct = wk / row_tiles, rt = wk % row_tiles;
       const int tok0 = tiles[ct * 3 + 1], ntok = tiles[ct * 3 + 2];
-      if (!mbar_wait(&tfull[acc], (it >> 1) & 1, abort_flag, 15)) break;
+      if (!mbar_wait<256>(&tfull[acc], (it / kAccBufs) & 1, abort_flag, 15)) break;
       tc_fence_after();
-      const uint32_t d0 = lane_addr + acc * kMats * NT;
+      const uint32_t d0 = lane_addr + acc * 2 * NT;
       const int orow = rt * kRowsTile + r;  // intermediate index (mode 1) / hidden index (mode 2)
 #pragma unroll 1
-      for (int c0 = 0; c0 < NT; c0 += 32) {
+      for (int c0 = 0; c0 < NT; c0 += 16) {
         if (c0 >= ntok) break;
-        uint32_t g[32];
-        tmem_ld_32x32(d0 + c0, g);
-        if (MODE == 1) {
-          uint32_t u[32];
-          tmem_ld_32x32(d0 + NT + c0, u);
-          tmem_ld_wait();
+        uint32_t g[16], u[16];
+        tmem_ld_32x16(d0 + c0, g);
+        tmem_ld_32x16(d0 + NT + c0, u);
+        tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if (c0 + c < ntok) {
+        for (int c = 0; c < 16; ++c) {
+          if (c0 + c < ntok) {
+            if (MODE == 1) {
               float gv = bf2f(f2bf(__uint_as_float(g[c]))), uv = bf2f(f2bf(__uint_as_float(u[c])));
               if (limit > 0.f) {
                 gv = fminf(gv, limit);
                 uv = fminf(fmaxf(uv, -limit), limit);
               }
               const float a = gv / (1.f + expf(-gv)) * uv;
-              out[(size_t)(tok0 + c0 + c) * ld_out + orow] = f2bf(a);
-            }
-          }
-        } else {
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if (c0 + c < ntok) {
+              // bf16 rounding of the activation, held as fp16 for the second GEMM's operand
+              reinterpret_cast<__half*>(out)[(size_t)(tok0 + c0 + c) * ld_out + orow] =
+                  __float2half_rn(bf2f(f2bf(a)));
+            } else {
               const int pos = tok0 + c0 + c;
-              const __nv_bfloat16 y = f2bf(__uint_as_float(g[c]));
+              const __nv_bfloat16 y = f2bf(kDual ? __uint_as_float(g[c]) + __uint_as_float(u[c]) : __uint_as_float(g[c]));
               const __nv_bfloat16 wv = f2bf(sorted_w[pos]);
               out[(size_t)sorted_route[pos] * ld_out + orow] = __hmul(y, wv);
             }
@@ -381,53 +445,82 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         }
       }
       tc_fence_before();
-      mbar_arrive(&tempty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);  // one arrival per warp: arrivals on one barrier serialise
     }
-  } else {
-    // builders: thread b -> weight row (b % 128); MODE 1: matrix b / 128, all 4 sub-tiles of a stage;
-    // MODE 2: sub-tiles {2*(b/128), 2*(b/128)+1}
-    const int bt = threadIdx.x - 192;
-    const int r = bt & 127, half = bt >> 7;
-    int ps = 0, ob = 0;
-    for (int wk = blockIdx.x; wk < total_work; wk += gridDim.x) {
+  } else if (warp < 6 + kBuilders / 32) {
+    // builders: two teams of 8 warps; team t dequantises the chunks of parity t (chunk t of every packed stage), so
+    // one team builds while the other waits for its buffer.  A warp writes the tensor-memory lanes of its own
+    // quarter (warp % 4), so a thread covers weight row (warp % 4) * 32 + lane and, by the warp's position in the
+    // team, MODE 1: the chunk's 128 K elements of the gate (first four warps) or up matrix; MODE 2: the first or
+    // second 64 K elements of the chunk.
+    const int j = (warp - 6) & 7, team = (warp - 6) >> 3;
+    const int quarter = warp & 3, half = j >> 2;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = a_base + ((uint32_t)(quarter * 32) << 16);
+    const size_t expert_rows = MODE == 1 ? 2 * (size_t)rows_per_expert : (size_t)rows_per_expert;
+    auto scale_row = [&](int wk) -> const uint8_t* {
       const int ct = wk / row_tiles, rt = wk % row_tiles;
-      const int e = tiles[ct * 3];
-      const size_t wrow = (size_t)e * (MODE == 1 ? 2 * rows_per_expert : rows_per_expert) + rt * kRowsTile + r +
-                          (MODE == 1 ? half * rows_per_expert : 0);
-      const uint8_t* srow = scales + wrow * scale_ld;
+      const size_t wrow = (size_t)tiles[ct * 3] * expert_rows + rt * kRowsTile + r +
+                          (MODE == 1 ? (size_t)half * rows_per_expert : 0);
+      return scales + wrow * scale_ld;
+    };
+    long long ps = 0;
+    int wk = blockIdx.x;
+    const uint8_t* srow = wk < total_work ? scale_row(wk) : nullptr;
+    // the 4 scale bytes of this team's chunk are fetched one stage ahead: they come from HBM
+    uint32_t scn = srow ? __ldg(reinterpret_cast<const uint32_t*>(srow + team * 4)) : 0u;
+    for (; wk < total_work; wk += gridDim.x) {
+      const int wk_next = wk + gridDim.x;
+      const uint8_t* srow_next = wk_next < total_work ? scale_row(wk_next) : nullptr;
       bool ok = true;
-      for (int ks = 0; ks < kstages && ok; ++ks, ++ps) {
-        const int s = ps % kPStages;
-        const uint2 scv = *reinterpret_cast<const uint2*>(srow + ks * 8);  // 8 scale bytes: 2 per sub-tile
-        if (!mbar_wait(&pfull[s], (ps / kPStages) & 1, abort_flag, 16)) { ok = false; break; }
+      for (int ks = 0; ks < kstages; ++ks, ++ps) {
+        const int s = (int)(ps % kPStages);
+        const uint32_t sw = scn;
+        if (ks + 1 < kstages)
+          scn = __ldg(reinterpret_cast<const uint32_t*>(srow + (ks + 1) * 8 + team * 4));
+        else if (srow_next)
+          scn = __ldg(reinterpret_cast<const uint32_t*>(srow_next + team * 4));
+        if (!mbar_wait<kSleep>(&pfull[s], (uint32_t)(ps / kPStages) & 1, abort_flag, 16)) { ok = false; break; }
+        // chunk `team` of the stage = bytes [64 team, 64 team + 64) of the 128-byte packed row = 16-byte pieces
+        // 4 team .. 4 team + 3 (swizzled by row), one scale byte each
         const uint8_t* prow = packed + s * S::kPackedBytes + (MODE == 1 ? half * kRowsTile * 128 : 0) + r * 128;
-        for (int q = 0; q < 4; ++q, ++ob) {
-          const int b = ob % kOBufs;
-          if (!mbar_wait(&oempty[b], ((ob / kOBufs) & 1) ^ 1, abort_flag, 17)) { ok = false; break; }
-          if (MODE == 1 || (q >> 1) == half) {
-            const uint32_t sw = q < 2 ? scv.x : scv.y;
-            const uint32_t m0 = scale_mul2((sw >> ((q & 1) * 16)) & 0xff);
-            const uint32_t m1 = scale_mul2((sw >> ((q & 1) * 16 + 8)) & 0xff);
-            // packed sub-tile q = bytes [32q, 32q+32) of the 128-byte row = 16B chunks 2q, 2q+1 (swizzled by row)
-            const uint4 p0 = *reinterpret_cast<const uint4*>(prow + (((2 * q) ^ (r & 7)) << 4));
-            const uint4 p1 = *reinterpret_cast<const uint4*>(prow + (((2 * q + 1) ^ (r & 7)) << 4));
-            uint8_t* arow = obuf + b * S::kOBytes + (MODE == 1 ? half * S::kABytes : 0) + r * 128;
-            const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        constexpr int kPieces = MODE == 1 ? 4 : 2;
+        const int piece0 = team * 4 + (MODE == 1 ? 0 : half * 2);
+        uint4 p[kPieces];
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-              *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = dequant8(w[c], c < 4 ? m0 : m1);
-          }
-          fence_proxy_async_smem();
-          mbar_arrive(&ofull[b]);
+        for (int i = 0; i < kPieces; ++i)
+          p[i] = *reinterpret_cast<const uint4*>(prow + (((piece0 + i) ^ (r & 7)) << 4));
+        const long long ob = ps * 2 + team;
+        const int b = (int)(ob % kOBufs);
+        if (!mbar_wait<kSleep>(&oempty[b], ((uint32_t)(ob / kOBufs) & 1) ^ 1, abort_flag, 17)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t dst = lane_addr + b * S::kACols + (MODE == 1 ? half * 64 : half * 32);
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+          const uint32_t sc = (sw >> (8 * ((MODE == 1 ? 0 : half * 2) + i))) & 0xff;
+          uint32_t v[16];
+          dequant8x4(p[i], scale_mul2(sc), v);
+          tmem_st_32x16(dst + i * 16, v);
         }
-        if (ok) mbar_arrive(&pempty[s]);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&ofull[b]);
+          // Release the packed stage only now, after its bytes were consumed by real instructions.  Releasing it
+          // right after the loads were issued produced wrong sums: an arrival does not wait for loads whose results
+          // nobody has used yet.
+          mbar_arrive(&pempty[s]);
+        }
       }
       if (!ok) break;
+      srow = srow_next;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) tmem_dealloc(tmem_base, S::kTmemCols);
 }
 
 // out[t] = bf16( float(bf16(sum_k local route rows)) + float(shared[t]) ); rows >= num_valid -> 0
@@ -591,9 +684,9 @@ DSV4_API int dsv4_moe_gemm(int mode, int nt, const void* w, const void* scales, 
   return launch_moe_gemm<M, N>(w, sc, x, x_rows, hdr, tiles, sorted_route, sorted_w, out, e_local, K,           \
                                rows_per_expert, ld_out, limit, num_sms, st)
   if (mode == 1 && nt == 32) MOE_LAUNCH(1, 32);
-  if (mode == 1 && nt == 128) MOE_LAUNCH(1, 128);
+  if (mode == 1 && nt == 64) MOE_LAUNCH(1, 64);
   if (mode == 2 && nt == 32) MOE_LAUNCH(2, 32);
-  if (mode == 2 && nt == 128) MOE_LAUNCH(2, 128);
+  if (mode == 2 && nt == 64) MOE_LAUNCH(2, 64);
 #undef MOE_LAUNCH
   return 221;
 }

@@ -234,14 +234,14 @@ def moe_routed(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
     routes = t * topk
     e_local, two_i = w13.shape[0], w13.shape[1]
     inter = two_i // 2
-    nt = 32 if routes <= 32 * e_local else 128
+    nt = 32 if routes <= 32 * e_local else 64
     max_tiles = min(e_local, routes) + routes // nt + 1
     plan = torch.empty(4 + 3 * max_tiles + 3 * routes, dtype=torch.int32, device=y.device)
     nv.call("moe_plan", nv.ptr(idx), nv.ptr(w), I(routes), I(e_local), I(expert_base), I(nt), nv.ptr(plan),
             I(max_tiles))
-    xs = torch.empty(routes, h, dtype=y.dtype, device=y.device)
+    xs = torch.empty(routes, h, dtype=torch.float16, device=y.device)
     nv.call("moe_permute", nv.ptr(y), nv.ptr(xs), nv.ptr(plan), I(routes), I(max_tiles), I(topk), I(h))
-    act = torch.empty(routes, inter, dtype=y.dtype, device=y.device)
+    act = torch.empty(routes, inter, dtype=torch.float16, device=y.device)
     sms = num_sms(y.device)
     nv.call("moe_gemm", I(1), I(nt), nv.ptr(w13), nv.ptr(s13), nv.ptr(xs), I(routes), nv.ptr(plan), I(routes),
             I(max_tiles), nv.ptr(act), I(e_local), I(h), I(inter), I(inter), F(limit or 0.0), I(sms))
