@@ -87,6 +87,7 @@ struct AttnCfg {
 
 template <int HL>
 __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnArgs a) {
+  pdl_entry();
   using C = AttnCfg<HL>;
   constexpr int HP = C::HP, MT = C::MT, G = C::G, KT = C::KT, NT = C::NT, TPR = C::TPR, PCH = C::PCH;
   constexpr int NTHR = C::NW * 32;
@@ -285,7 +286,7 @@ int launch_attn(const AttnArgs& a, int t, cudaStream_t st) {
       return 301;
     set = true;
   }
-  sparse_attn_kernel<HL><<<t, C::NW * 32, C::SMEM, st>>>(a);
+  dsv4_launch(sparse_attn_kernel<HL>, t, C::NW * 32, C::SMEM, st, a);
   return (int)cudaGetLastError();
 }
 

@@ -8,6 +8,7 @@ namespace {
 
 __global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
                                                         int rows, int cols, const CommCtx comm) {
+  pdl_entry();
   __shared__ int ok;
   const uint32_t epoch = comm_epoch(comm);
   const int parity = epoch & 1;
@@ -34,6 +35,7 @@ __global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __r
 // A wait that nothing satisfies: used by the failure-detection test to show that a missing peer ends in an error
 // status (DSV4_ERR_PEER_TIMEOUT) within `limit_ns`, with the context still usable.  It polls a LOCAL flag.
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, unsigned long long limit_ns, int* result) {
+  pdl_entry();
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
     if (ld_acquire_sys(flag) == want) {
@@ -63,11 +65,11 @@ DSV4_API int dsv4_allreduce(const void* x, void* out, int rows, int cols, const 
   if (cols % 8) return 500;
   if ((long long)rows * cols * 2 > comm->data_bytes) return 501;
   int grid = rows < 1024 ? rows : 1024;
-  allreduce_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, cols, *comm);
+  dsv4_launch(allreduce_kernel, grid, 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, cols, *comm);
   return (int)cudaGetLastError();
 }
 
 DSV4_API int dsv4_wait_flag(const void* flag, unsigned want, long long limit_ns, int* result, cudaStream_t st) {
-  wait_flag_kernel<<<1, 1, 0, st>>>((const uint32_t*)flag, want, (unsigned long long)limit_ns, result);
+  dsv4_launch(wait_flag_kernel, 1, 1, 0, st, (const uint32_t*)flag, want, (unsigned long long)limit_ns, result);
   return (int)cudaGetLastError();
 }

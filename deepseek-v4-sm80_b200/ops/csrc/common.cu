@@ -1,6 +1,8 @@
 // Library-wide state: the device status word, tensor-map encoding, version probe.
 #include "common.cuh"
 
+#include <cstdlib>
+
 #include <stdio.h>
 #include <string.h>
 
@@ -51,6 +53,14 @@ DSV4_API int dsv4_read_status(int* host_out, int clear) {
     e = cudaMemcpyToSymbol(g_dsv4_status, z, sizeof(z));
   }
   return (int)e;
+}
+
+bool dsv4_pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("DSV4_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 DSV4_API int dsv4_abi_version() { return 1; }

@@ -100,6 +100,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of this library is launched with the programmatic-stream-serialization attribute: it may start while
+// the kernel before it in the stream is still draining, which hides launch latency and the prologue (barrier
+// init, tensor-memory allocation).  pdl_wait() blocks until every earlier kernel has completed and its memory is
+// visible; no kernel touches global memory before it.  pdl_launch_dependents() lets the next kernel start early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_entry() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int x, int y) {
   asm volatile(
@@ -243,6 +255,24 @@ __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float
 __device__ __forceinline__ __nv_bfloat16 f2bf(float v) { return __float2bfloat16_rn(v); }
 
 // host side -----------------------------------------------------------------
+// Launches `kernel` with programmatic dependent launch allowed (set DSV4_PDL=0 in the environment to launch plainly).
+bool dsv4_pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t dsv4_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                               Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dsv4_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Encodes a 2-D row-major tensor map (inner = contiguous dimension) with the given box and swizzle.
 // Returns 0 on success.  elem: 0 = uint8, 1 = bf16, 2 = fp32.  swizzle: 0 = none, 3 = 128 B.
 int dsv4_make_tmap_2d(CUtensorMap* out, const void* base, int elem, uint64_t inner, uint64_t outer,

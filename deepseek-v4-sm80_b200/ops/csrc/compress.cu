@@ -25,6 +25,7 @@ __global__ void compress_pool4_kernel(const float* __restrict__ proj, const int*
                                       const int* __restrict__ slots, const int* __restrict__ page_table, int ld_pt,
                                       const float* __restrict__ ring, const float* __restrict__ ckpt,
                                       const float* __restrict__ ape, float* __restrict__ out, int d, int ps) {
+  pdl_entry();
   const int row = blockIdx.x;
   const int p = pos[row], s = slots[row];
   const int w4 = 4 * d;
@@ -75,6 +76,7 @@ __global__ void compress_pool4_kernel(const float* __restrict__ proj, const int*
 __global__ void compress_state4_kernel(const float* __restrict__ proj, const int* __restrict__ pos,
                                        const int* __restrict__ slots, const int* __restrict__ page_table, int ld_pt,
                                        float* __restrict__ ring, float* __restrict__ ckpt, int d, int ps, int t_rows) {
+  pdl_entry();
   const int row = blockIdx.x;
   const int p = pos[row], s = slots[row];
   const int w4 = 4 * d;
@@ -99,6 +101,7 @@ __global__ void compress_state4_kernel(const float* __restrict__ proj, const int
 __global__ void compress_pool128_kernel(const float* __restrict__ proj, const int* __restrict__ pos,
                                         const int* __restrict__ slots, const float* __restrict__ ring,
                                         const float* __restrict__ ape, float* __restrict__ out, int d, int ratio) {
+  pdl_entry();
   const int row = blockIdx.x;
   const int p = pos[row], s = slots[row];
   const int w2 = 2 * d;
@@ -152,6 +155,7 @@ __global__ void compress_pool128_kernel(const float* __restrict__ proj, const in
 __global__ void compress_state128_kernel(const float* __restrict__ proj, const int* __restrict__ pos,
                                          const int* __restrict__ slots, const float* __restrict__ ape,
                                          float* __restrict__ ring, int d, int ratio, int t_rows) {
+  pdl_entry();
   const int row = blockIdx.x;
   const int p = pos[row], s = slots[row];
   const int later = row + ratio;
@@ -172,6 +176,7 @@ __global__ void __launch_bounds__(128) compress_store_kernel(const float* __rest
                                                              const __nv_bfloat16* __restrict__ w, float eps,
                                                              RopeParams rp, __nv_bfloat16* __restrict__ cache, int ps,
                                                              int ratio) {
+  pdl_entry();
   constexpr int D = 512;
   __shared__ float sh[4];
   const int row = blockIdx.x, tid = threadIdx.x;
@@ -214,6 +219,7 @@ __global__ void indexer_kv_store_kernel(const float* __restrict__ pooled, const 
                                         const int* __restrict__ out_loc, const float* __restrict__ w, float eps,
                                         RopeParams rp, uint8_t* __restrict__ vals, float* __restrict__ scales, int ps,
                                         int t_rows) {
+  pdl_entry();
   constexpr int D = 128;
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (row >= t_rows) return;
@@ -275,6 +281,7 @@ __global__ void indexer_kv_store_kernel(const float* __restrict__ pooled, const 
 __global__ void indexer_q_encode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ wts,
                                         const int* __restrict__ pos, RopeParams rp, float fold,
                                         uint8_t* __restrict__ codes, float* __restrict__ wout, int heads, int rows) {
+  pdl_entry();
   constexpr int D = 128;
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -321,10 +328,10 @@ DSV4_API int dsv4_compress_pool(const float* proj, const int* pos, const int* sl
                                 int ratio, int ps, cudaStream_t st) {
   if (t <= 0) return 0;
   if (ratio == 4)
-    compress_pool4_kernel<<<t, d < 256 ? d : 256, 0, st>>>(proj, pos, slots, page_table, ld_pt, ring, ckpt, ape, out, d,
+    dsv4_launch(compress_pool4_kernel, t, d < 256 ? d : 256, 0, st, proj, pos, slots, page_table, ld_pt, ring, ckpt, ape, out, d,
                                                           ps);
   else
-    compress_pool128_kernel<<<t, d < 256 ? d : 256, ratio * sizeof(int), st>>>(proj, pos, slots, ring, ape, out, d,
+    dsv4_launch(compress_pool128_kernel, t, d < 256 ? d : 256, ratio * sizeof(int), st, proj, pos, slots, ring, ape, out, d,
                                                                               ratio);
   return (int)cudaGetLastError();
 }
@@ -333,16 +340,16 @@ DSV4_API int dsv4_compress_state(const float* proj, const int* pos, const int* s
                                  cudaStream_t st) {
   if (t <= 0) return 0;
   if (ratio == 4)
-    compress_state4_kernel<<<t, 256, 0, st>>>(proj, pos, slots, page_table, ld_pt, ring, ckpt, d, ps, t);
+    dsv4_launch(compress_state4_kernel, t, 256, 0, st, proj, pos, slots, page_table, ld_pt, ring, ckpt, d, ps, t);
   else
-    compress_state128_kernel<<<t, 256, 0, st>>>(proj, pos, slots, ape, ring, d, ratio, t);
+    dsv4_launch(compress_state128_kernel, t, 256, 0, st, proj, pos, slots, ape, ring, d, ratio, t);
   return (int)cudaGetLastError();
 }
 DSV4_API int dsv4_compress_store(const float* pooled, const int* pos, const int* out_loc, const void* w, float eps,
                                  RopeParams rp, void* cache, int t, int d, int ps, int ratio, cudaStream_t st) {
   if (t <= 0) return 0;
   if (d != 512 || rp.rotary_dim != 64) return 140;
-  compress_store_kernel<<<t, 128, 0, st>>>(pooled, pos, out_loc, (const __nv_bfloat16*)w, eps, rp,
+  dsv4_launch(compress_store_kernel, t, 128, 0, st, pooled, pos, out_loc, (const __nv_bfloat16*)w, eps, rp,
                                            (__nv_bfloat16*)cache, ps, ratio);
   return (int)cudaGetLastError();
 }
@@ -350,7 +357,7 @@ DSV4_API int dsv4_indexer_kv_store(const float* pooled, const int* pos, const in
                                    RopeParams rp, void* vals, float* scales, int t, int d, int ps, cudaStream_t st) {
   if (t <= 0) return 0;
   if (d != 128 || rp.rotary_dim != 64) return 141;
-  indexer_kv_store_kernel<<<(t * 32 + 255) / 256, 256, 0, st>>>(pooled, pos, out_loc, w, eps, rp, (uint8_t*)vals, scales,
+  dsv4_launch(indexer_kv_store_kernel, (t * 32 + 255) / 256, 256, 0, st, pooled, pos, out_loc, w, eps, rp, (uint8_t*)vals, scales,
                                                                ps, t);
   return (int)cudaGetLastError();
 }
@@ -359,7 +366,7 @@ DSV4_API int dsv4_indexer_q_encode(const void* q, const void* wts, const int* po
   if (t <= 0) return 0;
   if (d != 128 || rp.rotary_dim != 64) return 142;
   const int rows = t * heads;
-  indexer_q_encode_kernel<<<(rows * 32 + 255) / 256, 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)wts,
+  dsv4_launch(indexer_q_encode_kernel, (rows * 32 + 255) / 256, 256, 0, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)wts,
                                                                   pos, rp, fold, (uint8_t*)codes, wout, heads, rows);
   return (int)cudaGetLastError();
 }

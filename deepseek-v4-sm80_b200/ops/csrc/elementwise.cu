@@ -30,6 +30,7 @@ __device__ __forceinline__ float block_max(float v, float* sh) {
 // ------------------------------------------------------------------ embedding
 __global__ void embed_kernel(const int* __restrict__ ids, const uint4* __restrict__ w, uint4* __restrict__ out, int m,
                              int h8) {
+  pdl_entry();
   const int t = blockIdx.x;
   const uint4* src = w + (size_t)ids[t] * h8;
   for (int i = threadIdx.x; i < h8; i += blockDim.x) {
@@ -42,6 +43,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const uint4* __restric
 __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
                                                        const __nv_bfloat16* __restrict__ w,
                                                        __nv_bfloat16* __restrict__ out, int ldo, int d, float eps) {
+  pdl_entry();
   __shared__ float sh[32];
   const int row = blockIdx.x;
   const __nv_bfloat16* xr = x + (size_t)row * ldx;
@@ -99,6 +101,7 @@ __device__ __forceinline__ float pow2_ceil_scale(float amax) {
 template <int BLOCK>
 __global__ void fp8_quant_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ q,
                                  float* __restrict__ s, int rows, int k) {
+  pdl_entry();
   constexpr int PER = BLOCK / 32;  // elements per lane: 4 (128) or 2 (64)
   const int nb = k / BLOCK;
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -135,6 +138,7 @@ __global__ void fp8_quant_kernel(const __nv_bfloat16* __restrict__ x, int ldx, u
 // ------------------------------------------------------------------ SwiGLU with clamp: [T,2I] -> [T,I]
 __global__ void silu_mul_clamp_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows,
                                       int inter, float limit) {
+  pdl_entry();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t total = (size_t)rows * inter / 2;
   if (idx >= total) return;
@@ -156,6 +160,7 @@ __global__ void silu_mul_clamp_kernel(const __nv_bfloat16* __restrict__ gu, __nv
 // ------------------------------------------------------------------ out = bf16(float(a) + float(b)); padded rows -> 0
 __global__ void add_cast_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                                 __nv_bfloat16* __restrict__ out, int rows, int h, const int* __restrict__ num_valid) {
+  pdl_entry();
   const size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (idx >= (size_t)rows * h) return;
   const int row = (int)(idx / h);
@@ -177,6 +182,7 @@ __global__ void add_cast_kernel(const __nv_bfloat16* __restrict__ a, const __nv_
 // ------------------------------------------------------------------ RoPE on the last R dims of [rows, D] (in place)
 __global__ void rope_tail_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ pos, int heads, int d,
                                  RopeParams rp, int inverse, int pos_offset) {
+  pdl_entry();
   const int row = blockIdx.x;
   const int pair = threadIdx.x;
   if (pair >= rp.rotary_dim / 2) return;
@@ -195,6 +201,7 @@ __global__ void __launch_bounds__(128) q_kv_norm_rope_store_kernel(
     __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ kv, int ldkv, const int* __restrict__ pos,
     const __nv_bfloat16* __restrict__ kvw, float eps, RopeParams rp, __nv_bfloat16* __restrict__ swa,
     const int* __restrict__ out_loc, const int* __restrict__ swa_map, int ps, int t_rows, int heads, int qat) {
+  pdl_entry();
   constexpr int D = 512;
   __shared__ float sh[32];
   const int tid = threadIdx.x;
@@ -267,6 +274,7 @@ __global__ void __launch_bounds__(128) q_kv_norm_rope_store_kernel(
 // ------------------------------------------------------------------ argmax over fp32 rows (lowest index wins ties)
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, long long* __restrict__ out,
                                                       int v) {
+  pdl_entry();
   __shared__ float sv[32];
   __shared__ int si[32];
   const float* row = logits + (size_t)blockIdx.x * v;
@@ -302,14 +310,14 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 DSV4_API int dsv4_embed(const int* ids, const void* w, void* out, int t, int m, int h, cudaStream_t st) {
   if (t <= 0) return 0;
   if (h % 8) return 120;
-  embed_kernel<<<t, 256, 0, st>>>(ids, (const uint4*)w, (uint4*)out, m, h / 8);
+  dsv4_launch(embed_kernel, t, 256, 0, st, ids, (const uint4*)w, (uint4*)out, m, h / 8);
   return (int)cudaGetLastError();
 }
 DSV4_API int dsv4_rms_norm(const void* x, int ldx, const void* w, void* out, int ldo, int rows, int d, float eps,
                            cudaStream_t st) {
   if (rows <= 0) return 0;
   if (d % 8 || d > 8192 || ldx % 8 || ldo % 8) return 121;
-  rms_norm_kernel<<<rows, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo,
+  dsv4_launch(rms_norm_kernel, rows, 256, 0, st, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo,
                                         d, eps);
   return (int)cudaGetLastError();
 }
@@ -319,16 +327,16 @@ DSV4_API int dsv4_fp8_quant(const void* x, int ldx, void* q, float* s, int rows,
   const long long warps = (long long)rows * (k / block);
   const int blocks = (int)((warps * 32 + 255) / 256);
   if (block == 128)
-    fp8_quant_kernel<128><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, s, rows, k);
+    dsv4_launch(fp8_quant_kernel<128>, blocks, 256, 0, st, (const __nv_bfloat16*)x, ldx, (uint8_t*)q, s, rows, k);
   else
-    fp8_quant_kernel<64><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, s, rows, k);
+    dsv4_launch(fp8_quant_kernel<64>, blocks, 256, 0, st, (const __nv_bfloat16*)x, ldx, (uint8_t*)q, s, rows, k);
   return (int)cudaGetLastError();
 }
 DSV4_API int dsv4_silu_mul_clamp(const void* gu, void* out, int rows, int inter, float limit, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (inter % 2) return 123;
   const size_t total = (size_t)rows * inter / 2;
-  silu_mul_clamp_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+  dsv4_launch(silu_mul_clamp_kernel, (unsigned)((total + 255) / 256), 256, 0, st, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
                                                                         rows, inter, limit);
   return (int)cudaGetLastError();
 }
@@ -337,7 +345,7 @@ DSV4_API int dsv4_add_cast(const void* a, const void* b, void* out, int rows, in
   if (rows <= 0) return 0;
   if (h % 8) return 124;
   const size_t total = (size_t)rows * h / 8;
-  add_cast_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+  dsv4_launch(add_cast_kernel, (unsigned)((total + 255) / 256), 256, 0, st, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
                                                                   (__nv_bfloat16*)out, rows, h, num_valid);
   return (int)cudaGetLastError();
 }
@@ -345,7 +353,7 @@ DSV4_API int dsv4_rope_tail(void* x, const int* pos, int rows, int heads, int d,
                             int pos_offset, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (rp.rotary_dim > 128 || rp.rotary_dim % 2) return 125;
-  rope_tail_kernel<<<rows, 64, 0, st>>>((__nv_bfloat16*)x, pos, heads, d, rp, inverse, pos_offset);
+  dsv4_launch(rope_tail_kernel, rows, 64, 0, st, (__nv_bfloat16*)x, pos, heads, d, rp, inverse, pos_offset);
   return (int)cudaGetLastError();
 }
 DSV4_API int dsv4_q_kv_norm_rope_store(void* q, void* kv, int ldkv, const int* pos, const void* kvw, float eps,
@@ -353,13 +361,13 @@ DSV4_API int dsv4_q_kv_norm_rope_store(void* q, void* kv, int ldkv, const int* p
                                        int heads, int d, int qat, cudaStream_t st) {
   if (t <= 0) return 0;
   if (d != 512 || rp.rotary_dim != 64 || ldkv % 4) return 126;
-  q_kv_norm_rope_store_kernel<<<t * heads + t, 128, 0, st>>>((__nv_bfloat16*)q, (__nv_bfloat16*)kv, ldkv, pos,
+  dsv4_launch(q_kv_norm_rope_store_kernel, t * heads + t, 128, 0, st, (__nv_bfloat16*)q, (__nv_bfloat16*)kv, ldkv, pos,
                                                             (const __nv_bfloat16*)kvw, eps, rp, (__nv_bfloat16*)swa,
                                                             out_loc, swa_map, ps, t, heads, qat);
   return (int)cudaGetLastError();
 }
 DSV4_API int dsv4_argmax(const float* logits, long long* out, int rows, int v, cudaStream_t st) {
   if (rows <= 0) return 0;
-  argmax_kernel<<<rows, 1024, 0, st>>>(logits, out, v);
+  dsv4_launch(argmax_kernel, rows, 1024, 0, st, logits, out, v);
   return (int)cudaGetLastError();
 }

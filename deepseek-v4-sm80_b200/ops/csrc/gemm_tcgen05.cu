@@ -45,6 +45,8 @@ struct GemmArgs {
   int splits;
   float* ws;           // [tiles][splits][128][BN] fp32 partials
   int* counters;       // [tiles], zero between launches
+  long long partial_stride;  // > 0: split s writes its own partial product to out + s * partial_stride (no reduction;
+                             //      the consumer kernel sums the splits in order)
 };
 
 __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const float* v, int ncols_valid) {
@@ -84,6 +86,7 @@ template <int BN, bool FP8, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ out,
                const GemmArgs g, const CommCtx comm) {
+  pdl_launch_dependents();
   using Cfg = GemmCfg<BN>;
   constexpr int S = Cfg::kStages;
   constexpr int BK = FP8 ? 128 : 64;  // elements per k-tile (= 128 bytes)
@@ -132,6 +135,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
+  pdl_wait();  // barriers and tensor memory are set up; from here on the kernel touches global memory
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -141,7 +145,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int i = 0; i < nkt; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, 1)) break;
+        if (!mbar_wait<32>(&empty[s], ph ^ 1, abort_flag, 1)) break;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
         uint8_t* a = tiles + s * Cfg::kStageBytes;
         tma_load_2d(a, &tmA, &full[s], ax + (kt0 + i) * BK, m0);
@@ -186,7 +190,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const bool fused = comm.world > 1;
     uint32_t epoch = 0;
-    OutT* part = out + (size_t)batch * g.out_col_pb;
+    OutT* part = out + (size_t)batch * g.out_col_pb + (g.partial_stride > 0 ? (size_t)split * g.partial_stride : 0);
     int ld_part = g.ldo;
     if (fused) {
       epoch = comm_epoch(comm);
@@ -199,7 +203,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     if (!FP8) {
       if (nkt > 0) {
-        ok = mbar_wait(&tfull[0], 0, abort_flag, 4);
+        ok = mbar_wait<64>(&tfull[0], 0, abort_flag, 4);
         tc_fence_after();
         if (ok) {
 #pragma unroll
@@ -237,7 +241,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     bool write_out = ok;
-    if (g.splits > 1) {
+    if (g.splits > 1 && g.partial_stride == 0) {
       // publish this split's fp32 partial, the last split to arrive reduces all of them in split order
       const int tile = (batch * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
       float* wsp = g.ws + (((size_t)tile * g.splits + split) * kBM + row) * BN;
@@ -311,6 +315,7 @@ struct LaunchOpts {
   int batches = 1, a_col_pb = 0, b_row_pb = 0, out_col_pb = 0;
   int splits = 1;
   float* ws = nullptr;
+  long long partial_stride = 0;
   int* counters = nullptr;
   int a_cols = 0, b_rows = 0;  // full extents of the operands (0 = K / N)
   int sb_ld = 0;
@@ -341,8 +346,8 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
     if ((long long)grid.x * grid.y > kCommSlots || o.splits != 1 || o.batches != 1) return 104;
   }
   GemmArgs g{M, N, K, ldo, sa, sb, o.sb_ld ? o.sb_ld : (K + 127) / 128, accumulate_out, o.a_col_pb, o.b_row_pb,
-             o.out_col_pb, o.splits, o.ws, o.counters};
-  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, g, comm);
+             o.out_col_pb, o.splits, o.ws, o.counters, o.partial_stride};
+  dsv4_launch(kern, grid, 192, Cfg::kSmemBytes, stream, tmA, tmB, out, g, comm);
   return (int)cudaGetLastError();
 }
 
@@ -396,6 +401,19 @@ DSV4_API int dsv4_gemm_bf16(const void* x, const void* w, void* out, int M, int 
                                      stream, o);
   return dispatch_bn<false, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, nullptr, nullptr,
                                            accumulate_out, bn, stream, o);
+}
+
+// Split-K without the reduction: split s writes x[:, K_s] . w[:, K_s]^T as fp32 to out + s * split_stride (row stride
+// ldo); the consuming kernel adds the `splits` partial products in order.  For very skinny outputs (a handful of
+// columns over a long K) this spreads both the weight stream and the reduction over the GPU.
+DSV4_API int dsv4_gemm_bf16_partials(const void* x, const void* w, float* out, int M, int N, int K, int ldx, int ldw,
+                                     int ldo, int bn, int splits, long long split_stride, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 8) || (ldx % 8) || (ldw % 8) || splits < 1 || split_stride < (long long)M * ldo) return 118;
+  LaunchOpts o;
+  o.splits = splits;
+  o.partial_stride = split_stride;
+  return dispatch_bn<false, float>(x, w, out, M, N, K, ldx, ldw, ldo, nullptr, nullptr, 0, bn ? bn : 32, stream, o);
 }
 
 // x: e4m3 [M,K] with sa fp32 [M, K/128];  w: e4m3 [N,K] with sb fp32 [ceil(N/128), K/128].

@@ -18,11 +18,14 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-
 template <int MIX>  // 24 = layer (pre, post, comb), 4 = head (pre only)
 __global__ void __launch_bounds__(256) hc_pre_kernel(const __nv_bfloat16* __restrict__ x,
                                                      const __nv_bfloat16* __restrict__ fn,
+                                                     const float* __restrict__ mixes_in, int ld_mix, int n_part,
+                                                     long long part_stride,
                                                      const float* __restrict__ scale, const float* __restrict__ base,
                                                      const __nv_bfloat16* __restrict__ norm_w,
                                                      __nv_bfloat16* __restrict__ y, float* __restrict__ post,
                                                      float* __restrict__ comb, int h, int iters, float eps,
                                                      float norm_eps, float rms_eps) {
+  pdl_entry();
   extern __shared__ __align__(16) uint8_t hc_smem[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(hc_smem);  // [4*h]
   __shared__ float red[32];
@@ -45,7 +48,15 @@ __global__ void __launch_bounds__(256) hc_pre_kernel(const __nv_bfloat16* __rest
   ss = warp_sum(ss);
   if (lane == 0) red[warp] = ss;
   __syncthreads();
-  // mix rows: warp w handles rows w, w+8, ...
+  // mix rows: taken from a tensor-core GEMM over all tokens when the caller ran one (every CTA re-reading the
+  // [MIX, 4h] matrix costs more than the rest of the kernel), else warp w computes rows w, w+8, ...
+  if (mixes_in) {
+    if (tid < MIX) {  // split-K partial products, added in split order
+      float a = 0.f;
+      for (int p = 0; p < n_part; ++p) a += __ldg(mixes_in + (size_t)p * part_stride + (size_t)t * ld_mix + tid);
+      mixes[tid] = a;
+    }
+  } else
   for (int r = warp; r < MIX; r += 8) {
     const __nv_bfloat16* fr = fn + (size_t)r * total;
     float acc = 0.f;
@@ -165,6 +176,7 @@ __global__ void __launch_bounds__(256) hc_post_kernel(const __nv_bfloat16* __res
                                                       const __nv_bfloat16* __restrict__ res,
                                                       const float* __restrict__ post, const float* __restrict__ comb,
                                                       __nv_bfloat16* __restrict__ out, int h) {
+  pdl_entry();
   const int t = blockIdx.x;
   const int i = (blockIdx.y * 256 + threadIdx.x) * 8;
   __shared__ float ps[kM], cs[16];
@@ -213,7 +225,12 @@ __global__ void __launch_bounds__(256) hc_post_kernel(const __nv_bfloat16* __res
 }  // namespace
 
 // mix_rows = 24: writes y, post, comb.  mix_rows = 4: head collapse (post/comb unused).  norm_w may be null.
-DSV4_API int dsv4_hc_pre(const void* x, const void* fn, const float* scale, const float* base, const void* norm_w,
+// mixes (may be null): n_part split-K partial products of x_flat . fn^T from a GEMM over all tokens, fp32
+// [n_part][t, ld_mix] spaced part_stride floats apart; the kernel adds them in order.  When null it computes the
+// products itself.
+DSV4_API int dsv4_hc_pre(const void* x, const void* fn, const float* mixes, int ld_mix, int n_part,
+                         long long part_stride, const float* scale,
+                         const float* base, const void* norm_w,
                          void* y, float* post, float* comb, int t, int h, int mix_rows, int iters, float eps,
                          float norm_eps, float rms_eps, cudaStream_t st) {
   if (t <= 0) return 0;
@@ -225,7 +242,7 @@ DSV4_API int dsv4_hc_pre(const void* x, const void* fn, const float* scale, cons
       cudaFuncSetAttribute(hc_pre_kernel<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 4096 * 2);
       set = true;
     }
-    hc_pre_kernel<24><<<t, 256, smem, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)fn, scale, base,
+    dsv4_launch(hc_pre_kernel<24>, t, 256, smem, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)fn, mixes, ld_mix, n_part, part_stride, scale, base,
                                            (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)y, post, comb, h, iters, eps,
                                            norm_eps, rms_eps);
   } else if (mix_rows == 4) {
@@ -234,7 +251,7 @@ DSV4_API int dsv4_hc_pre(const void* x, const void* fn, const float* scale, cons
       cudaFuncSetAttribute(hc_pre_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * 4096 * 2);
       set4 = true;
     }
-    hc_pre_kernel<4><<<t, 256, smem, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)fn, scale, base,
+    dsv4_launch(hc_pre_kernel<4>, t, 256, smem, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)fn, mixes, ld_mix, n_part, part_stride, scale, base,
                                           (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)y, post, comb, h, iters, eps,
                                           norm_eps, rms_eps);
   } else {
@@ -248,7 +265,7 @@ DSV4_API int dsv4_hc_post(const void* y, const void* res, const float* post, con
   if (t <= 0) return 0;
   if (h % 8) return 132;
   dim3 grid(t, (h / 8 + 255) / 256);
-  hc_post_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)res, post, comb,
+  dsv4_launch(hc_post_kernel, grid, 256, 0, st, (const __nv_bfloat16*)y, (const __nv_bfloat16*)res, post, comb,
                                        (__nv_bfloat16*)out, h);
   return (int)cudaGetLastError();
 }

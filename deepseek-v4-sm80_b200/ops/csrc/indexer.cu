@@ -26,6 +26,7 @@ __global__ void __launch_bounds__(256) indexer_logits_kernel(const uint8_t* __re
                                                              const int* __restrict__ slots, const int* __restrict__ pos,
                                                              const int* __restrict__ page_table, int ld_pt, int ps,
                                                              float* __restrict__ logits, int width, int heads) {
+  pdl_entry();
   extern __shared__ __align__(16) float ix_smem[];
   float* qs = ix_smem;                  // [heads][QLD]
   float* ks = qs + heads * QLD;         // [8 warps][DI]
@@ -111,6 +112,7 @@ __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int& total)
 __global__ void __launch_bounds__(1024) topk_kernel(const float* __restrict__ logits, int width,
                                                     const int* __restrict__ pos, int* __restrict__ idx,
                                                     int* __restrict__ out_len, int k) {
+  pdl_entry();
   __shared__ int hist[256];
   __shared__ int wt[32];
   __shared__ int sh_bad, sh_bin, sh_rem;
@@ -186,7 +188,7 @@ DSV4_API int dsv4_indexer_logits(const void* qc, const float* wf, const void* kv
   if (d != DI || (heads != 32 && heads != 64)) return 400;
   const int smem = (heads * QLD + 8 * DI) * 4;
   dim3 grid(t, (width + 63) / 64);
-  indexer_logits_kernel<<<grid, 256, smem, st>>>((const uint8_t*)qc, wf, (const uint8_t*)kvals, kscale, slots, pos,
+  dsv4_launch(indexer_logits_kernel, grid, 256, smem, st, (const uint8_t*)qc, wf, (const uint8_t*)kvals, kscale, slots, pos,
                                                  page_table, ld_pt, ps, logits, width, heads);
   return (int)cudaGetLastError();
 }
@@ -194,7 +196,7 @@ DSV4_API int dsv4_indexer_logits(const void* qc, const float* wf, const void* kv
 DSV4_API int dsv4_topk(const float* logits, int width, const int* pos, int* idx, int* out_len, int t, int k,
                        cudaStream_t st) {
   if (t <= 0) return 0;
-  topk_kernel<<<t, 1024, 0, st>>>(logits, width, pos, idx, out_len, k);
+  dsv4_launch(topk_kernel, t, 1024, 0, st, logits, width, pos, idx, out_len, k);
   return (int)cudaGetLastError();
 }
 

@@ -30,13 +30,21 @@ struct PlanHeader {
 };
 
 // ------------------------------------------------------------------ router post-processing
-// scores fp32 [T,E] -> p = sqrt(softplus) | sigmoid ; select top-k of p + bias (ties: lower id) or the hash
+// scores fp32 [n_part][T,E] (split-K partial products, summed here) -> p = sqrt(softplus) | sigmoid ; select top-k of p + bias (ties: lower id) or the hash
 // table row; w = p[idx] / (sum + 1e-8) * scaling.  Rows >= num_valid get (-1, 0).
 __global__ void moe_topk_kernel(const float* __restrict__ scores, const float* __restrict__ bias,
                                 const int* __restrict__ tid2eid, const int* __restrict__ token_ids,
                                 const int* __restrict__ num_valid, int* __restrict__ idx, float* __restrict__ wts,
-                                int t_rows, int e, int k, float scaling, int scoring) {
+                                int t_rows, int e, int k, float scaling, int scoring, int n_part,
+                                long long part_stride) {
+  pdl_entry();
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  // scores may come as n_part split-K partial products (spaced part_stride floats apart), added here in order
+  auto score_at = [&](int j) {
+    float a = 0.f;
+    for (int q = 0; q < n_part; ++q) a += __ldg(scores + (size_t)q * part_stride + (size_t)row * e + j);
+    return a;
+  };
   if (row >= t_rows) return;
   if (num_valid && row >= *num_valid) {
     if (lane < k) idx[row * k + lane] = -1, wts[row * k + lane] = 0.f;
@@ -49,7 +57,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ scores, const float* _
   if (scoring == 2) {
     for (int i = 0; i < per; ++i) {
       const int j = lane + i * 32;
-      if (j < e) smax = fmaxf(smax, scores[(size_t)row * e + j]);
+      if (j < e) smax = fmaxf(smax, score_at(j));
     }
     smax = warp_max(smax);
   }
@@ -60,7 +68,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ scores, const float* _
     p[i] = 0.f;
     sel[i] = -INFINITY;
     if (i < per && j < e) {
-      const float s = scores[(size_t)row * e + j];
+      const float s = score_at(j);
       float v;
       if (scoring == 0) {
         const float sp = s > 20.f ? s : log1pf(expf(s));
@@ -135,6 +143,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
                                                         PlanHeader* __restrict__ hdr, int* __restrict__ tiles,
                                                         int* __restrict__ sorted_route, int* __restrict__ route_pos,
                                                         float* __restrict__ sorted_w) {
+  pdl_entry();
   extern __shared__ int sm[];
   int* cnt = sm;                 // [e_local]
   int* off = sm + e_local;       // [e_local + 1]
@@ -188,6 +197,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
 __global__ void moe_permute_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs,
                                    const int* __restrict__ sorted_route, const PlanHeader* __restrict__ hdr, int topk,
                                    int h8) {
+  pdl_entry();
   const int pos = blockIdx.x;
   if (pos >= hdr->num_routes_local) return;
   const int tok = sorted_route[pos] / topk;
@@ -284,6 +294,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 const int* __restrict__ sorted_route, const float* __restrict__ sorted_w,
                 __nv_bfloat16* __restrict__ out, int K, int rows_per_expert /*I (mode1) or H (mode2)*/,
                 int ld_out, float limit) {
+  pdl_launch_dependents();
   using S = MoeSmem<MODE, NT>;
   constexpr int kOBufs = S::kOBufs, kPStages = S::kPStages, kAccBufs = S::kAccBufs;
   constexpr uint32_t kIdesc = umma_idesc(128, NT, 0, 0);  // fp16 x fp16 -> fp32
@@ -327,6 +338,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // barriers and tensor memory are set up; from here on the kernel touches global memory
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t a_base = tmem_base + S::kAccCols;  // operand buffer b starts at column a_base + b * kACols
   const int total_work = hdr->num_tiles * row_tiles;
@@ -527,6 +539,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 __global__ void moe_finalize_kernel(const __nv_bfloat16* __restrict__ yr, const int* __restrict__ route_pos,
                                     const __nv_bfloat16* __restrict__ shared, __nv_bfloat16* __restrict__ out,
                                     const int* __restrict__ num_valid, int topk, int h) {
+  pdl_entry();
   const int t = blockIdx.x;
   const bool valid = !num_valid || t < *num_valid;
   for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
@@ -566,6 +579,7 @@ __global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat1
                                                               __nv_bfloat16* __restrict__ out,
                                                               const int* __restrict__ num_valid, int topk, int h,
                                                               int t_rows, const CommCtx comm) {
+  pdl_entry();
   __shared__ int ok;
   const uint32_t epoch = comm_epoch(comm);
   const int parity = epoch & 1;
@@ -630,7 +644,7 @@ int launch_moe_gemm(const void* w, const uint8_t* scales, const void* x, int x_r
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return 203;
     set = true;
   }
-  kern<<<num_sms, kThreads, S::kTotal, st>>>(tmW, tmX, scales, hdr, tiles, sorted_route, sorted_w, (__nv_bfloat16*)out,
+  dsv4_launch(kern, num_sms, kThreads, S::kTotal, st, tmW, tmX, scales, hdr, tiles, sorted_route, sorted_w, (__nv_bfloat16*)out,
                                             K, rows_per_expert, ld_out, limit);
   return (int)cudaGetLastError();
 }
@@ -639,11 +653,12 @@ int launch_moe_gemm(const void* w, const uint8_t* scales, const void* x, int x_r
 
 DSV4_API int dsv4_moe_topk(const float* scores, const float* bias, const int* tid2eid, const int* token_ids,
                            const int* num_valid, int* idx, float* wts, int t, int e, int k, float scaling, int scoring,
-                           cudaStream_t st) {
+                           int n_part, long long part_stride, cudaStream_t st) {
   if (t <= 0) return 0;
-  if (e > 512 || k > 32) return 210;
-  moe_topk_kernel<<<(t * 32 + 255) / 256, 256, 0, st>>>(scores, bias, tid2eid, token_ids, num_valid, idx, wts, t, e, k,
-                                                       scaling, scoring);
+  if (e > 512 || k > 32 || n_part < 1) return 210;
+  // one warp per token, two warps per CTA: a decode batch of 128 tokens then covers 64 SMs instead of 16
+  dsv4_launch(moe_topk_kernel, (t * 32 + 63) / 64, 64, 0, st, scores, bias, tid2eid, token_ids, num_valid, idx, wts, t,
+              e, k, scaling, scoring, n_part, part_stride);
   return (int)cudaGetLastError();
 }
 
@@ -656,7 +671,7 @@ DSV4_API int dsv4_moe_plan(const int* idx, const float* wts, int routes, int e_l
   int* route_pos = sorted_route + routes;
   float* sorted_w = reinterpret_cast<float*>(route_pos + routes);
   const int smem = (4 * e_local + 2) * sizeof(int);
-  moe_plan_kernel<<<1, 1024, smem, st>>>(idx, wts, routes, e_local, base, nt, hdr, tiles, sorted_route, route_pos,
+  dsv4_launch(moe_plan_kernel, 1, 1024, smem, st, idx, wts, routes, e_local, base, nt, hdr, tiles, sorted_route, route_pos,
                                          sorted_w);
   return (int)cudaGetLastError();
 }
@@ -666,7 +681,7 @@ DSV4_API int dsv4_moe_permute(const void* x, void* xs, const int* plan, int rout
   if (routes <= 0) return 0;
   const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(plan);
   const int* sorted_route = plan + 4 + 3 * max_tiles;
-  moe_permute_kernel<<<routes, 128, 0, st>>>((const uint4*)x, (uint4*)xs, sorted_route, hdr, topk, h / 8);
+  dsv4_launch(moe_permute_kernel, routes, 128, 0, st, (const uint4*)x, (uint4*)xs, sorted_route, hdr, topk, h / 8);
   return (int)cudaGetLastError();
 }
 
@@ -695,7 +710,7 @@ DSV4_API int dsv4_moe_finalize(const void* yr, const int* plan, int routes, int 
                                const int* num_valid, int t, int topk, int h, cudaStream_t st) {
   if (t <= 0) return 0;
   const int* route_pos = plan + 4 + 3 * max_tiles + routes;
-  moe_finalize_kernel<<<t, 256, 0, st>>>((const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
+  dsv4_launch(moe_finalize_kernel, t, 256, 0, st, (const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
                                          (__nv_bfloat16*)out, num_valid, topk, h);
   return (int)cudaGetLastError();
 }
@@ -707,7 +722,7 @@ DSV4_API int dsv4_moe_finalize_allreduce(const void* yr, const int* plan, int ro
   if (h % 8 || (long long)t * h * 2 > comm->data_bytes) return 230;
   const int* route_pos = plan + 4 + 3 * max_tiles + routes;
   const int grid = t < 1024 ? t : 1024;
-  moe_finalize_ar_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
+  dsv4_launch(moe_finalize_ar_kernel, grid, 256, 0, st, (const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
                                                (__nv_bfloat16*)out, num_valid, topk, h, t, *comm);
   return (int)cudaGetLastError();
 }

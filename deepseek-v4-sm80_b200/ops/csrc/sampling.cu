@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
                                                       const float* __restrict__ uniform,
                                                       const int* __restrict__ mask_ids, int n_mask,
                                                       long long* __restrict__ out) {
+  pdl_entry();
   __shared__ float sf[32];
   __shared__ int si[32];
   __shared__ unsigned long long wt[32];
@@ -200,6 +201,6 @@ DSV4_API int dsv4_sample(const float* logits, int rows, int v, const float* temp
                          const float* top_p, const float* uniform, const int* mask_ids, int n_mask, long long* out,
                          cudaStream_t st) {
   if (rows <= 0) return 0;
-  sample_kernel<<<rows, 1024, 0, st>>>(logits, v, temperature, top_k, top_p, uniform, mask_ids, n_mask, out);
+  dsv4_launch(sample_kernel, rows, 1024, 0, st, logits, v, temperature, top_k, top_p, uniform, mask_ids, n_mask, out);
   return (int)cudaGetLastError();
 }

@@ -11,7 +11,7 @@ import math
 import torch
 
 from . import native as nv
-from .native import F, I
+from .native import F, I, L
 from .ref import RopeSpec
 
 
@@ -109,14 +109,26 @@ def q_kv_norm_rope_store(q, kv, positions, kv_w, eps, spec, swa_cache, out_loc, 
 
 
 # --------------------------------------------------------------------------- hyper-connections
+def _hc_mixes(x, fn):
+    """Split-K partial products [S, t, MIX] of flatten(x[t]) . fn^T: one tensor-core GEMM over all tokens, whose
+    splits the per-token kernel adds up."""
+    from .gemm import gemm_bf16_partials
+
+    t = x.shape[0]
+    return gemm_bf16_partials(x.reshape(t, -1), fn)
+
+
 def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None):
     t, m, h = x.shape
     assert m == 4 and x.is_contiguous()
     y = torch.empty(t, h, dtype=x.dtype, device=x.device)
     post = torch.empty(t, m, dtype=torch.float32, device=x.device)
     comb = torch.empty(t, m, m, dtype=torch.float32, device=x.device)
-    nv.call("hc_pre", nv.ptr(x), nv.ptr(fn), nv.ptr(scale), nv.ptr(base), nv.ptr(norm_w), nv.ptr(y), nv.ptr(post),
-            nv.ptr(comb), I(t), I(h), I(24), I(iters), F(eps), F(norm_eps), F(norm_eps))
+    mixes = _hc_mixes(x, fn)
+    nv.call("hc_pre", nv.ptr(x), nv.ptr(fn), nv.ptr(mixes), I(mixes.stride(1)), I(mixes.shape[0]),
+            L(mixes.stride(0)), nv.ptr(scale), nv.ptr(base),
+            nv.ptr(norm_w), nv.ptr(y), nv.ptr(post), nv.ptr(comb), I(t), I(h), I(24), I(iters), F(eps), F(norm_eps),
+            F(norm_eps))
     return y, post, comb
 
 
@@ -131,8 +143,11 @@ def hc_head(x, fn, scale, base, eps, norm_eps, norm_w=None):
     t, m, h = x.shape
     x = x.contiguous()
     y = torch.empty(t, h, dtype=x.dtype, device=x.device)
-    nv.call("hc_pre", nv.ptr(x), nv.ptr(fn), nv.ptr(scale), nv.ptr(base), nv.ptr(norm_w), nv.ptr(y), nv.ptr(None),
-            nv.ptr(None), I(t), I(h), I(4), I(0), F(eps), F(norm_eps), F(norm_eps))
+    mixes = _hc_mixes(x, fn)
+    nv.call("hc_pre", nv.ptr(x), nv.ptr(fn), nv.ptr(mixes), I(mixes.stride(1)), I(mixes.shape[0]),
+            L(mixes.stride(0)), nv.ptr(scale), nv.ptr(base),
+            nv.ptr(norm_w), nv.ptr(y), nv.ptr(None), nv.ptr(None), I(t), I(h), I(4), I(0), F(eps), F(norm_eps),
+            F(norm_eps))
     return y
 
 
@@ -210,7 +225,7 @@ _GATE_BF16 = {}
 
 
 def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid=None):
-    from .gemm import gemm_bf16
+    from .gemm import gemm_bf16_partials
 
     key = gate_w.data_ptr()
     wb = _GATE_BF16.get(key)
@@ -218,12 +233,12 @@ def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_va
         wb = gate_w.to(torch.bfloat16)
         _GATE_BF16[key] = wb
     t, e = y.shape[0], gate_w.shape[0]
-    scores = gemm_bf16(y, wb, out_dtype=torch.float32)
+    scores = gemm_bf16_partials(y, wb)  # [S, T, E]; the selection kernel adds the splits
     idx = torch.empty(t, topk, dtype=torch.int32, device=y.device)
     wts = torch.empty(t, topk, dtype=torch.float32, device=y.device)
     nv.call("moe_topk", nv.ptr(scores), nv.ptr(bias if tid2eid is None else None), nv.ptr(tid2eid),
             nv.ptr(token_ids), nv.ptr(num_valid), nv.ptr(idx), nv.ptr(wts), I(t), I(e), I(topk), F(scaling),
-            I(_SCORING[scoring]))
+            I(_SCORING[scoring]), I(scores.shape[0]), L(scores.stride(0)))
     return idx, wts
 
 

@@ -15,7 +15,7 @@ import ctypes
 import torch
 
 from . import native as nv
-from .native import I
+from .native import I, L
 
 _COUNTERS = {}
 NUM_SMS_HINT = 148
@@ -50,7 +50,7 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
         ctas = mt * ((n + bn - 1) // bn)
         splits = 1
         if ctas <= NUM_SMS_HINT // 2 and k_tiles >= 8:
-            splits = max(min(NUM_SMS_HINT // ctas, k_tiles // 4, 16), 1)
+            splits = max(min(NUM_SMS_HINT // ctas, k_tiles // 4, 32 if ctas <= 4 else 16), 1)
     if mt * ((n + bn - 1) // bn) > (1 << 16):
         splits = 1
     return bn, splits
@@ -89,6 +89,27 @@ def gemm_bf16(x, w, out=None, out_dtype=torch.bfloat16, accumulate=False, bn=0, 
     nv.call("gemm_bf16", nv.ptr(x2), nv.ptr(w), nv.ptr(o2), I(m), I(n), I(k), I(x2.stride(0)), I(w.stride(0)),
             I(o2.stride(0)), I(1 if out.dtype == torch.float32 else 0), I(1 if accumulate else 0), I(bn), I(1),
             I(splits), nv.ptr(ws), nv.ptr(cnt))
+    return out
+
+
+def gemm_bf16_partials(x, w, splits: int = 0):
+    """Split-K bf16 GEMM that leaves the reduction to its consumer: returns fp32 [splits, M, N] with
+    sum(0) == x @ w^T.  A split whose K range is empty writes zeros."""
+    x2 = _as2d(x)
+    m, k = x2.shape
+    n = w.shape[0]
+    k_tiles = (k + 63) // 64
+    if splits <= 0:
+        ctas = ((m + 127) // 128) * ((n + 31) // 32)
+        splits = max(1, min(NUM_SMS_HINT // ctas, k_tiles // 4, 64))
+    if not x.is_cuda:
+        per = (k_tiles + splits - 1) // splits * 64
+        xf, wf = x2.float(), w.float()
+        return torch.stack([xf[:, s * per:(s + 1) * per] @ wf[:, s * per:(s + 1) * per].t() for s in range(splits)])
+    assert x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x2.stride(-1) == 1 and w.stride(-1) == 1
+    out = torch.empty(splits, m, n, dtype=torch.float32, device=x.device)
+    nv.call("gemm_bf16_partials", nv.ptr(x2), nv.ptr(w), nv.ptr(out), I(m), I(n), I(k), I(x2.stride(0)),
+            I(w.stride(0)), I(n), I(32), I(splits), L(m * n))
     return out
 
 
