@@ -45,6 +45,8 @@ struct GemmArgs {
   int splits;
   float* ws;           // [tiles][splits][128][BN] fp32 partials
   int* counters;       // [tiles], zero between launches
+  int cluster;         // > 0: the `splits` CTAs of a tile form one thread-block cluster and reduce over distributed
+                       //      shared memory (no workspace, no atomics)
   long long partial_stride;  // > 0: split s writes its own partial product to out + s * partial_stride (no reduction;
                              //      the consumer kernel sums the splits in order)
 };
@@ -241,7 +243,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
     bool write_out = ok;
-    if (g.splits > 1 && g.partial_stride == 0) {
+    if (g.cluster) {
+      // park this split's fp32 partial in shared memory (the pipeline stages are idle by now); the cluster reduces
+      // it below.  Rows are padded by 4 floats so that both the row-wise writes here and the 16-byte reads of the
+      // reduction are free of bank conflicts.
+      float* red = reinterpret_cast<float*>(tiles) + (size_t)row * (BN + 4);
+#pragma unroll
+      for (int j = 0; j < BN; j += 4)
+        *reinterpret_cast<float4*>(red + j) =
+            ok ? make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]) : make_float4(0.f, 0.f, 0.f, 0.f);
+      write_out = false;
+    } else if (g.splits > 1 && g.partial_stride == 0) {
       // publish this split's fp32 partial, the last split to arrive reduces all of them in split order
       const int tile = (batch * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
       float* wsp = g.ws + (((size_t)tile * g.splits + split) * kBM + row) * BN;
@@ -306,6 +318,43 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   }
+  if (g.cluster) {
+    // Cluster split-K: CTA r of the cluster owns rows [r * 128 / S, (r + 1) * 128 / S) of the tile and adds the S
+    // partials in split order (bit-reproducible), reading its peers' shared memory directly.
+    const int S2 = g.splits;
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int t = threadIdx.x - 64;                    // 0..127
+      const int rows_per = kBM / S2;                     // S2 in {2, 4, 8}
+      const int f4_per_row = BN / 4;
+      const int total_f4 = rows_per * f4_per_row;
+      const uint32_t my_rank = cluster_ctarank();
+      const uint32_t red_base = smem_u32(tiles);
+      OutT* outb = out + (size_t)batch * g.out_col_pb;
+      for (int f = t; f < total_f4; f += 128) {
+        const int row = (int)my_rank * rows_per + f / f4_per_row, c4 = f % f4_per_row;
+        const uint32_t addr = red_base + (uint32_t)(row * (BN + 4) + c4 * 4) * 4u;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < S2; ++sp) {
+          const float4 v = ld_dsmem_f4(addr, (uint32_t)sp);
+          a.x += v.x, a.y += v.y, a.z += v.z, a.w += v.w;
+        }
+        const int grow = m0 + row, col = n0 + c4 * 4;
+        if (grow < M && col < N) {
+          OutT* dst = outb + (size_t)grow * g.ldo + col;
+          float v4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (col + j < N) {
+              if (g.accumulate_out) v4[j] += (float)dst[j];
+              dst[j] = (OutT)v4[j];
+            }
+        }
+      }
+    }
+    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
@@ -316,6 +365,7 @@ struct LaunchOpts {
   int splits = 1;
   float* ws = nullptr;
   long long partial_stride = 0;
+  int cluster = 0;
   int* counters = nullptr;
   int a_cols = 0, b_rows = 0;  // full extents of the operands (0 = K / N)
   int sb_ld = 0;
@@ -346,8 +396,13 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
     if ((long long)grid.x * grid.y > kCommSlots || o.splits != 1 || o.batches != 1) return 104;
   }
   GemmArgs g{M, N, K, ldo, sa, sb, o.sb_ld ? o.sb_ld : (K + 127) / 128, accumulate_out, o.a_col_pb, o.b_row_pb,
-             o.out_col_pb, o.splits, o.ws, o.counters, o.partial_stride};
-  dsv4_launch(kern, grid, 192, Cfg::kSmemBytes, stream, tmA, tmB, out, g, comm);
+             o.out_col_pb, o.splits, o.ws, o.counters, o.cluster, o.partial_stride};
+  if (o.cluster) {
+    if (o.splits != 2 && o.splits != 4 && o.splits != 8) return 105;
+    dsv4_launch_cluster(kern, grid, 192, Cfg::kSmemBytes, stream, o.splits, tmA, tmB, out, g, comm);
+  } else {
+    dsv4_launch(kern, grid, 192, Cfg::kSmemBytes, stream, tmA, tmB, out, g, comm);
+  }
   return (int)cudaGetLastError();
 }
 
@@ -395,7 +450,8 @@ DSV4_API int dsv4_gemm_bf16(const void* x, const void* w, void* out, int M, int 
   o.splits = splits < 1 ? 1 : splits;
   o.ws = ws, o.counters = counters;
   if (o.batches > 1) o.a_col_pb = K, o.b_row_pb = N, o.out_col_pb = N, o.a_cols = K * o.batches, o.b_rows = N * o.batches;
-  if (o.splits > 1 && (bn == 0 || !ws || !counters)) return 116;
+  if (o.splits > 1 && bn == 0) return 116;
+  if (o.splits > 1 && (!ws || !counters)) o.cluster = 1;  // no workspace given: reduce inside a thread-block cluster
   if (out_fp32)
     return dispatch_bn<false, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, nullptr, nullptr, accumulate_out, bn,
                                      stream, o);
@@ -425,7 +481,8 @@ DSV4_API int dsv4_gemm_fp8(const void* x, const void* w, void* out, const float*
   LaunchOpts o;
   o.splits = splits < 1 ? 1 : splits;
   o.ws = ws, o.counters = counters;
-  if (o.splits > 1 && (bn == 0 || !ws || !counters)) return 117;
+  if (o.splits > 1 && bn == 0) return 117;
+  if (o.splits > 1 && (!ws || !counters)) o.cluster = 1;
   if (out_fp32)
     return dispatch_bn<true, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn, stream, o);
   return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn,

@@ -5,8 +5,8 @@ CPU tensors run the fp32 PyTorch statement of the same arithmetic, which is also
 oracle the GPU tests compare against.  These replace the reference's cuBLAS calls on
 dequantised BF16 weight caches (python/minisgl/models/deepseek_v4.py:145-149).
 
-Skinny problems (few output tiles, long K) are split along K so that the whole GPU streams the weight; the
-partials meet in an fp32 workspace and the last split per tile reduces them in a fixed order.
+Skinny problems (few output tiles, long K) are split along K so that the whole GPU streams the weight; the CTAs
+of a tile form a thread-block cluster and add their partials in split order over distributed shared memory.
 """
 from __future__ import annotations
 
@@ -50,14 +50,18 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
         ctas = mt * ((n + bn - 1) // bn)
         splits = 1
         if ctas <= NUM_SMS_HINT // 2 and k_tiles >= 8:
-            splits = max(min(NUM_SMS_HINT // ctas, k_tiles // 4, 32 if ctas <= 4 else 16), 1)
+            # the splits of a tile form one thread-block cluster (2, 4 or 8 CTAs) that reduces in shared memory
+            want = max(min(NUM_SMS_HINT // ctas, k_tiles // 4, 8), 1)
+            splits = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
     if mt * ((n + bn - 1) // bn) > (1 << 16):
         splits = 1
     return bn, splits
 
 
 def _ws(m, n, bn, batches, splits, device):
-    if splits <= 1:
+    """Workspace of the global-memory split-K reduction.  Splits of 2, 4 or 8 need none: they reduce inside a
+    thread-block cluster.  Other split counts (only reachable by asking for them) use the workspace."""
+    if splits <= 1 or splits in (2, 4, 8):
         return None, None
     elems = nv.cuda_lib().dsv4_gemm_splitk_ws_elems
     elems.restype = ctypes.c_longlong

@@ -46,7 +46,8 @@ def test_gemm_fp8_block_scaled(m, n, k, bn):
     assert torch.allclose(y, ref, rtol=1e-3, atol=1e-3), (y - ref).abs().max().item()
 
 
-@pytest.mark.parametrize("m,n,k,splits", [(128, 64, 4096, 16), (128, 1536, 4096, 3), (40, 256, 4096, 0), (128, 2048, 4096, 2)])
+@pytest.mark.parametrize("m,n,k,splits", [(128, 64, 4096, 16), (128, 1536, 4096, 3), (40, 256, 4096, 0), (128, 2048, 4096, 2),
+                                            (128, 520, 4096, 8), (300, 96, 2048, 4)])
 def test_gemm_bf16_split_k(m, n, k, splits):
     torch.manual_seed(2)
     x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
@@ -59,7 +60,22 @@ def test_gemm_bf16_split_k(m, n, k, splits):
     assert torch.equal(y, y1)  # fixed reduction order: bitwise repeatable
 
 
-@pytest.mark.parametrize("splits", [0, 4])
+def test_gemm_bf16_cluster_split_k_bf16_out_and_partials():
+    """Cluster reduction with a bf16 result and an odd edge; raw split-K partial products sum to the product."""
+    torch.manual_seed(4)
+    m, n, k = 100, 72, 4096
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    y = gemm.gemm_bf16(x, w, bn=32, splits=8)
+    assert y.dtype == torch.bfloat16
+    assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2), (y.float() - ref).abs().max().item()
+    parts = gemm.gemm_bf16_partials(x, w)
+    assert parts.shape[1:] == (m, n) and parts.shape[0] > 1
+    assert torch.allclose(parts.sum(0), ref, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("splits", [0, 4, 8])
 def test_gemm_fp8_split_k(splits):
     torch.manual_seed(3)
     m, n, k = 128, 1536, 4096
