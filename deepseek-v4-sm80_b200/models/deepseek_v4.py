@@ -77,18 +77,18 @@ class DSV4Model:
             xq = O.fp8_quant(x)
         return O.gemm_fp8(xq[0], xq[1], self.w[name + ".weight"], self.w[name + ".scale"])
 
-    def attention(self, l: int, y: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+    def attention(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None) -> torch.Tensor:
         cfg, w, p = self.cfg, self.w, f"L{l}.attn."
         t = y.shape[0]
         rope = self.ropes[l]
         ratio = cfg.ratio(l)
         kvv = self.pool.layer_views(l)
         ps = self.pool.page_size
-        yq = O.fp8_quant(y)
+        if yq is None:
+            yq = O.fp8_quant(y)
         qkv = O.gemm_fp8(yq[0], yq[1], w[p + "wqkv_a.weight"], w[p + "wqkv_a.scale"])
-        q_lora = O.rms_norm(qkv[:, : cfg.q_lora_rank], w[p + "q_norm.weight"], cfg.rms_norm_eps)
+        q_lora, qlq = O.rms_norm(qkv[:, : cfg.q_lora_rank], w[p + "q_norm.weight"], cfg.rms_norm_eps, want_q=True)
         kv = qkv[:, cfg.q_lora_rank:]
-        qlq = O.fp8_quant(q_lora)
         q = O.gemm_fp8(qlq[0], qlq[1], w[p + "wq_b.weight"], w[p + "wq_b.scale"]).view(t, self.h_local, cfg.head_dim)
         q, kv = O.q_kv_norm_rope_store(q, kv, fb.positions, w[p + "kv_norm.weight"], cfg.rms_norm_eps, rope,
                                        kvv["swa"], fb.out_loc, self.pool.swa_map, ps, self.qat)
@@ -119,15 +119,16 @@ class DSV4Model:
         out = self._fp8_linear(o2, p + "wo_b")
         return self.comm.all_reduce(out, "attn")
 
-    def moe(self, l: int, y: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+    def moe(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None) -> torch.Tensor:
         cfg, w, p = self.cfg, self.w, f"L{l}.moe."
         idx, wt = O.moe_gate(y, w[p + "gate.weight"], w.get(p + "gate.bias"), cfg.num_experts_per_tok,
                              cfg.routed_scaling_factor, cfg.scoring_func, w.get(p + "gate.tid2eid"), fb.input_ids,
                              fb.num_valid)
-        yq = O.fp8_quant(y)
+        if yq is None:
+            yq = O.fp8_quant(y)
         gu = O.gemm_fp8(yq[0], yq[1], w[p + "sh_gate_up.weight"], w[p + "sh_gate_up.scale"])
-        a = O.silu_mul_clamp(gu, cfg.swiglu_limit)
-        shared = self._fp8_linear(a, p + "sh_down")
+        aq = O.silu_mul_clamp_quant(gu, cfg.swiglu_limit)
+        shared = O.gemm_fp8(aq[0], aq[1], w[p + "sh_down.weight"], w[p + "sh_down.scale"])
         if y.is_cuda:
             # routed rows stay per route; the combine kernel sums them with the shared expert (and, with fused
             # communication, all-reduces the result in the same kernel)
@@ -148,9 +149,10 @@ class DSV4Model:
     def layer(self, l: int, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
         cfg, w, p = self.cfg, self.w, f"L{l}."
         for blk, fn, norm in (("hc_attn", self.attention, "attn_norm"), ("hc_ffn", self.moe, "ffn_norm")):
-            y, post, comb = O.hc_pre(x, w[p + blk + ".fn"], w[p + blk + ".scale"], w[p + blk + ".base"],
-                                     cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps, w[p + norm + ".weight"])
-            y = fn(l, y, fb)
+            y, post, comb, yq = O.hc_pre(x, w[p + blk + ".fn"], w[p + blk + ".scale"], w[p + blk + ".base"],
+                                         cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps,
+                                         w[p + norm + ".weight"], want_q=True)
+            y = fn(l, y, fb, yq)
             x = O.hc_post(y, x, post, comb)
         return x
 

@@ -58,10 +58,12 @@ def embed(ids, weight, m: int):
     return weight[ids.long()].unsqueeze(1).repeat(1, m, 1)
 
 
-def rms_norm(x, weight, eps: float):
+def rms_norm(x, weight, eps: float, want_q: bool = False):
+    """want_q: returns (out, (e4m3, scales)) -- on CUDA the normalising kernel writes the quantisation too."""
     if x.is_cuda:
-        return _cu().rms_norm(x, weight, eps)
-    return ref.rms_norm(x, weight, eps)
+        return _cu().rms_norm(x, weight, eps, want_q)
+    out = ref.rms_norm(x, weight, eps)
+    return (out, fp8_quant(out)) if want_q else out
 
 
 def fp8_quant(x, block: int = 128):
@@ -76,6 +78,13 @@ def silu_mul_clamp(gate_up, limit):
     if gate_up.is_cuda:
         return _cu().silu_mul_clamp(gate_up, limit)
     return ref.silu_mul_clamp(gate_up, limit)
+
+
+def silu_mul_clamp_quant(gate_up, limit):
+    """(e4m3, scales) of the SwiGLU activation (one kernel on CUDA)."""
+    if gate_up.is_cuda:
+        return _cu().silu_mul_clamp_quant(gate_up, limit)
+    return fp8_quant(ref.silu_mul_clamp(gate_up, limit))
 
 
 def add_cast(routed, shared, num_valid=None):
@@ -105,14 +114,15 @@ def q_kv_norm_rope_store(q, kv, positions, kv_w, eps, spec, swa_cache, out_loc, 
 
 
 # --------------------------------------------------------------------------- hyper-connections
-def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None):
-    """Returns (y, post, comb); with ``norm_w`` y is additionally RMS-normalised (fused on CUDA)."""
+def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None, want_q: bool = False):
+    """Returns (y, post, comb); with ``norm_w`` y is additionally RMS-normalised (fused on CUDA); with ``want_q``
+    a fourth item, the (e4m3, scales) quantisation of y (also fused on CUDA)."""
     if x.is_cuda:
-        return _cu().hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w)
+        return _cu().hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w, want_q)
     y, post, comb = ref.hc_pre(x, fn, scale, base, iters, eps, norm_eps)
     if norm_w is not None:
         y = ref.rms_norm(y, norm_w, norm_eps)
-    return y, post, comb
+    return (y, post, comb, fp8_quant(y)) if want_q else (y, post, comb)
 
 
 def hc_post(y, residual, post, comb):

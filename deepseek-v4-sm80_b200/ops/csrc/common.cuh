@@ -276,6 +276,35 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ __nv_bfloat16 f2bf(float v) { return __float2bfloat16_rn(v); }
 
+// ---------------------------------------------------------------- FP8 activation quantisation (shared by the fused producers)
+// scale = 2^ceil(log2(max(absmax, 1e-4) / 448)); q = e4m3_rn(clamp(x / scale)), one scale per (row, 128 columns)
+__device__ __forceinline__ float pow2_ceil_scale(float amax) {
+  const float v = __fdiv_rn(fmaxf(amax, 1e-4f), 448.f);
+  const uint32_t b = __float_as_uint(v);
+  int e = (int)((b >> 23) & 0xff) - 127 + ((b & 0x7fffff) ? 1 : 0);
+  return __uint_as_float((uint32_t)(e + 127) << 23);
+}
+// v: 8 consecutive (already bf16-rounded) values of one row starting at column `col` (a multiple of 8).  The 16
+// lanes that share (lane / 16) hold one 128-column block; every lane of the warp must call this together.
+__device__ __forceinline__ void quant8_store(const float (&v)[8], uint8_t* __restrict__ qrow, float* __restrict__ srow,
+                                             int col) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float sc = pow2_ceil_scale(amax);
+  const float inv = 1.f / sc;  // exact: power of two
+  uint32_t w[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float c = fminf(fmaxf(v[i] * inv, -448.f), 448.f);
+    w[i >> 2] |= (uint32_t)__nv_cvt_float_to_fp8(c, __NV_SATFINITE, __NV_E4M3) << (8 * (i & 3));
+  }
+  *reinterpret_cast<uint2*>(qrow + col) = make_uint2(w[0], w[1]);
+  if ((threadIdx.x & 15) == 0) srow[col >> 7] = sc;
+}
+
 // host side -----------------------------------------------------------------
 // Launches `kernel` with programmatic dependent launch allowed (set DSV4_PDL=0 in the environment to launch plainly).
 bool dsv4_pdl_enabled();

@@ -42,7 +42,8 @@ __global__ void embed_kernel(const int* __restrict__ ids, const uint4* __restric
 // ------------------------------------------------------------------ RMSNorm (D <= 8192, D % 8 == 0)
 __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
                                                        const __nv_bfloat16* __restrict__ w,
-                                                       __nv_bfloat16* __restrict__ out, int ldo, int d, float eps) {
+                                                       __nv_bfloat16* __restrict__ out, int ldo, int d, float eps,
+                                                       uint8_t* __restrict__ q_out, float* __restrict__ s_out) {
   pdl_entry();
   __shared__ float sh[32];
   const int row = blockIdx.x;
@@ -86,18 +87,21 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __re
         po[k] = __floats2bfloat162_rn(a, b);
       }
       *reinterpret_cast<uint4*>(out + (size_t)row * ldo + i) = o;
+      if (q_out) {  // fused FP8 quantisation of the rounded result (needs d % 256 == 0: whole warps)
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 t = __bfloat1622float2(po[k]);
+          f[2 * k] = t.x, f[2 * k + 1] = t.y;
+        }
+        quant8_store(f, q_out + (size_t)row * d, s_out + (size_t)row * (d / 128), i);
+      }
     }
   }
 }
 
 // ------------------------------------------------------------------ FP8 activation quantisation
 // scale = 2^ceil(log2(max(absmax, 1e-4) / 448)); q = e4m3_rn(clamp(x / scale)).  One warp per (row, block).
-__device__ __forceinline__ float pow2_ceil_scale(float amax) {
-  const float v = __fdiv_rn(fmaxf(amax, 1e-4f), 448.f);
-  const uint32_t b = __float_as_uint(v);
-  int e = (int)((b >> 23) & 0xff) - 127 + ((b & 0x7fffff) ? 1 : 0);
-  return __uint_as_float((uint32_t)(e + 127) << 23);
-}
 template <int BLOCK>
 __global__ void fp8_quant_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ q,
                                  float* __restrict__ s, int rows, int k) {
@@ -155,6 +159,38 @@ __global__ void silu_mul_clamp_kernel(const __nv_bfloat16* __restrict__ gu, __nv
   }
   const float a0 = g0 / (1.f + expf(-g0)) * u0, a1 = g1 / (1.f + expf(-g1)) * u1;
   *reinterpret_cast<__nv_bfloat162*>(out + (size_t)row * inter + c) = __floats2bfloat162_rn(a0, a1);
+}
+
+// Same activation, 8 columns per thread, written only as e4m3 + block scales (the bf16 rounding of the activation
+// is kept: the quantiser sees the rounded values).  inter % 128 == 0, so 16 consecutive threads share a block and
+// every warp is whole.
+__global__ void silu_mul_clamp_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ q_out,
+                                            float* __restrict__ s_out, int rows, int inter, float limit) {
+  pdl_entry();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t total = (size_t)rows * inter / 8;
+  if (idx >= total) return;  // total is a multiple of 16 per row and rows * inter / 8 of 32 when inter % 256 == 0
+  const int row = (int)(idx / (inter / 8)), c = (int)(idx % (inter / 8)) * 8;
+  const uint4 ug = *reinterpret_cast<const uint4*>(gu + (size_t)row * 2 * inter + c);
+  const uint4 uu = *reinterpret_cast<const uint4*>(gu + (size_t)row * 2 * inter + inter + c);
+  const __nv_bfloat162* pg = reinterpret_cast<const __nv_bfloat162*>(&ug);
+  const __nv_bfloat162* pu = reinterpret_cast<const __nv_bfloat162*>(&uu);
+  float f[8];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 g = __bfloat1622float2(pg[k]), u = __bfloat1622float2(pu[k]);
+    float g0 = g.x, g1 = g.y, u0 = u.x, u1 = u.y;
+    if (limit > 0.f) {
+      g0 = fminf(g0, limit);
+      g1 = fminf(g1, limit);
+      u0 = fminf(fmaxf(u0, -limit), limit);
+      u1 = fminf(fmaxf(u1, -limit), limit);
+    }
+    const float2 r = __bfloat1622float2(
+        __floats2bfloat162_rn(g0 / (1.f + expf(-g0)) * u0, g1 / (1.f + expf(-g1)) * u1));
+    f[2 * k] = r.x, f[2 * k + 1] = r.y;
+  }
+  quant8_store(f, q_out + (size_t)row * inter, s_out + (size_t)row * (inter / 128), c);
 }
 
 // ------------------------------------------------------------------ out = bf16(float(a) + float(b)); padded rows -> 0
@@ -313,12 +349,15 @@ DSV4_API int dsv4_embed(const int* ids, const void* w, void* out, int t, int m, 
   dsv4_launch(embed_kernel, t, 256, 0, st, ids, (const uint4*)w, (uint4*)out, m, h / 8);
   return (int)cudaGetLastError();
 }
+// q_out / s_out (may be null): additionally writes the e4m3 quantisation of the result, dense [rows, d] with one
+// fp32 scale per 128 columns (needs d % 256 == 0).
 DSV4_API int dsv4_rms_norm(const void* x, int ldx, const void* w, void* out, int ldo, int rows, int d, float eps,
-                           cudaStream_t st) {
+                           void* q_out, float* s_out, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (d % 8 || d > 8192 || ldx % 8 || ldo % 8) return 121;
-  dsv4_launch(rms_norm_kernel, rows, 256, 0, st, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo,
-                                        d, eps);
+  if (q_out && (d % 256 || !s_out)) return 124;
+  dsv4_launch(rms_norm_kernel, rows, 256, 0, st, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w,
+              (__nv_bfloat16*)out, ldo, d, eps, (uint8_t*)q_out, s_out);
   return (int)cudaGetLastError();
 }
 DSV4_API int dsv4_fp8_quant(const void* x, int ldx, void* q, float* s, int rows, int k, int block, cudaStream_t st) {
@@ -330,6 +369,16 @@ DSV4_API int dsv4_fp8_quant(const void* x, int ldx, void* q, float* s, int rows,
     dsv4_launch(fp8_quant_kernel<128>, blocks, 256, 0, st, (const __nv_bfloat16*)x, ldx, (uint8_t*)q, s, rows, k);
   else
     dsv4_launch(fp8_quant_kernel<64>, blocks, 256, 0, st, (const __nv_bfloat16*)x, ldx, (uint8_t*)q, s, rows, k);
+  return (int)cudaGetLastError();
+}
+// SwiGLU with clamp whose only output is the e4m3 quantisation (dense [rows, inter], one scale per 128 columns).
+DSV4_API int dsv4_silu_mul_clamp_quant(const void* gu, void* q_out, float* s_out, int rows, int inter, float limit,
+                                       cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (inter % 128) return 125;
+  const size_t total = (size_t)rows * inter / 8;
+  dsv4_launch(silu_mul_clamp_quant_kernel, (unsigned)((total + 255) / 256), 256, 0, st, (const __nv_bfloat16*)gu,
+              (uint8_t*)q_out, s_out, rows, inter, limit);
   return (int)cudaGetLastError();
 }
 DSV4_API int dsv4_silu_mul_clamp(const void* gu, void* out, int rows, int inter, float limit, cudaStream_t st) {

@@ -24,7 +24,8 @@ __global__ void __launch_bounds__(256) hc_pre_kernel(const __nv_bfloat16* __rest
                                                      const __nv_bfloat16* __restrict__ norm_w,
                                                      __nv_bfloat16* __restrict__ y, float* __restrict__ post,
                                                      float* __restrict__ comb, int h, int iters, float eps,
-                                                     float norm_eps, float rms_eps) {
+                                                     float norm_eps, float rms_eps, uint8_t* __restrict__ q_out,
+                                                     float* __restrict__ s_out) {
   pdl_entry();
   extern __shared__ __align__(16) uint8_t hc_smem[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(hc_smem);  // [4*h]
@@ -51,10 +52,20 @@ __global__ void __launch_bounds__(256) hc_pre_kernel(const __nv_bfloat16* __rest
   // mix rows: taken from a tensor-core GEMM over all tokens when the caller ran one (every CTA re-reading the
   // [MIX, 4h] matrix costs more than the rest of the kernel), else warp w computes rows w, w+8, ...
   if (mixes_in) {
-    if (tid < MIX) {  // split-K partial products, added in split order
-      float a = 0.f;
-      for (int p = 0; p < n_part; ++p) a += __ldg(mixes_in + (size_t)p * part_stride + (size_t)t * ld_mix + tid);
-      mixes[tid] = a;
+    // split-K partial products: warp w adds splits w, w + 8, ..., then the eight sums are added in warp order
+    // (a fixed tree, so the result does not depend on timing)
+    __shared__ float part_s[8][32];
+    float a = 0.f;
+    if (lane < MIX)
+      for (int p = warp; p < n_part; p += 8)
+        a += __ldg(mixes_in + (size_t)p * part_stride + (size_t)t * ld_mix + lane);
+    part_s[warp][lane] = a;
+    __syncthreads();
+    if (tid < MIX) {
+      float m = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < 8; ++w8) m += part_s[w8][tid];
+      mixes[tid] = m;
     }
   } else
   for (int r = warp; r < MIX; r += 8) {
@@ -168,6 +179,15 @@ __global__ void __launch_bounds__(256) hc_pre_kernel(const __nv_bfloat16* __rest
         po[k] = __floats2bfloat162_rn(a, b);
       }
       *reinterpret_cast<uint4*>(y + (size_t)t * h + i) = o;
+      if (q_out) {  // fused FP8 quantisation of the rounded result (h % 256 == 0: whole warps)
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 tt = __bfloat1622float2(po[k]);
+          f[2 * k] = tt.x, f[2 * k + 1] = tt.y;
+        }
+        quant8_store(f, q_out + (size_t)t * h, s_out + (size_t)t * (h / 128), i);
+      }
     }
   }
 }
@@ -232,9 +252,10 @@ DSV4_API int dsv4_hc_pre(const void* x, const void* fn, const float* mixes, int 
                          long long part_stride, const float* scale,
                          const float* base, const void* norm_w,
                          void* y, float* post, float* comb, int t, int h, int mix_rows, int iters, float eps,
-                         float norm_eps, float rms_eps, cudaStream_t st) {
+                         float norm_eps, float rms_eps, void* q_out, float* s_out, cudaStream_t st) {
   if (t <= 0) return 0;
   if (h % 8 || h > 4096) return 130;
+  if (q_out && (h % 256 || !s_out)) return 133;
   const int smem = kM * h * 2;
   if (mix_rows == 24) {
     static bool set = false;
@@ -244,7 +265,7 @@ DSV4_API int dsv4_hc_pre(const void* x, const void* fn, const float* mixes, int 
     }
     dsv4_launch(hc_pre_kernel<24>, t, 256, smem, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)fn, mixes, ld_mix, n_part, part_stride, scale, base,
                                            (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)y, post, comb, h, iters, eps,
-                                           norm_eps, rms_eps);
+                                           norm_eps, rms_eps, (uint8_t*)q_out, s_out);
   } else if (mix_rows == 4) {
     static bool set4 = false;
     if (!set4) {
@@ -253,7 +274,7 @@ DSV4_API int dsv4_hc_pre(const void* x, const void* fn, const float* mixes, int 
     }
     dsv4_launch(hc_pre_kernel<4>, t, 256, smem, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)fn, mixes, ld_mix, n_part, part_stride, scale, base,
                                           (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)y, post, comb, h, iters, eps,
-                                          norm_eps, rms_eps);
+                                          norm_eps, rms_eps, (uint8_t*)q_out, s_out);
   } else {
     return 131;
   }

@@ -42,7 +42,14 @@ __global__ void moe_topk_kernel(const float* __restrict__ scores, const float* _
   // scores may come as n_part split-K partial products (spaced part_stride floats apart), added here in order
   auto score_at = [&](int j) {
     float a = 0.f;
-    for (int q = 0; q < n_part; ++q) a += __ldg(scores + (size_t)q * part_stride + (size_t)row * e + j);
+    const float* sp = scores + (size_t)row * e + j;
+    int q = 0;
+    for (; q + 4 <= n_part; q += 4) {  // four loads in flight, added in split order
+      const float v0 = __ldg(sp + (size_t)q * part_stride), v1 = __ldg(sp + (size_t)(q + 1) * part_stride);
+      const float v2 = __ldg(sp + (size_t)(q + 2) * part_stride), v3 = __ldg(sp + (size_t)(q + 3) * part_stride);
+      a = (((a + v0) + v1) + v2) + v3;
+    }
+    for (; q < n_part; ++q) a += __ldg(sp + (size_t)q * part_stride);
     return a;
   };
   if (row >= t_rows) return;

@@ -55,13 +55,26 @@ def embed(ids, weight, m: int):
     return out
 
 
-def rms_norm(x, weight, eps: float):
+def _quant_out(rows, d, device, want_q):
+    if not want_q or d % 256:
+        return None, None
+    return (torch.empty(rows, d, dtype=torch.float8_e4m3fn, device=device),
+            torch.empty(rows, d // 128, dtype=torch.float32, device=device))
+
+
+def rms_norm(x, weight, eps: float, want_q: bool = False):
+    """want_q: also returns the (e4m3, scales) quantisation of the result, written by the same kernel."""
     d = x.shape[-1]
     x2 = x if x.dim() == 2 else x.reshape(-1, d)
     assert x2.stride(-1) == 1
     out = torch.empty(x2.shape[0], d, dtype=x.dtype, device=x.device)
-    nv.call("rms_norm", nv.ptr(x2), I(x2.stride(0)), nv.ptr(weight), nv.ptr(out), I(d), I(x2.shape[0]), I(d), F(eps))
-    return out.reshape(*x.shape[:-1], d)
+    q, s = _quant_out(x2.shape[0], d, x.device, want_q)
+    nv.call("rms_norm", nv.ptr(x2), I(x2.stride(0)), nv.ptr(weight), nv.ptr(out), I(d), I(x2.shape[0]), I(d), F(eps),
+            nv.ptr(q), nv.ptr(s))
+    out = out.reshape(*x.shape[:-1], d)
+    if want_q:
+        return out, ((q, s) if q is not None else fp8_quant(out))
+    return out
 
 
 def fp8_quant(x, block: int = 128):
@@ -80,6 +93,18 @@ def silu_mul_clamp(gate_up, limit):
     out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
     nv.call("silu_mul_clamp", nv.ptr(gate_up), nv.ptr(out), I(rows), I(two_i // 2), F(limit or 0.0))
     return out
+
+
+def silu_mul_clamp_quant(gate_up, limit):
+    """SwiGLU with clamp straight to (e4m3, scales); the bf16 activation is not materialised."""
+    rows, two_i = gate_up.shape
+    inter = two_i // 2
+    if inter % 128:
+        return fp8_quant(silu_mul_clamp(gate_up, limit))
+    q = torch.empty(rows, inter, dtype=torch.float8_e4m3fn, device=gate_up.device)
+    s = torch.empty(rows, inter // 128, dtype=torch.float32, device=gate_up.device)
+    nv.call("silu_mul_clamp_quant", nv.ptr(gate_up), nv.ptr(q), nv.ptr(s), I(rows), I(inter), F(limit or 0.0))
+    return q, s
 
 
 def add_cast(routed, shared, num_valid=None):
@@ -118,17 +143,20 @@ def _hc_mixes(x, fn):
     return gemm_bf16_partials(x.reshape(t, -1), fn)
 
 
-def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None):
+def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None, want_q: bool = False):
     t, m, h = x.shape
     assert m == 4 and x.is_contiguous()
     y = torch.empty(t, h, dtype=x.dtype, device=x.device)
+    q, s = _quant_out(t, h, x.device, want_q)
     post = torch.empty(t, m, dtype=torch.float32, device=x.device)
     comb = torch.empty(t, m, m, dtype=torch.float32, device=x.device)
     mixes = _hc_mixes(x, fn)
     nv.call("hc_pre", nv.ptr(x), nv.ptr(fn), nv.ptr(mixes), I(mixes.stride(1)), I(mixes.shape[0]),
             L(mixes.stride(0)), nv.ptr(scale), nv.ptr(base),
             nv.ptr(norm_w), nv.ptr(y), nv.ptr(post), nv.ptr(comb), I(t), I(h), I(24), I(iters), F(eps), F(norm_eps),
-            F(norm_eps))
+            F(norm_eps), nv.ptr(q), nv.ptr(s))
+    if want_q:
+        return y, post, comb, ((q, s) if q is not None else fp8_quant(y))
     return y, post, comb
 
 
@@ -147,7 +175,7 @@ def hc_head(x, fn, scale, base, eps, norm_eps, norm_w=None):
     nv.call("hc_pre", nv.ptr(x), nv.ptr(fn), nv.ptr(mixes), I(mixes.stride(1)), I(mixes.shape[0]),
             L(mixes.stride(0)), nv.ptr(scale), nv.ptr(base),
             nv.ptr(norm_w), nv.ptr(y), nv.ptr(None), nv.ptr(None), I(t), I(h), I(4), I(0), F(eps), F(norm_eps),
-            F(norm_eps))
+            F(norm_eps), nv.ptr(None), nv.ptr(None))
     return y
 
 
