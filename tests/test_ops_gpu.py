@@ -299,6 +299,36 @@ def test_moe_full_size_repeatable(e_local, m):
     close(got, exp, atol=0.13, rtol=3e-2)
 
 
+def test_fused_quant_matches_separate_quant():
+    """The producers that also write FP8 (rms_norm, hc_pre, SwiGLU) give exactly what fp8_quant gives on their
+    bf16 result."""
+    from minisgl.ops import cuda as C
+
+    g = torch.Generator().manual_seed(21)
+    x = (torch.randn(40, 1024, generator=g) * 3).to(torch.bfloat16).to(DEV)
+    w = torch.rand(1024, generator=g).to(torch.bfloat16).to(DEV)
+    y, (q, s) = O.rms_norm(x, w, 1e-6, want_q=True)
+    q2, s2 = O.fp8_quant(y)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s, s2)
+
+    gu = (torch.randn(33, 2 * 512, generator=g) * 4).to(torch.bfloat16).to(DEV)
+    qa, sa = O.silu_mul_clamp_quant(gu, 7.0)
+    qb, sb = O.fp8_quant(O.silu_mul_clamp(gu, 7.0))
+    assert torch.equal(qa.view(torch.uint8), qb.view(torch.uint8)) and torch.equal(sa, sb)
+
+    t, h = 24, 1024
+    xs = (torch.randn(t, 4, h, generator=g)).to(torch.bfloat16).to(DEV)
+    fn = (torch.randn(24, 4 * h, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    scale = torch.rand(3, generator=g).to(DEV)
+    base = torch.randn(24, generator=g).to(DEV) * 0.1
+    nw = torch.rand(h, generator=g).to(torch.bfloat16).to(DEV)
+    yy, post, comb, (qh, sh) = O.hc_pre(xs, fn, scale, base, 20, 1e-6, 1e-6, nw, want_q=True)
+    q3, s3 = O.fp8_quant(yy)
+    assert torch.equal(qh.view(torch.uint8), q3.view(torch.uint8)) and torch.equal(sh, s3)
+    y0, p0, c0 = O.hc_pre(xs, fn, scale, base, 20, 1e-6, 1e-6, nw)
+    assert torch.equal(y0, yy) and torch.equal(p0, post) and torch.equal(c0, comb)
+
+
 def test_sampling():
     g = torch.Generator().manual_seed(7)
     b, v = 6, 129280
