@@ -25,8 +25,17 @@ __global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __r
   __syncthreads();
   if (ok) {
     for (int r = blockIdx.x; r < rows; r += gridDim.x)
-      for (int i = threadIdx.x; i < c8; i += blockDim.x)
-        reinterpret_cast<uint4*>(out + (size_t)r * cols)[i] = comm_reduce16(comm, parity, (size_t)r * cols + i * 8);
+      for (int i = threadIdx.x; i < c8; i += 2 * blockDim.x) {
+        const int i1 = i + blockDim.x;
+        uint4 o0, o1;
+        if (i1 < c8) {
+          comm_reduce16x2(comm, parity, (size_t)r * cols + i * 8, (size_t)r * cols + i1 * 8, o0, o1);
+          reinterpret_cast<uint4*>(out + (size_t)r * cols)[i1] = o1;
+        } else {
+          o0 = comm_reduce16(comm, parity, (size_t)r * cols + i * 8);
+        }
+        reinterpret_cast<uint4*>(out + (size_t)r * cols)[i] = o0;
+      }
   }
   __syncthreads();
   if (threadIdx.x == 0) comm_finish(comm, gridDim.x);

@@ -73,16 +73,25 @@ __device__ __forceinline__ bool comm_wait(const CommCtx& c, int slot, uint32_t e
   return true;
 }
 // Sum `world` bf16x8 vectors (one per rank, same offset) in rank order, fp32 accumulate, round once.
-__device__ __forceinline__ uint4 comm_reduce16(const CommCtx& c, int parity, size_t elem_offset) {
-  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int p = 0; p < c.world; ++p) {
-    const uint4 u = ld_peer16(comm_data(c, p, parity) + elem_offset);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+// The loads are issued back to back before the first add: a peer load takes microseconds over NVLink, and a loop that
+// adds each vector before asking for the next one pays that latency `world` times.
+__device__ __forceinline__ void comm_gather16(const CommCtx& c, int parity, size_t elem_offset, uint4 (&v)[kMaxRanks]) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float2 f = __bfloat1622float2(h[k]);
-      acc[2 * k] += f.x;
-      acc[2 * k + 1] += f.y;
+  for (int p = 0; p < kMaxRanks; ++p)
+    if (p < c.world) v[p] = ld_peer16(comm_data(c, p, parity) + elem_offset);
+}
+__device__ __forceinline__ uint4 comm_sum16(const CommCtx& c, const uint4 (&v)[kMaxRanks]) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int p = 0; p < kMaxRanks; ++p) {
+    if (p < c.world) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[p]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+      }
     }
   }
   uint4 o;
@@ -90,6 +99,20 @@ __device__ __forceinline__ uint4 comm_reduce16(const CommCtx& c, int parity, siz
 #pragma unroll
   for (int k = 0; k < 4; ++k) ho[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
   return o;
+}
+__device__ __forceinline__ uint4 comm_reduce16(const CommCtx& c, int parity, size_t elem_offset) {
+  uint4 v[kMaxRanks];
+  comm_gather16(c, parity, elem_offset, v);
+  return comm_sum16(c, v);
+}
+// Two vectors at once (16 peer loads in flight per thread).
+__device__ __forceinline__ void comm_reduce16x2(const CommCtx& c, int parity, size_t off0, size_t off1, uint4& o0,
+                                                uint4& o1) {
+  uint4 v0[kMaxRanks], v1[kMaxRanks];
+  comm_gather16(c, parity, off0, v0);
+  comm_gather16(c, parity, off1, v1);
+  o0 = comm_sum16(c, v0);
+  o1 = comm_sum16(c, v1);
 }
 // Last CTA of the grid advances the channel epoch (call once per CTA, by one thread, at the very end).
 __device__ __forceinline__ void comm_finish(const CommCtx& c, int total_ctas) {

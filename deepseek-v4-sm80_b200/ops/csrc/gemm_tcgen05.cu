@@ -306,11 +306,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*sh_flag && grow < M) {
 #pragma unroll 1
-          for (int c8 = 0; c8 < BN; c8 += 8) {
+          for (int c8 = 0; c8 < BN; c8 += 16) {
             const int col = n0 + c8;
-            if (col < N)
+            if (col + 8 < N) {
+              uint4 o0, o1;
+              comm_reduce16x2(comm, epoch & 1, (size_t)grow * N + col, (size_t)grow * N + col + 8, o0, o1);
+              *reinterpret_cast<uint4*>(out + (size_t)grow * g.ldo + col) = o0;
+              *reinterpret_cast<uint4*>(out + (size_t)grow * g.ldo + col + 8) = o1;
+            } else if (col < N) {
               *reinterpret_cast<uint4*>(out + (size_t)grow * g.ldo + col) =
                   comm_reduce16(comm, epoch & 1, (size_t)grow * N + col);
+            }
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -629,8 +629,17 @@ __global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat1
   __syncthreads();
   if (ok) {
     for (int t = blockIdx.x; t < t_rows; t += gridDim.x)
-      for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8)
-        *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = comm_reduce16(comm, parity, (size_t)t * h + i);
+      for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 16) {
+        const int i1 = i + blockDim.x * 8;
+        uint4 o0, o1;
+        if (i1 < h) {
+          comm_reduce16x2(comm, parity, (size_t)t * h + i, (size_t)t * h + i1, o0, o1);
+          *reinterpret_cast<uint4*>(out + (size_t)t * h + i1) = o1;
+        } else {
+          o0 = comm_reduce16(comm, parity, (size_t)t * h + i);
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = o0;
+      }
   }
   __syncthreads();
   if (threadIdx.x == 0) comm_finish(comm, gridDim.x);
