@@ -1,0 +1,133 @@
+"""Scenario matrix over the offline engine: the same catalogue the reference's perf-matrix harness runs
+(benchmark/perf_matrix: P1K / P4K prompts x M concurrent requests, mixed arrival, one long resident prompt beside
+short ones, KV-pressure cases), each scenario through an instrumented ``LLM`` that records per-request TTFT / TPOT,
+engine step counts per phase and prefix-cache metrics.
+
+    python -m minisgl.benchmark.perf_matrix --dummy --layers 4 --scenarios P1K_M32 P1K_M128 MIXED_ARRIVAL
+
+With ``--dummy`` the model is random-init (``--layers`` trims its depth so that it fits a small GPU or a CPU run with
+the tiny config, ``--tiny``).  Prints one JSON object per scenario and a final summary list.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import time
+from dataclasses import dataclass
+from typing import Dict, List
+
+
+@dataclass(frozen=True)
+class Scenario:
+    name: str
+    prompt_lens: tuple          # one entry per request
+    output_len: int
+    arrival_gap_steps: int = 0  # 0: all requests present at the start; k: one new request every k engine steps
+    note: str = ""
+
+
+def catalogue(scale: float = 1.0) -> Dict[str, Scenario]:
+    def n(x):
+        return max(int(x * scale), 1)
+
+    c = {}
+    for p, tag in ((1024, "P1K"), (4096, "P4K")):
+        for m in (1, 8, 32, 64, 128, 256):
+            c[f"{tag}_M{m}"] = Scenario(f"{tag}_M{m}", (n(p),) * m, n(256), note="uniform wave")
+    c["MIXED_ARRIVAL"] = Scenario("MIXED_ARRIVAL", tuple(n(x) for x in (1024, 256, 4096, 512) * 16), n(128), 2,
+                                  "requests trickle in while others decode: exercises the mixed-phase policy")
+    c["LONG_RESIDENT_64K"] = Scenario("LONG_RESIDENT_64K", (n(65536),) + (n(512),) * 31, n(128), 0,
+                                      "one 64 K prompt beside 31 short ones: fair chunked prefill must not starve them")
+    c["PRESSURE_512K"] = Scenario("PRESSURE_512K", (n(8192),) * 64, n(256), 0, "512 Ki resident tokens")
+    c["PRESSURE_1M"] = Scenario("PRESSURE_1M", (n(16384),) * 64, n(256), 0, "1 Mi resident tokens: admission waits")
+    c["SHARED_PREFIX"] = Scenario("SHARED_PREFIX", (n(2048),) * 32, n(64), 4,
+                                  "identical prompts arriving over time: radix prefix hits")
+    return c
+
+
+def _percentile(xs: List[float], q: float) -> float:
+    if not xs:
+        return float("nan")
+    xs = sorted(xs)
+    return xs[min(int(q * (len(xs) - 1) + 0.5), len(xs) - 1)]
+
+
+def run_scenario(llm, sc: Scenario, seed: int = 0) -> dict:
+    import torch
+
+    from minisgl.core import SamplingParams
+
+    vocab = llm.engine.model_config.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    if sc.name == "SHARED_PREFIX":
+        base = torch.randint(0, vocab, (sc.prompt_lens[0],), generator=g, dtype=torch.int32)
+        prompts = [base.clone() for _ in sc.prompt_lens]
+    else:
+        prompts = [torch.randint(0, vocab, (p,), generator=g, dtype=torch.int32) for p in sc.prompt_lens]
+    steps0 = dict(getattr(llm, "phase_steps", {}))
+    t0 = time.perf_counter()
+    outs = llm.generate(prompts, SamplingParams(max_tokens=sc.output_len, ignore_eos=True),
+                        arrival_gap_steps=sc.arrival_gap_steps)
+    wall = time.perf_counter() - t0
+    ttft = [o.t_first - t0 for o in outs if o.t_first is not None]
+    tpot = []
+    for o in outs:
+        if len(o.t_tokens) > 1:
+            tpot.append((o.t_tokens[-1] - o.t_tokens[0]) / (len(o.t_tokens) - 1))
+    n_out = sum(len(o.token_ids) for o in outs)
+    steps1 = dict(getattr(llm, "phase_steps", {}))
+    return {
+        "scenario": sc.name, "note": sc.note, "requests": len(outs), "prompt_tokens": int(sum(sc.prompt_lens)),
+        "output_tokens": n_out, "wall_s": round(wall, 4), "output_tok_s": round(n_out / wall, 2),
+        "ttft_s": {"p50": _percentile(ttft, 0.5), "p99": _percentile(ttft, 0.99), "max": max(ttft) if ttft else None},
+        "tpot_ms": {"p50": 1e3 * _percentile(tpot, 0.5), "p99": 1e3 * _percentile(tpot, 0.99),
+                    "mean": 1e3 * statistics.fmean(tpot) if tpot else None},
+        "steps": {k: steps1.get(k, 0) - steps0.get(k, 0) for k in steps1},
+        "prefix": llm.cache.prefix_metrics_snapshot(),
+    }
+
+
+def main(argv=None) -> List[dict]:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="")
+    ap.add_argument("--dummy", action="store_true")
+    ap.add_argument("--tiny", action="store_true", help="tiny architecture (CPU-sized); implies --dummy")
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--scale", type=float, default=1.0, help="multiplies every length of the catalogue")
+    ap.add_argument("--max-running", type=int, default=256)
+    ap.add_argument("--device", default="cuda")
+    ap.add_argument("--page-size", type=int, default=256)
+    ap.add_argument("--num-pages", type=int, default=0, help="override the KV page count (CPU runs need it)")
+    ap.add_argument("--scenarios", nargs="*", default=["P1K_M32", "P1K_M128", "MIXED_ARRIVAL"])
+    ap.add_argument("--list", action="store_true")
+    a = ap.parse_args(argv)
+    cat = catalogue(a.scale)
+    if a.list:
+        for s in cat.values():
+            print(f"{s.name:20s} requests={len(s.prompt_lens):4d} prompt={max(s.prompt_lens):6d} out={s.output_len} {s.note}")
+        return []
+    from minisgl.llm import LLM
+    from minisgl.models.config import ModelConfig
+
+    kw = {}
+    if a.tiny or a.dummy or not a.model:
+        cfg = ModelConfig.tiny() if a.tiny else ModelConfig.flash()
+        kw = dict(model_config=cfg.with_layers(a.layers) if a.layers else cfg, use_dummy_weight=True)
+    longest = max(max(cat[s].prompt_lens) + cat[s].output_len for s in a.scenarios)
+    if a.num_pages:
+        kw["num_page_override"] = a.num_pages
+    llm = LLM(a.model, max_running_req=a.max_running, context_length=max(longest + 64, 4096), device=a.device,
+              page_size=a.page_size, **kw)
+    results = []
+    for name in a.scenarios:
+        res = run_scenario(llm, cat[name])
+        results.append(res)
+        if llm.tp.is_primary():
+            print(json.dumps(res), flush=True)
+    llm.shutdown()
+    return results
+
+
+if __name__ == "__main__":
+    main()

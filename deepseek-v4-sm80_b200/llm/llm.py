@@ -46,6 +46,13 @@ class LLM(Scheduler):
         self._results: Dict[int, RequestOutput] = {}
         self._next_uid = 0
         self._open = 0
+        self._gap = 0          # engine steps between two released requests (0: release by prefill budget)
+        self._since = 0
+
+    @property
+    def phase_steps(self) -> Dict[str, int]:
+        """Engine forwards so far, per phase (for scenario harnesses)."""
+        return {"prefill": self.stats.prefill_steps, "decode": self.stats.decode_steps}
 
     @staticmethod
     def _info_from_env() -> DistributedInfo:
@@ -59,6 +66,13 @@ class LLM(Scheduler):
             if self._open == 0:
                 raise RequestAllFinished()
             return []
+        if self._gap > 0:  # staggered arrival: one request every `gap` polls
+            self._since += 1
+            if self._since < self._gap and self._open_released > 0:
+                return []
+            self._since = 0
+            self._open_released += 1
+            return [self._queue.pop(0)]
         budget, out = self.config.max_extend_tokens, []
         while self._queue and (budget > 0 or not out):
             m = self._queue.pop(0)
@@ -94,9 +108,11 @@ class LLM(Scheduler):
         return TokenizeManager(self.tokenizer, self.config.model_path).encode_messages(prompt, reasoning_effort)
 
     def generate(self, prompts: Sequence[Any], sampling_params: Union[SamplingParams, Sequence[SamplingParams]],
-                 reasoning_effort: Optional[str] = None) -> List[RequestOutput]:
+                 reasoning_effort: Optional[str] = None, arrival_gap_steps: int = 0) -> List[RequestOutput]:
         """prompts: token-id lists / tensors, strings, or chat message lists.  Returns one RequestOutput per prompt
-        (token ids, decoded text when a tokenizer is available, finish reason, per-token host timestamps)."""
+        (token ids, decoded text when a tokenizer is available, finish reason, per-token host timestamps).
+        ``arrival_gap_steps`` > 0 releases one request every that many scheduler polls instead of all at once."""
+        self._gap, self._since, self._open_released = int(arrival_gap_steps), 0, 0
         if isinstance(sampling_params, SamplingParams):
             sampling_params = [sampling_params] * len(prompts)
         uids = []

@@ -10,14 +10,17 @@ class StatsTracker:
         self.t0 = clock()
         self.prompt_tokens = self.gen_tokens = 0
         self.total_prompt = self.total_gen = 0
+        self.prefill_steps = self.decode_steps = 0
 
     def on_prefill(self, n: int) -> None:
         self.prompt_tokens += n
         self.total_prompt += n
+        self.prefill_steps += 1
 
     def on_decode(self, n: int) -> None:
         self.gen_tokens += n
         self.total_gen += n
+        self.decode_steps += 1
 
     def maybe_report(self, running: int, waiting: int, kv_used: float):
         now = self.clock()

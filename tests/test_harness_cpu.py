@@ -1,0 +1,33 @@
+"""The harnesses that need no GPU: static audit + census, scheduler policy simulation, scenario catalogue."""
+from minisgl.benchmark import audit, perf_matrix, scheduler_sim
+
+
+def test_static_audit_is_clean():
+    rep = audit.audit()
+    assert rep["violations"] == [], rep["violations"]
+    assert rep["num_kernels"] >= 25 and rep["num_exports"] >= 30
+    assert rep["lines"]["tests"] > 500
+
+
+def test_scheduler_sim_long_prefill_does_not_starve_short_prompts():
+    res = scheduler_sim.simulate(scheduler_sim.scenario("long_prefill"))
+    done = res["prefill_done_step"]
+    assert all(done[u] <= 1 for u in range(1, 16))       # short prompts finish in the first prefill forward(s)
+    assert done[0] > 5                                     # the 64 K prompt takes many chunks
+    assert res["inter_token_ms"]["max"] < 60               # decodes keep running in between (2 048-token chunks)
+    # never two prefills back to back while decodes are runnable (the short requests decode for 32 tokens)
+    assert "PP" not in res["first_steps"][1:30]
+
+
+def test_scheduler_sim_mixed_policy_bounds_decode_gaps():
+    calm = scheduler_sim.simulate(scheduler_sim.scenario("mixed"), max_consecutive_decode=4)
+    eager = scheduler_sim.simulate(scheduler_sim.scenario("mixed"), max_consecutive_decode=1)
+    assert eager["ttft_ms"]["p99"] <= calm["ttft_ms"]["p99"]       # more prefill turns -> earlier first tokens
+    assert calm["inter_token_ms"]["p99"] < 40
+
+
+def test_perf_matrix_catalogue():
+    cat = perf_matrix.catalogue()
+    assert {"P1K_M128", "P4K_M256", "MIXED_ARRIVAL", "LONG_RESIDENT_64K", "PRESSURE_1M"} <= set(cat)
+    assert len(cat["P1K_M128"].prompt_lens) == 128 and cat["P1K_M128"].prompt_lens[0] == 1024
+    assert sum(cat["PRESSURE_1M"].prompt_lens) == 1 << 20
