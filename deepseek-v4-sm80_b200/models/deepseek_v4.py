@@ -14,6 +14,7 @@ fp32 PyTorch oracle.  Differences by design:
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Any, Dict, Optional
 
@@ -70,6 +71,32 @@ class DSV4Model:
         e_local = weights["L0.moe.w13"].shape[0]
         self.expert_base = self.comm.rank * e_local if (moe_mode == "ep" and tp > 1) else 0
         self.qat = cfg.nope_head_dim % 64 == 0
+        if any(t.is_cuda for t in (weights["embed.weight"],)):
+            from ..ops import native
+
+            # the weights of this model are never written after loading: let the GEMMs fetch them ahead of the
+            # dependent-launch wait
+            native.check(native.cuda_lib().dsv4_gemm_set_weight_prefetch(1), "dsv4_gemm_set_weight_prefetch")
+        self._side = None  # second CUDA stream for branches that do not depend on each other (created on first use)
+
+    # ------------------------------------------------------------------ independent branches on a second stream
+    def _fork(self, ref: torch.Tensor):
+        """Context in which kernels go to the side stream, ordered after everything issued so far on the current
+        stream.  The compressor / indexer-cache branch of attention and the shared expert do not depend on the main
+        chain, and each of their kernels fills only part of the GPU, so they run beside it (also inside a captured
+        CUDA graph, where the fork and the join become graph edges).  On CPU it is a no-op."""
+        import contextlib
+
+        if not ref.is_cuda or os.environ.get("MINISGL_SINGLE_STREAM", "0") == "1":
+            return contextlib.nullcontext()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=ref.device)
+        self._side.wait_stream(torch.cuda.current_stream(ref.device))
+        return torch.cuda.stream(self._side)
+
+    def _join(self, ref: torch.Tensor) -> None:
+        if ref.is_cuda and self._side is not None and os.environ.get("MINISGL_SINGLE_STREAM", "0") != "1":
+            torch.cuda.current_stream(ref.device).wait_stream(self._side)
 
     # ------------------------------------------------------------------ blocks
     def _fp8_linear(self, x, name: str, xq=None):
@@ -86,6 +113,24 @@ class DSV4Model:
         ps = self.pool.page_size
         if yq is None:
             yq = O.fp8_quant(y)
+        iw = None
+        if ratio:
+            # compressor (and indexer cache) branch: depends only on y, meets the query chain at the selection
+            with self._fork(y):
+                if ratio == 4:
+                    iw = O.gemm_bf16(y, w[p + "idx.weights_proj"])
+                    n1 = w[p + "comp.wkv_gate"].shape[0]
+                    both = O.gemm_bf16(y, w[p + "comp_all.wkv_gate"], out_dtype=torch.float32)  # one GEMM, two slices
+                    proj, proj_i = both[:, :n1], both[:, n1:]
+                    pooled_i = O.compress(proj_i, fb, 4, cfg.index_head_dim, w[p + "idx.comp.ape"], kvv["idx_ring"],
+                                          kvv["idx_ckpt"], ps)
+                    O.indexer_kv_store(pooled_i, fb, w[p + "idx.comp.norm"], cfg.rms_norm_eps, rope, kvv["idx_vals"],
+                                       kvv["idx_scale"], ps)
+                else:
+                    proj = O.gemm_bf16(y, w[p + "comp.wkv_gate"], out_dtype=torch.float32)
+                pooled = O.compress(proj, fb, ratio, cfg.head_dim, w[p + "comp.ape"], kvv["ring"], kvv.get("ckpt"),
+                                    ps)
+                O.compress_store(pooled, fb, w[p + "comp.norm"], cfg.rms_norm_eps, rope, kvv["comp"], ps, ratio)
         qkv = O.gemm_fp8(yq[0], yq[1], w[p + "wqkv_a.weight"], w[p + "wqkv_a.scale"])
         q_lora, qlq = O.rms_norm(qkv[:, : cfg.q_lora_rank], w[p + "q_norm.weight"], cfg.rms_norm_eps, want_q=True)
         kv = qkv[:, cfg.q_lora_rank:]
@@ -96,19 +141,12 @@ class DSV4Model:
         if ratio == 4:
             iq = O.gemm_fp8(qlq[0], qlq[1], w[p + "idx.wq_b.weight"], w[p + "idx.wq_b.scale"])
             iq = iq.view(t, cfg.index_n_heads, cfg.index_head_dim)
-            iw = O.gemm_bf16(y, w[p + "idx.weights_proj"])
+        if ratio:
+            self._join(y)
+        if ratio == 4:
             qc, wf = O.indexer_q_encode(iq, iw, fb.positions, rope, cfg.index_head_dim ** -0.5,
                                         cfg.index_n_heads ** -0.5)
-            proj = O.gemm_bf16(y, w[p + "idx.comp.wkv_gate"], out_dtype=torch.float32)
-            pooled = O.compress(proj, fb, 4, cfg.index_head_dim, w[p + "idx.comp.ape"], kvv["idx_ring"],
-                                kvv["idx_ckpt"], ps)
-            O.indexer_kv_store(pooled, fb, w[p + "idx.comp.norm"], cfg.rms_norm_eps, rope, kvv["idx_vals"],
-                               kvv["idx_scale"], ps)
             topk_idx, topk_len = O.indexer_select(qc, wf, kvv["idx_vals"], kvv["idx_scale"], fb, ps, cfg.index_topk)
-        if ratio:
-            proj = O.gemm_bf16(y, w[p + "comp.wkv_gate"], out_dtype=torch.float32)
-            pooled = O.compress(proj, fb, ratio, cfg.head_dim, w[p + "comp.ape"], kvv["ring"], kvv.get("ckpt"), ps)
-            O.compress_store(pooled, fb, w[p + "comp.norm"], cfg.rms_norm_eps, rope, kvv["comp"], ps, ratio)
         o = O.attention(q, fb, kvv["swa"], self.pool.swa_map, kvv.get("comp"), ratio, topk_idx, topk_len,
                         w[p + "sink"], cfg.head_dim ** -0.5, ps, cfg.window_size)
         o = O.rope_tail(o, fb.positions, rope, inverse=True)
@@ -121,14 +159,15 @@ class DSV4Model:
 
     def moe(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None) -> torch.Tensor:
         cfg, w, p = self.cfg, self.w, f"L{l}.moe."
+        if yq is None:
+            yq = O.fp8_quant(y)
+        with self._fork(y):  # shared expert beside the router / planning chain
+            gu = O.gemm_fp8(yq[0], yq[1], w[p + "sh_gate_up.weight"], w[p + "sh_gate_up.scale"])
+            aq = O.silu_mul_clamp_quant(gu, cfg.swiglu_limit)
+            shared = O.gemm_fp8(aq[0], aq[1], w[p + "sh_down.weight"], w[p + "sh_down.scale"])
         idx, wt = O.moe_gate(y, w[p + "gate.weight"], w.get(p + "gate.bias"), cfg.num_experts_per_tok,
                              cfg.routed_scaling_factor, cfg.scoring_func, w.get(p + "gate.tid2eid"), fb.input_ids,
                              fb.num_valid)
-        if yq is None:
-            yq = O.fp8_quant(y)
-        gu = O.gemm_fp8(yq[0], yq[1], w[p + "sh_gate_up.weight"], w[p + "sh_gate_up.scale"])
-        aq = O.silu_mul_clamp_quant(gu, cfg.swiglu_limit)
-        shared = O.gemm_fp8(aq[0], aq[1], w[p + "sh_down.weight"], w[p + "sh_down.scale"])
         if y.is_cuda:
             # routed rows stay per route; the combine kernel sums them with the shared expert (and, with fused
             # communication, all-reduces the result in the same kernel)
@@ -137,6 +176,7 @@ class DSV4Model:
             rows, plan, mt = C.moe_routed(y, idx, wt, w[p + "w13"], w[p + "s13"], w[p + "w2"], w[p + "s2"],
                                           cfg.swiglu_limit, self.expert_base)
             t, k, h = y.shape[0], idx.shape[1], y.shape[1]
+            self._join(y)
             if getattr(self.comm, "fused", False):
                 return self.comm.moe_finalize_allreduce(rows, plan, mt, shared, fb.num_valid, t, k, h)
             out = C.moe_finalize(rows, plan, mt, shared, fb.num_valid, t, k, h)

@@ -132,9 +132,15 @@ def build_layer(cfg: ModelConfig, l: int, raw: Dict[str, torch.Tensor], rank: in
         out[p + "attn.idx.wq_b.scale"] = _scale_f32(g("attn.indexer.wq_b.scale"))
         out[p + "attn.idx.weights_proj"] = g("attn.indexer.weights_proj.weight").to(torch.bfloat16).contiguous()
         out[p + "attn.idx.comp.ape"] = g("attn.indexer.compressor.ape").float().contiguous()
-        out[p + "attn.idx.comp.wkv_gate"] = torch.cat(
+        idx_wkv_gate = torch.cat(
             [g("attn.indexer.compressor.wkv.weight"), g("attn.indexer.compressor.wgate.weight")], 0
-        ).to(torch.bfloat16).contiguous()
+        ).to(torch.bfloat16)
+        # both compressors read the same activations: one stacked weight (one GEMM), the two parts are row views of it
+        both = torch.cat([out[p + "attn.comp.wkv_gate"], idx_wkv_gate], 0).contiguous()
+        n1 = out[p + "attn.comp.wkv_gate"].shape[0]
+        out[p + "attn.comp_all.wkv_gate"] = both
+        out[p + "attn.comp.wkv_gate"] = both[:n1]
+        out[p + "attn.idx.comp.wkv_gate"] = both[n1:]
         out[p + "attn.idx.comp.norm"] = g("attn.indexer.compressor.norm.weight").float().contiguous()
     # MoE
     out[p + "moe.gate.weight"] = g("ffn.gate.weight").float().contiguous()

@@ -21,7 +21,7 @@ __device__ __forceinline__ float pow2_ceil_scale_c(float amax) {
 }
 
 // ------------------------------------------------------------------ C4 pooling
-__global__ void compress_pool4_kernel(const float* __restrict__ proj, const int* __restrict__ pos,
+__global__ void compress_pool4_kernel(const float* __restrict__ proj, int ldp, const int* __restrict__ pos,
                                       const int* __restrict__ slots, const int* __restrict__ page_table, int ld_pt,
                                       const float* __restrict__ ring, const float* __restrict__ ckpt,
                                       const float* __restrict__ ape, float* __restrict__ out, int d, int ps) {
@@ -47,8 +47,8 @@ __global__ void compress_pool4_kernel(const float* __restrict__ proj, const int*
       if (lp < 0) continue;
       const bool cur = cand >= 0 && slots[cand] == s && pos[cand] == lp;
       if (cur) {
-        kv[src] = proj[(size_t)cand * w4 + ko + f];
-        sc[src] = proj[(size_t)cand * w4 + so + f];
+        kv[src] = proj[(size_t)cand * ldp + ko + f];
+        sc[src] = proj[(size_t)cand * ldp + so + f];
       } else if (!right && (lp / ps) != (p / ps)) {
         const int page = page_table[(size_t)s * ld_pt + lp] / ps;
         const float* c = ckpt + ((size_t)page * 4 + (lp & 3)) * 2 * d;
@@ -73,7 +73,7 @@ __global__ void compress_pool4_kernel(const float* __restrict__ proj, const int*
   }
 }
 
-__global__ void compress_state4_kernel(const float* __restrict__ proj, const int* __restrict__ pos,
+__global__ void compress_state4_kernel(const float* __restrict__ proj, int ldp, const int* __restrict__ pos,
                                        const int* __restrict__ slots, const int* __restrict__ page_table, int ld_pt,
                                        float* __restrict__ ring, float* __restrict__ ckpt, int d, int ps, int t_rows) {
   pdl_entry();
@@ -82,7 +82,7 @@ __global__ void compress_state4_kernel(const float* __restrict__ proj, const int
   const int w4 = 4 * d;
   const int later = row + 8;
   const bool overwritten = later < t_rows && slots[later] == s && pos[later] == p + 8;
-  const float* src = proj + (size_t)row * w4;
+  const float* src = proj + (size_t)row * ldp;
   if (!overwritten) {
     float* dst = ring + ((size_t)s * 8 + (p & 7)) * w4;
     for (int f = threadIdx.x; f < w4; f += blockDim.x) dst[f] = src[f];
@@ -98,7 +98,7 @@ __global__ void compress_state4_kernel(const float* __restrict__ proj, const int
 }
 
 // ------------------------------------------------------------------ C128 pooling (generic ratio without overlap)
-__global__ void compress_pool128_kernel(const float* __restrict__ proj, const int* __restrict__ pos,
+__global__ void compress_pool128_kernel(const float* __restrict__ proj, int ldp, const int* __restrict__ pos,
                                         const int* __restrict__ slots, const float* __restrict__ ring,
                                         const float* __restrict__ ape, float* __restrict__ out, int d, int ratio) {
   pdl_entry();
@@ -127,7 +127,7 @@ __global__ void compress_pool128_kernel(const float* __restrict__ proj, const in
     for (int i = 0; i < ratio; ++i) {
       const int c = cur_row[i];
       if (c == -2) continue;
-      const float scv = c >= 0 ? proj[(size_t)c * w2 + d + f] + ape[(size_t)i * d + f]
+      const float scv = c >= 0 ? proj[(size_t)c * ldp + d + f] + ape[(size_t)i * d + f]
                                : ring[((size_t)s * ratio + i) * w2 + d + f];
       mx = fmaxf(mx, scv);
     }
@@ -137,8 +137,8 @@ __global__ void compress_pool128_kernel(const float* __restrict__ proj, const in
       if (c == -2) continue;
       float kvv, scv;
       if (c >= 0) {
-        kvv = proj[(size_t)c * w2 + f];
-        scv = proj[(size_t)c * w2 + d + f] + ape[(size_t)i * d + f];
+        kvv = proj[(size_t)c * ldp + f];
+        scv = proj[(size_t)c * ldp + d + f] + ape[(size_t)i * d + f];
       } else {
         const float* r = ring + ((size_t)s * ratio + i) * w2;
         kvv = r[f];
@@ -152,7 +152,7 @@ __global__ void compress_pool128_kernel(const float* __restrict__ proj, const in
   }
 }
 
-__global__ void compress_state128_kernel(const float* __restrict__ proj, const int* __restrict__ pos,
+__global__ void compress_state128_kernel(const float* __restrict__ proj, int ldp, const int* __restrict__ pos,
                                          const int* __restrict__ slots, const float* __restrict__ ape,
                                          float* __restrict__ ring, int d, int ratio, int t_rows) {
   pdl_entry();
@@ -161,7 +161,7 @@ __global__ void compress_state128_kernel(const float* __restrict__ proj, const i
   const int later = row + ratio;
   if (later < t_rows && slots[later] == s && pos[later] == p + ratio) return;
   const int w2 = 2 * d, i = p % ratio;
-  const float* src = proj + (size_t)row * w2;
+  const float* src = proj + (size_t)row * ldp;
   float* dst = ring + ((size_t)s * ratio + i) * w2;
   for (int f = threadIdx.x; f < d; f += blockDim.x) {
     dst[f] = src[f];
@@ -323,26 +323,26 @@ __global__ void indexer_q_encode_kernel(const __nv_bfloat16* __restrict__ q, con
 
 }  // namespace
 
-DSV4_API int dsv4_compress_pool(const float* proj, const int* pos, const int* slots, const int* page_table, int ld_pt,
+DSV4_API int dsv4_compress_pool(const float* proj, int ldp, const int* pos, const int* slots, const int* page_table, int ld_pt,
                                 const float* ring, const float* ckpt, const float* ape, float* out, int t, int d,
                                 int ratio, int ps, cudaStream_t st) {
   if (t <= 0) return 0;
   if (ratio == 4)
-    dsv4_launch(compress_pool4_kernel, t, d < 256 ? d : 256, 0, st, proj, pos, slots, page_table, ld_pt, ring, ckpt, ape, out, d,
+    dsv4_launch(compress_pool4_kernel, t, d < 256 ? d : 256, 0, st, proj, ldp, pos, slots, page_table, ld_pt, ring, ckpt, ape, out, d,
                                                           ps);
   else
-    dsv4_launch(compress_pool128_kernel, t, d < 256 ? d : 256, ratio * sizeof(int), st, proj, pos, slots, ring, ape, out, d,
+    dsv4_launch(compress_pool128_kernel, t, d < 256 ? d : 256, ratio * sizeof(int), st, proj, ldp, pos, slots, ring, ape, out, d,
                                                                               ratio);
   return (int)cudaGetLastError();
 }
-DSV4_API int dsv4_compress_state(const float* proj, const int* pos, const int* slots, const int* page_table, int ld_pt,
+DSV4_API int dsv4_compress_state(const float* proj, int ldp, const int* pos, const int* slots, const int* page_table, int ld_pt,
                                  float* ring, float* ckpt, const float* ape, int t, int d, int ratio, int ps,
                                  cudaStream_t st) {
   if (t <= 0) return 0;
   if (ratio == 4)
-    dsv4_launch(compress_state4_kernel, t, 256, 0, st, proj, pos, slots, page_table, ld_pt, ring, ckpt, d, ps, t);
+    dsv4_launch(compress_state4_kernel, t, 256, 0, st, proj, ldp, pos, slots, page_table, ld_pt, ring, ckpt, d, ps, t);
   else
-    dsv4_launch(compress_state128_kernel, t, 256, 0, st, proj, pos, slots, ape, ring, d, ratio, t);
+    dsv4_launch(compress_state128_kernel, t, 256, 0, st, proj, ldp, pos, slots, ape, ring, d, ratio, t);
   return (int)cudaGetLastError();
 }
 DSV4_API int dsv4_compress_store(const float* pooled, const int* pos, const int* out_loc, const void* w, float eps,

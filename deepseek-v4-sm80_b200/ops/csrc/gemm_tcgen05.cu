@@ -45,6 +45,7 @@ struct GemmArgs {
   int splits;
   float* ws;           // [tiles][splits][128][BN] fp32 partials
   int* counters;       // [tiles], zero between launches
+  int prefetch_b;      // the weight operand is not written by the kernel before this one: load it before pdl_wait()
   int cluster;         // > 0: the `splits` CTAs of a tile form one thread-block cluster and reduce over distributed
                        //      shared memory (no workspace, no atomics)
   long long partial_stride;  // > 0: split s writes its own partial product to out + s * partial_stride (no reduction;
@@ -137,9 +138,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
-  pdl_wait();  // barriers and tensor memory are set up; from here on the kernel touches global memory
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // Barriers and tensor memory are set up.  The weight operand does not depend on the kernel before this one, so the
+  // producer asks for the first ring of weight tiles BEFORE waiting for that kernel (under programmatic dependent
+  // launch this CTA is already resident while it drains): their HBM latency is paid in the shadow of the previous
+  // kernel.  Everything else (activation loads, scale reads, output writes) comes after pdl_wait().
+  const int pre = g.prefetch_b ? (nkt < S ? nkt : S) : 0;
+  if (warp == 0 && lane == 0) {
+    const int by = batch * g.b_row_pb + n0;
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(&full[i], Cfg::kStageBytes);
+      tma_load_2d(tiles + i * Cfg::kStageBytes + Cfg::kABytes, &tmB, &full[i], (kt0 + i) * BK, by);
+    }
+  }
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -147,9 +160,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int i = 0; i < nkt; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
+        uint8_t* a = tiles + s * Cfg::kStageBytes;
+        if (i < pre) {  // weights already requested above
+          tma_load_2d(a, &tmA, &full[s], ax + (kt0 + i) * BK, m0);
+          continue;
+        }
         if (!mbar_wait<32>(&empty[s], ph ^ 1, abort_flag, 1)) break;
         mbar_expect_tx(&full[s], Cfg::kStageBytes);
-        uint8_t* a = tiles + s * Cfg::kStageBytes;
         tma_load_2d(a, &tmA, &full[s], ax + (kt0 + i) * BK, m0);
         tma_load_2d(a + Cfg::kABytes, &tmB, &full[s], (kt0 + i) * BK, by);
       }
@@ -378,6 +395,8 @@ struct LaunchOpts {
   const CommCtx* comm = nullptr;
 };
 
+int g_weight_prefetch = 0;  // set by dsv4_gemm_set_weight_prefetch
+
 template <int BN, bool FP8, typename OutT>
 int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, int ldx, int ldw, int ldo, const float* sa,
                 const float* sb, int accumulate_out, cudaStream_t stream, const LaunchOpts& o) {
@@ -402,7 +421,7 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
     if ((long long)grid.x * grid.y > kCommSlots || o.splits != 1 || o.batches != 1) return 104;
   }
   GemmArgs g{M, N, K, ldo, sa, sb, o.sb_ld ? o.sb_ld : (K + 127) / 128, accumulate_out, o.a_col_pb, o.b_row_pb,
-             o.out_col_pb, o.splits, o.ws, o.counters, o.cluster, o.partial_stride};
+             o.out_col_pb, o.splits, o.ws, o.counters, g_weight_prefetch, o.cluster, o.partial_stride};
   if (o.cluster) {
     if (o.splits != 2 && o.splits != 4 && o.splits != 8) return 105;
     dsv4_launch_cluster(kern, grid, 192, Cfg::kSmemBytes, stream, o.splits, tmA, tmB, out, g, comm);
@@ -436,6 +455,14 @@ int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, in
 }
 
 }  // namespace
+
+// on != 0: the callers promise that the weight operand (w) of every GEMM launched from now on is not produced by the
+// kernel that precedes it in the stream (model weights are static), so its first tiles may be fetched before the
+// dependent-launch wait.  Off by default.
+DSV4_API int dsv4_gemm_set_weight_prefetch(int on) {
+  g_weight_prefetch = on ? 1 : 0;
+  return 0;
+}
 
 // Workspace floats needed for a split-K launch: tiles * splits * 128 * bn.
 DSV4_API long long dsv4_gemm_splitk_ws_elems(int M, int N, int bn, int batches, int splits) {

@@ -182,12 +182,12 @@ def hc_head(x, fn, scale, base, eps, norm_eps, norm_w=None):
 # --------------------------------------------------------------------------- compressors / indexer producers
 def compress(proj, fb, ratio: int, d: int, ape, ring, ckpt, ps: int):
     t = proj.shape[0]
-    assert proj.is_contiguous() and proj.dtype == torch.float32
+    assert proj.stride(1) == 1 and proj.dtype == torch.float32  # may be a column slice of a wider GEMM output
     out = torch.empty(t, d, dtype=torch.float32, device=proj.device)
     pt = fb.page_table
-    nv.call("compress_pool", nv.ptr(proj), _i32(fb.positions), _i32(fb.slots), _i32(pt), I(pt.stride(0)),
+    nv.call("compress_pool", nv.ptr(proj), I(proj.stride(0)), _i32(fb.positions), _i32(fb.slots), _i32(pt), I(pt.stride(0)),
             nv.ptr(ring), nv.ptr(ckpt), nv.ptr(ape), nv.ptr(out), I(t), I(d), I(ratio), I(ps))
-    nv.call("compress_state", nv.ptr(proj), _i32(fb.positions), _i32(fb.slots), _i32(pt), I(pt.stride(0)),
+    nv.call("compress_state", nv.ptr(proj), I(proj.stride(0)), _i32(fb.positions), _i32(fb.slots), _i32(pt), I(pt.stride(0)),
             nv.ptr(ring), nv.ptr(ckpt), nv.ptr(ape), I(t), I(d), I(ratio), I(ps))
     return out
 

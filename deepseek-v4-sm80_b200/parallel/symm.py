@@ -24,6 +24,12 @@ from ..ops import native as nv
 from ..ops.native import I
 from .info import DistributedInfo
 
+# Diagnosis only (MINISGL_SKIP_EXCHANGE=1): run the two fused call sites without their peer exchange, to read the
+# cost of the collectives off a benchmark.  The results are then wrong (each rank keeps its partial sums).
+import os as _os
+
+_SKIP_EXCHANGE = _os.environ.get("MINISGL_SKIP_EXCHANGE", "0") == "1"
+
 MAX_RANKS = 8
 
 
@@ -87,6 +93,10 @@ class SymmComm(Comm):
         m, k = xq.shape
         n = w.shape[0]
         self.counters["gemm_allreduce"] += 1
+        if _SKIP_EXCHANGE:
+            from ..ops import api as O
+
+            return O.gemm_fp8(xq, sx, w, ws)
         out = torch.empty(m, n, dtype=torch.bfloat16, device=xq.device)
         nv.call("gemm_fp8_allreduce", nv.ptr(xq), nv.ptr(w), nv.ptr(out), nv.ptr(sx), nv.ptr(ws), I(m), I(n), I(k),
                 I(xq.stride(0)), I(w.stride(0)), ctypes.byref(self.ctx[self.CH_ATTN]), I(bn))
@@ -102,6 +112,10 @@ class SymmComm(Comm):
 
     def moe_finalize_allreduce(self, rows, plan, max_tiles, shared, num_valid, t, topk, h) -> torch.Tensor:
         self.counters["moe_allreduce"] += 1
+        if _SKIP_EXCHANGE:
+            from ..ops import cuda as C
+
+            return C.moe_finalize(rows, plan, max_tiles, shared, num_valid, t, topk, h)
         out = torch.empty(t, h, dtype=rows.dtype, device=rows.device)
         nv.call("moe_finalize_allreduce", nv.ptr(rows), nv.ptr(plan), I(t * topk), I(max_tiles), nv.ptr(shared),
                 nv.ptr(out), nv.ptr(num_valid), I(t), I(topk), I(h), ctypes.byref(self.ctx[self.CH_MOE]))
