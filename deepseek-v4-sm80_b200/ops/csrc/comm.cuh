@@ -38,6 +38,9 @@ __device__ __forceinline__ __nv_bfloat16* comm_data(const CommCtx& c, int on_ran
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -51,25 +54,42 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
 
 // Called by ONE thread after the CTA's partial tile is written and the writers have synchronised.
 __device__ __forceinline__ void comm_publish(const CommCtx& c, int slot, uint32_t epoch) {
+  // one system-scope fence orders the tile before all flags; the flag stores themselves are then posted without
+  // waiting for one another (a release store per peer would pay an NVLink round trip each, in series)
   __threadfence_system();
-  for (int p = 0; p < c.world; ++p)
-    if (p != c.rank) st_release_sys(comm_flag(c, p, c.rank, slot), epoch);
+#pragma unroll
+  for (int p = 0; p < kMaxRanks; ++p)
+    if (p < c.world && p != c.rank) st_relaxed_sys(comm_flag(c, p, c.rank, slot), epoch);
 }
-// Called by ONE thread; returns false when a peer's flag did not arrive in time.
+// Called by ONE thread; returns false when a peer's flag did not arrive in time.  All peers' flags are polled
+// together (independent relaxed loads), then one acquire fence orders the data reads after them.
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ bool comm_wait(const CommCtx& c, int slot, uint32_t epoch) {
-  for (int p = 0; p < c.world; ++p) {
-    if (p == c.rank) continue;
-    const uint32_t* f = comm_flag(c, c.rank, p, slot);
-    if ((int)(ld_acquire_sys(f) - epoch) >= 0) continue;
-    const unsigned long long t0 = globaltimer_ns();
-    for (;;) {
-      if ((int)(ld_acquire_sys(f) - epoch) >= 0) break;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        dsv4_set_error(DSV4_ERR_PEER_TIMEOUT, p, slot);
+  unsigned long long t0 = 0;
+  for (int spin = 0;; ++spin) {
+    uint32_t v[kMaxRanks];
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p)
+      v[p] = (p < c.world && p != c.rank) ? ld_relaxed_sys(comm_flag(c, c.rank, p, slot)) : epoch;
+    int late = -1;
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p)
+      if ((int)(v[p] - epoch) < 0) late = p;
+    if (late < 0) break;
+    if ((spin & 63) == 63) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        dsv4_set_error(DSV4_ERR_PEER_TIMEOUT, late, slot);
         return false;
       }
     }
   }
+  __threadfence_system();
   return true;
 }
 // Sum `world` bf16x8 vectors (one per rank, same offset) in rank order, fp32 accumulate, round once.
