@@ -9,7 +9,8 @@ full model's shapes:
                         epilogue vs the same GEMM followed by NCCL
   * moe_combine       : expert-parallel routed experts (256/N experts per rank, uniform-random top-6 routing), with the
                         per-token route sum + shared expert + all-reduce in one kernel vs unfused finalize + NCCL
-Times are CUDA-event medians with an L2 flush before every timed call, reduced with MAX over ranks.  The roofline of a
+Times are per call inside a CUDA graph of `--iters` calls (no host launch gaps), with an L2 flush before every call
+whose own cost is subtracted, reduced with MAX over ranks.  The roofline of a
 fused call is the slower of FLOPs / measured GEMM peak and NVLink bytes / 770 GB/s (one-shot all-reduce: each GPU
 pulls (N-1) * M * 4096 * 2 bytes).
 """
@@ -37,23 +38,41 @@ def _peaks():
 
 
 def _time(fn, iters, flush):
+    """Microseconds per call, max over ranks.  `iters` calls are captured in one CUDA graph (as the engine runs
+    them: no host launch gaps) together with an L2 flush before each when `flush` is set; the flush-only graph is
+    timed too and subtracted."""
     from minisgl.benchmark.perf import flush_l2
 
-    for _ in range(3):
-        fn()
-    torch.cuda.synchronize()
-    ts = []
-    for _ in range(iters):
-        if flush:
-            flush_l2()
+    def graph_ms(body):
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            for _ in range(2):
+                body()
+        st.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for _ in range(iters):
+                body()
+        g.replay()
+        torch.cuda.synchronize()
         dist.barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        fn()
+        for _ in range(3):
+            g.replay()
         b.record()
         torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b) * 1e3)
-    t = torch.tensor([statistics.median(ts)], device="cuda")
+        return a.elapsed_time(b) / 3
+
+    if flush:
+        def body():
+            flush_l2()
+            fn()
+        ms = graph_ms(body) - graph_ms(flush_l2)
+    else:
+        ms = graph_ms(fn)
+    t = torch.tensor([ms * 1e3 / iters], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t)
 

@@ -148,8 +148,7 @@ class DSV4Model:
                                         cfg.index_n_heads ** -0.5)
             topk_idx, topk_len = O.indexer_select(qc, wf, kvv["idx_vals"], kvv["idx_scale"], fb, ps, cfg.index_topk)
         o = O.attention(q, fb, kvv["swa"], self.pool.swa_map, kvv.get("comp"), ratio, topk_idx, topk_len,
-                        w[p + "sink"], cfg.head_dim ** -0.5, ps, cfg.window_size)
-        o = O.rope_tail(o, fb.positions, rope, inverse=True)
+                        w[p + "sink"], cfg.head_dim ** -0.5, ps, cfg.window_size, out_rope=rope)
         o2 = O.gemm_bf16_grouped(o.reshape(t, self.h_local * cfg.head_dim), w[p + "wo_a.weight_bf16"], self.g_local)
         if getattr(self.comm, "fused", False):
             oq = O.fp8_quant(o2)

@@ -187,10 +187,12 @@ def indexer_select(qc, wf, vals, scales, fb, ps: int, k: int):
 
 # --------------------------------------------------------------------------- attention
 def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_len, sink, scale, ps: int,
-              window: int):
+              window: int, out_rope=None):
+    """``out_rope``: also rotate the last ``rotary_dim`` dims of every output row by minus its position (fused into
+    the kernel's epilogue on CUDA, :func:`rope_tail` with ``inverse=True`` on the oracle path)."""
     if q.is_cuda:
         return _cu().attention(q, fb, swa_cache, swa_map, comp_cache, ratio, topk_idx, topk_len, sink, scale, ps,
-                               window)
+                               window, out_rope)
     srows = swa_rows(fb, swa_map, ps, window)
     crows = None
     if ratio == 4:
@@ -198,7 +200,8 @@ def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_
         crows = comp_rows_from_idx(fb, idx, ps, 4)
     elif ratio:
         crows = comp_rows_all(fb, ps, ratio, max(fb.max_context // ratio, 1))
-    return ref.sparse_attention(q, comp_cache, crows, swa_cache, srows, sink, scale)
+    o = ref.sparse_attention(q, comp_cache, crows, swa_cache, srows, sink, scale)
+    return rope_tail(o, fb.positions, out_rope, inverse=True) if out_rope is not None else o
 
 
 # --------------------------------------------------------------------------- MoE

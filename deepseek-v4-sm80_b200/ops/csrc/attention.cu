@@ -15,6 +15,7 @@
 // the reference's two-source kernel semantics
 // (python/minisgl/kernel/csrc/jit/dsv4_sparse_attention_two_source_bf16.cu:77-168).
 #include "common.cuh"
+#include "rope.cuh"
 
 namespace {
 
@@ -66,6 +67,8 @@ struct AttnArgs {
   int ps;
   int window;
   const int* num_valid;
+  int out_rope;   // != 0: rotate the last rp.rotary_dim dims of every output head row by -position (the inverse
+  RopeParams rp;  //       RoPE the output projection expects), on the bf16-rounded values, in the epilogue
 };
 
 // row of 512 bf16 = 64 chunks of 16 B; chunk c of row r is stored at chunk (c ^ (r & 7))
@@ -263,15 +266,21 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
   {
     const int r0 = mt * 16 + (lane >> 2);
     const float i0 = 1.f / ls[r0], i1 = 1.f / ls[r0 + 8];
+    const float fpos = a.out_rope ? (float)a.pos[t] : 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int d0 = g * C::DW + nt * 8 + (lane & 3) * 2;
-      if (r0 < HL)
-        *reinterpret_cast<__nv_bfloat162*>(a.o + ((size_t)t * HL + r0) * D + d0) =
-            __floats2bfloat162_rn(acc[nt][0] * i0, acc[nt][1] * i0);
-      if (r0 + 8 < HL)
-        *reinterpret_cast<__nv_bfloat162*>(a.o + ((size_t)t * HL + r0 + 8) * D + d0) =
-            __floats2bfloat162_rn(acc[nt][2] * i1, acc[nt][3] * i1);
+      __nv_bfloat162 v0 = __floats2bfloat162_rn(acc[nt][0] * i0, acc[nt][1] * i0);
+      __nv_bfloat162 v1 = __floats2bfloat162_rn(acc[nt][2] * i1, acc[nt][3] * i1);
+      if (a.out_rope && d0 >= D - a.rp.rotary_dim) {  // interleaved pair (d0, d0 + 1) sits in this thread
+        float c, sn;
+        rope_cos_sin(a.rp, fpos, (d0 - (D - a.rp.rotary_dim)) >> 1, 1, c, sn);
+        const float2 f0 = __bfloat1622float2(v0), f1 = __bfloat1622float2(v1);
+        v0 = __floats2bfloat162_rn(f0.x * c - f0.y * sn, f0.x * sn + f0.y * c);
+        v1 = __floats2bfloat162_rn(f1.x * c - f1.y * sn, f1.x * sn + f1.y * c);
+      }
+      if (r0 < HL) *reinterpret_cast<__nv_bfloat162*>(a.o + ((size_t)t * HL + r0) * D + d0) = v0;
+      if (r0 + 8 < HL) *reinterpret_cast<__nv_bfloat162*>(a.o + ((size_t)t * HL + r0 + 8) * D + d0) = v1;
     }
   }
 }
@@ -296,12 +305,13 @@ DSV4_API int dsv4_sparse_attention(const void* q, void* o, const int* slots, con
                                    int ld_pt, const void* swa, const int* swa_map, const void* comp,
                                    const int* topk_idx, const int* topk_len, int topk_width, int mode, int ratio,
                                    const float* sink, float scale, int ps, int window, const int* num_valid, int t,
-                                   int heads, int d, cudaStream_t st) {
+                                   int heads, int d, int out_rope, RopeParams rp, cudaStream_t st) {
   if (t <= 0) return 0;
   if (d != D) return 300;
+  if (out_rope && (rp.rotary_dim <= 0 || rp.rotary_dim > 128 || rp.rotary_dim % 8)) return 303;
   AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)o, slots, pos, page_table, ld_pt, (const __nv_bfloat16*)swa,
              swa_map, (const __nv_bfloat16*)comp, topk_idx, topk_len, topk_width, mode, ratio, sink, scale, ps,
-             window, num_valid};
+             window, num_valid, out_rope, rp};
   switch (heads) {
     case 8: return launch_attn<8>(a, t, st);
     case 16: return launch_attn<16>(a, t, st);

@@ -436,9 +436,9 @@ int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, in
                 const float* sb, int acc, int bn, cudaStream_t st, const LaunchOpts& o = LaunchOpts{}) {
   if (bn == 0) {
     const int mt = (M + kBM - 1) / kBM * o.batches;
-    if (mt * ((N + 127) / 128) >= 148 && !FP8)
+    if (mt * ((N + 127) / 128) >= 98 && !FP8)
       bn = 128;
-    else if (mt * ((N + 63) / 64) >= 148)
+    else if (mt * ((N + 63) / 64) >= 98)
       bn = 64;
     else
       bn = 32;

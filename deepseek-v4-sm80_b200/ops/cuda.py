@@ -234,7 +234,8 @@ def indexer_select(qc, wf, vals, scales, fb, ps: int, k: int):
 
 # --------------------------------------------------------------------------- attention
 def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_len, sink, scale, ps: int,
-              window: int):
+              window: int, out_rope=None):
+    """out_rope: RopeSpec whose inverse rotation the kernel applies to the tail of every output row."""
     t, h, d = q.shape
     o = torch.empty_like(q)
     mode = 1 if ratio == 4 else (2 if ratio else 0)
@@ -243,8 +244,12 @@ def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_
             nv.ptr(swa_cache), _i32(swa_map), nv.ptr(comp_cache if mode else None),
             nv.ptr(topk_idx if mode == 1 else None), nv.ptr(topk_len if mode == 1 else None),
             I(topk_idx.shape[1] if mode == 1 else 0), I(mode), I(ratio), nv.ptr(sink), F(scale), I(ps), I(window),
-            nv.ptr(fb.num_valid), I(t), I(h), I(d))
+            nv.ptr(fb.num_valid), I(t), I(h), I(d), I(1 if out_rope is not None else 0),
+            rope_params(out_rope if out_rope is not None else _NO_ROPE))
     return o
+
+
+_NO_ROPE = RopeSpec.make(64, 10000.0, 0, 1.0, 32, 1)
 
 
 # --------------------------------------------------------------------------- MoE

@@ -38,9 +38,12 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
     """(tile width, K splits) that put roughly one CTA on every SM."""
     mt = (m + 127) // 128 * batches
     if bn == 0:
-        if mt * ((n + 127) // 128) >= NUM_SMS_HINT and not fp8:
+        # the widest tile that still gives about one CTA per SM (a second, partial wave costs more than the
+        # narrower tile saves): 128 (bf16 only), 64, else 32
+        fill = NUM_SMS_HINT * 2 // 3
+        if mt * ((n + 127) // 128) >= fill and not fp8:
             bn = 128
-        elif mt * ((n + 63) // 64) >= NUM_SMS_HINT:
+        elif mt * ((n + 63) // 64) >= fill:
             bn = 64
         else:
             bn = 32

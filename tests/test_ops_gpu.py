@@ -237,6 +237,13 @@ def test_sparse_attention(heads, ratio):
                     sink.to(DEV), 512 ** -0.5, ps, 128)
     o_r = O.attention(q, fb, swa, swa_map, comp, ratio, tk_idx, tk_len, sink, 512 ** -0.5, ps, 128)
     close(o, o_r, atol=2e-2)
+    # inverse RoPE of the output tail fused into the epilogue == attention followed by rope_tail(inverse)
+    spec = RopeSpec.make(64, 10000.0, 65536, 16.0, 32, 1)
+    o2 = O.attention(q.to(DEV), fbd, swa.to(DEV), swa_map.to(DEV), dv(comp), ratio, dv(tk_idx), dv(tk_len),
+                     sink.to(DEV), 512 ** -0.5, ps, 128, out_rope=spec)
+    o2_r = O.rope_tail(o.clone(), fbd.positions, spec, inverse=True)
+    assert torch.equal(o2[..., :448], o[..., :448])
+    close(o2, o2_r, atol=1e-2)
 
 
 def test_moe_gate_and_experts():
