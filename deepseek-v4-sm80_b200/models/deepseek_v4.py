@@ -104,7 +104,9 @@ class DSV4Model:
             xq = O.fp8_quant(x)
         return O.gemm_fp8(xq[0], xq[1], self.w[name + ".weight"], self.w[name + ".scale"])
 
-    def attention(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None) -> torch.Tensor:
+    def attention(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None, hc=None) -> torch.Tensor:
+        """hc = (residual, post, comb): when the communicator can fuse the hyper-connection post mix behind its
+        reduction, the new residual streams are returned instead of the block output (flagged by ``self._mixed``)."""
         cfg, w, p = self.cfg, self.w, f"L{l}.attn."
         t = y.shape[0]
         rope = self.ropes[l]
@@ -152,11 +154,12 @@ class DSV4Model:
         o2 = O.gemm_bf16_grouped(o.reshape(t, self.h_local * cfg.head_dim), w[p + "wo_a.weight_bf16"], self.g_local)
         if getattr(self.comm, "fused", False):
             oq = O.fp8_quant(o2)
-            return self.comm.gemm_fp8_allreduce(oq[0], oq[1], w[p + "wo_b.weight"], w[p + "wo_b.scale"])
+            self._mixed = hc is not None
+            return self.comm.gemm_fp8_allreduce(oq[0], oq[1], w[p + "wo_b.weight"], w[p + "wo_b.scale"], hc=hc)
         out = self._fp8_linear(o2, p + "wo_b")
         return self.comm.all_reduce(out, "attn")
 
-    def moe(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None) -> torch.Tensor:
+    def moe(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None, hc=None) -> torch.Tensor:
         cfg, w, p = self.cfg, self.w, f"L{l}.moe."
         if yq is None:
             yq = O.fp8_quant(y)
@@ -177,7 +180,11 @@ class DSV4Model:
             t, k, h = y.shape[0], idx.shape[1], y.shape[1]
             self._join(y)
             if getattr(self.comm, "fused", False):
-                return self.comm.moe_finalize_allreduce(rows, plan, mt, shared, fb.num_valid, t, k, h)
+                self._mixed = hc is not None
+                return self.comm.moe_finalize_allreduce(rows, plan, mt, shared, fb.num_valid, t, k, h, hc=hc)
+            if self.comm.size == 1:
+                self._mixed = hc is not None
+                return C.moe_finalize(rows, plan, mt, shared, fb.num_valid, t, k, h, hc)
             out = C.moe_finalize(rows, plan, mt, shared, fb.num_valid, t, k, h)
             return self.comm.all_reduce(out, "moe")
         routed = O.moe_experts(y, idx, wt, w[p + "w13"], w[p + "s13"], w[p + "w2"], w[p + "s2"], cfg.swiglu_limit,
@@ -191,8 +198,9 @@ class DSV4Model:
             y, post, comb, yq = O.hc_pre(x, w[p + blk + ".fn"], w[p + blk + ".scale"], w[p + blk + ".base"],
                                          cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps,
                                          w[p + norm + ".weight"], want_q=True)
-            y = fn(l, y, fb, yq)
-            x = O.hc_post(y, x, post, comb)
+            self._mixed = False
+            y = fn(l, y, fb, yq, (x, post, comb))
+            x = y if self._mixed else O.hc_post(y, x, post, comb)
         return x
 
     # ------------------------------------------------------------------ forward

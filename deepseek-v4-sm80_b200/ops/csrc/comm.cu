@@ -3,39 +3,56 @@
 // moe.cu), used for the embedding-free generic reductions, for tests and as the microbenchmark baseline against
 // NCCL.  Each CTA owns rows b, b + grid, ...: copy to the symmetric buffer, publish, wait, reduce in rank order.
 #include "comm.cuh"
+#include "hc_post.cuh"
 
 namespace {
 
 __global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
-                                                        int rows, int cols, const CommCtx comm) {
+                                                        int rows, int cols, const HcPostArgs hc, const CommCtx comm) {
   pdl_entry();
   __shared__ int ok;
   const uint32_t epoch = comm_epoch(comm);
   const int parity = epoch & 1;
   __nv_bfloat16* mine = comm_data(comm, comm.rank, parity);
   const int c8 = cols / 8;
-  for (int r = blockIdx.x; r < rows; r += gridDim.x)
-    for (int i = threadIdx.x; i < c8; i += blockDim.x)
-      reinterpret_cast<uint4*>(mine + (size_t)r * cols)[i] = reinterpret_cast<const uint4*>(x + (size_t)r * cols)[i];
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    comm_publish(comm, blockIdx.x, epoch);
-    ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
+  if (x) {  // x == null: the producer (a GEMM in deposit mode) already wrote this rank's partial into `mine`
+    for (int r = blockIdx.x; r < rows; r += gridDim.x)
+      for (int i = threadIdx.x; i < c8; i += blockDim.x)
+        reinterpret_cast<uint4*>(mine + (size_t)r * cols)[i] = reinterpret_cast<const uint4*>(x + (size_t)r * cols)[i];
   }
   __syncthreads();
-  if (ok) {
-    for (int r = blockIdx.x; r < rows; r += gridDim.x)
-      for (int i = threadIdx.x; i < c8; i += 2 * blockDim.x) {
-        const int i1 = i + blockDim.x;
-        uint4 o0, o1;
-        if (i1 < c8) {
-          comm_reduce16x2(comm, parity, (size_t)r * cols + i * 8, (size_t)r * cols + i1 * 8, o0, o1);
-          reinterpret_cast<uint4*>(out + (size_t)r * cols)[i1] = o1;
-        } else {
-          o0 = comm_reduce16(comm, parity, (size_t)r * cols + i * 8);
+  auto emit_row = [&](int r) {
+    return [&, r](int col, const uint4& v) {
+      if (hc.res)
+        hc_post_store8(v, hc, r, cols, col);
+      else
+        *reinterpret_cast<uint4*>(out + (size_t)r * cols + col) = v;
+    };
+  };
+  if (comm_use_two_shot(comm, rows, cols)) {
+    if ((int)blockIdx.x < rows) comm_row_two_shot(comm, epoch, blockIdx.x, cols, &ok, emit_row(blockIdx.x));
+  } else {
+    if (threadIdx.x == 0) {
+      comm_publish(comm, blockIdx.x, epoch);
+      ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
+    }
+    __syncthreads();
+    if (ok) {
+      for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        auto emit = emit_row(r);
+        for (int i = threadIdx.x; i < c8; i += 2 * blockDim.x) {
+          const int i1 = i + blockDim.x;
+          uint4 o0, o1;
+          if (i1 < c8) {
+            comm_reduce16x2(comm, parity, (size_t)r * cols + i * 8, (size_t)r * cols + i1 * 8, o0, o1);
+            emit(i1 * 8, o1);
+          } else {
+            o0 = comm_reduce16(comm, parity, (size_t)r * cols + i * 8);
+          }
+          emit(i * 8, o0);
         }
-        reinterpret_cast<uint4*>(out + (size_t)r * cols)[i] = o0;
       }
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) comm_finish(comm, gridDim.x);
@@ -69,12 +86,18 @@ DSV4_API int dsv4_comm_layout(long long* flags_bytes, int* channels, int* slots,
   return 0;
 }
 
-DSV4_API int dsv4_allreduce(const void* x, void* out, int rows, int cols, const CommCtx* comm, cudaStream_t st) {
+// x may be null when this rank's partial is already in the channel's symmetric buffer (a GEMM launched in deposit
+// mode on the same channel wrote it).  res / post / comb / xout (all null or all given): the hyper-connection post
+// mix is applied to the reduced rows and xout [rows, 4, cols] is written instead of out.
+DSV4_API int dsv4_allreduce(const void* x, void* out, int rows, int cols, const void* res, const float* post,
+                            const float* comb, void* xout, const CommCtx* comm, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cols % 8) return 500;
   if ((long long)rows * cols * 2 > comm->data_bytes) return 501;
+  if (xout && (!res || !post || !comb)) return 502;
   int grid = rows < 1024 ? rows : 1024;
-  dsv4_launch(allreduce_kernel, grid, 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, cols, *comm);
+  HcPostArgs hc{xout ? (const __nv_bfloat16*)res : nullptr, post, comb, (__nv_bfloat16*)xout};
+  dsv4_launch(allreduce_kernel, grid, 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, cols, hc, *comm);
   return (int)cudaGetLastError();
 }
 

@@ -23,6 +23,7 @@ struct CommCtx {
   int rank, world;
   int channel;
   long long data_bytes;       // bytes of one parity buffer of one channel
+  long long small_bytes;      // bytes of one result buffer of the two-shot path (0: none)
   int* epoch;                 // local [kCommChannels] device ints
   int* done;                  // local [kCommChannels] device ints
 };
@@ -34,6 +35,12 @@ __device__ __forceinline__ uint32_t* comm_flag(const CommCtx& c, int on_rank, in
 __device__ __forceinline__ __nv_bfloat16* comm_data(const CommCtx& c, int on_rank, int parity) {
   return reinterpret_cast<__nv_bfloat16*>(c.peer[on_rank] + comm_flags_bytes() +
                                           ((size_t)c.channel * 2 + parity) * (size_t)c.data_bytes);
+}
+// result[channel][parity] of the two-shot path: final rows, written remotely by each row's owner
+__device__ __forceinline__ __nv_bfloat16* comm_result(const CommCtx& c, int on_rank, int parity) {
+  return reinterpret_cast<__nv_bfloat16*>(c.peer[on_rank] + comm_flags_bytes() +
+                                          (size_t)kCommChannels * 2 * (size_t)c.data_bytes +
+                                          ((size_t)c.channel * 2 + parity) * (size_t)c.small_bytes);
 }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -50,6 +57,11 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
   uint4 v;
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
+}
+
+__device__ __forceinline__ void st_peer16(void* p, const uint4& v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
 
 // Called by ONE thread after the CTA's partial tile is written and the writers have synchronised.
@@ -134,6 +146,86 @@ __device__ __forceinline__ void comm_reduce16x2(const CommCtx& c, int parity, si
   o0 = comm_sum16(c, v0);
   o1 = comm_sum16(c, v1);
 }
+// Wait for ONE writer's flag (two-shot path).  Called by one thread.
+__device__ __forceinline__ bool comm_wait_one(const CommCtx& c, int writer, int slot, uint32_t epoch) {
+  const uint32_t* f = comm_flag(c, c.rank, writer, slot);
+  unsigned long long t0 = 0;
+  for (int spin = 0;; ++spin) {
+    if ((int)(ld_relaxed_sys(f) - epoch) >= 0) break;
+    if ((spin & 63) == 63) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        dsv4_set_error(DSV4_ERR_PEER_TIMEOUT, writer, slot);
+        return false;
+      }
+    }
+  }
+  __threadfence_system();
+  return true;
+}
+
+// Two-shot all-reduce of ONE row by ONE CTA (all threads call it; the CTA's partial row already sits in
+// comm_data(rank, parity) and the CTA has synchronised).  Row r is owned by rank r % world: the owner waits for the
+// 7 partials, sums them in rank order, writes the result row into every rank's result buffer and raises a second
+// flag; the other ranks only tell the owner that their partial is ready and wait for that second flag.  Per rank
+// this moves 2 * (world-1)/world of the tensor over NVLink instead of (world-1) times the tensor, and a non-owner
+// sends one flag instead of world-1.  emit(col, v) receives 8 reduced bf16 values of the row.
+constexpr int kTwoShotSlot = kCommSlots / 2;
+template <class Emit>
+__device__ __forceinline__ void comm_row_two_shot(const CommCtx& c, uint32_t epoch, int row, int cols, int* sh_ok,
+                                                  Emit emit) {
+  const int parity = epoch & 1, owner = row % c.world;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    int ok;
+    if (owner != c.rank) {
+      st_relaxed_sys(comm_flag(c, owner, c.rank, row), epoch);
+      ok = comm_wait_one(c, owner, kTwoShotSlot + row, epoch) ? 1 : 0;
+    } else {
+      ok = comm_wait(c, row, epoch) ? 1 : 0;
+    }
+    *sh_ok = ok;
+  }
+  __syncthreads();
+  if (!*sh_ok) return;
+  const size_t off = (size_t)row * cols;
+  if (owner == c.rank) {
+    for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 16) {
+      const int i1 = i + blockDim.x * 8;
+      uint4 v0, v1 = make_uint4(0, 0, 0, 0);
+      if (i1 < cols)
+        comm_reduce16x2(c, parity, off + i, off + i1, v0, v1);
+      else
+        v0 = comm_reduce16(c, parity, off + i);
+#pragma unroll
+      for (int p = 0; p < kMaxRanks; ++p) {
+        if (p < c.world && p != c.rank) {
+          __nv_bfloat16* dst = comm_result(c, p, parity) + off;
+          st_peer16(dst + i, v0);
+          if (i1 < cols) st_peer16(dst + i1, v1);
+        }
+      }
+      emit(i, v0);
+      if (i1 < cols) emit(i1, v1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+#pragma unroll
+      for (int p = 0; p < kMaxRanks; ++p)
+        if (p < c.world && p != c.rank) st_relaxed_sys(comm_flag(c, p, c.rank, kTwoShotSlot + row), epoch);
+    }
+  } else {
+    const __nv_bfloat16* src = comm_result(c, c.rank, parity) + off;
+    for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 8) emit(i, ld_peer16(src + i));
+  }
+}
+__device__ __forceinline__ bool comm_use_two_shot(const CommCtx& c, int rows, int cols) {
+  return c.world >= 4 && c.small_bytes > 0 && rows <= 256 && rows <= (int)gridDim.x &&
+         (long long)rows * cols * 2 <= c.small_bytes;
+}
+
 // Last CTA of the grid advances the channel epoch (call once per CTA, by one thread, at the very end).
 __device__ __forceinline__ void comm_finish(const CommCtx& c, int total_ctas) {
   __threadfence();

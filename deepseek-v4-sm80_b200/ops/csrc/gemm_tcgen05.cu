@@ -45,6 +45,8 @@ struct GemmArgs {
   int splits;
   float* ws;           // [tiles][splits][128][BN] fp32 partials
   int* counters;       // [tiles], zero between launches
+  int deposit_only;    // with a communicator: only write this rank's partial into the channel's symmetric buffer;
+                       //   a following dsv4_allreduce(x = null) on the same channel reduces it
   int prefetch_b;      // the weight operand is not written by the kernel before this one: load it before pdl_wait()
   int cluster;         // > 0: the `splits` CTAs of a tile form one thread-block cluster and reduce over distributed
                        //      shared memory (no workspace, no atomics)
@@ -312,7 +314,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
     }
-    if (fused) {
+    if (fused && !g.deposit_only) {
       if constexpr (sizeof(OutT) == 2) {
         const int slot = blockIdx.y * gridDim.x + blockIdx.x;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -389,6 +391,7 @@ struct LaunchOpts {
   float* ws = nullptr;
   long long partial_stride = 0;
   int cluster = 0;
+  int deposit_only = 0;
   int* counters = nullptr;
   int a_cols = 0, b_rows = 0;  // full extents of the operands (0 = K / N)
   int sb_ld = 0;
@@ -421,7 +424,7 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
     if ((long long)grid.x * grid.y > kCommSlots || o.splits != 1 || o.batches != 1) return 104;
   }
   GemmArgs g{M, N, K, ldo, sa, sb, o.sb_ld ? o.sb_ld : (K + 127) / 128, accumulate_out, o.a_col_pb, o.b_row_pb,
-             o.out_col_pb, o.splits, o.ws, o.counters, g_weight_prefetch, o.cluster, o.partial_stride};
+             o.out_col_pb, o.splits, o.ws, o.counters, o.deposit_only, g_weight_prefetch, o.cluster, o.partial_stride};
   if (o.cluster) {
     if (o.splits != 2 && o.splits != 4 && o.splits != 8) return 105;
     dsv4_launch_cluster(kern, grid, 192, Cfg::kSmemBytes, stream, o.splits, tmA, tmB, out, g, comm);
@@ -524,13 +527,18 @@ DSV4_API int dsv4_gemm_fp8(const void* x, const void* w, void* out, const float*
 
 // Fused projection + all-reduce: every rank multiplies its K-shard, the epilogue publishes the partial tile to the
 // rank's symmetric buffer and reduces the peers' tiles over NVLink (see comm.cuh).  out is bf16 [M,N], dense.
+// deposit != 0: the GEMM only leaves its partial product in the channel's symmetric buffer (out is not written);
+// dsv4_allreduce(x = null, ...) on the same channel must follow.  For small row counts this beats reducing in the
+// GEMM epilogue, whose 128 x 32 tiles make the peer reads 64-byte pieces.
 DSV4_API int dsv4_gemm_fp8_allreduce(const void* x, const void* w, void* out, const float* sa, const float* sb, int M,
-                                     int N, int K, int ldx, int ldw, const CommCtx* comm, int bn, cudaStream_t stream) {
+                                     int N, int K, int ldx, int ldw, const CommCtx* comm, int bn, int deposit,
+                                     cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((K % 128) || (ldx % 16) || (ldw % 16) || (N % 8)) return 112;
   if ((long long)M * N * 2 > comm->data_bytes) return 113;
   LaunchOpts o;
   o.comm = comm;
+  o.deposit_only = deposit ? 1 : 0;
   return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, N, sa, sb, 0, bn, stream, o);
 }
 DSV4_API int dsv4_gemm_bf16_allreduce(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw,

@@ -16,6 +16,7 @@
 // (held as fp16 for the tensor core: exact for |x| in [2^-14, 65504]), exact FP4 dequantisation, fp32 accumulation, GEMM1 output rounded to bf16 before the fp32 SwiGLU, GEMM2
 // output rounded to bf16 and multiplied by the bf16 route weight, routes summed afterwards.
 #include "comm.cuh"
+#include "hc_post.cuh"
 
 namespace {
 
@@ -543,9 +544,10 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 }
 
 // out[t] = bf16( float(bf16(sum_k local route rows)) + float(shared[t]) ); rows >= num_valid -> 0
+// With xout != null the hyper-connection post mix is applied on the fly and xout [T,4,h] is written instead of out.
 __global__ void moe_finalize_kernel(const __nv_bfloat16* __restrict__ yr, const int* __restrict__ route_pos,
                                     const __nv_bfloat16* __restrict__ shared, __nv_bfloat16* __restrict__ out,
-                                    const int* __restrict__ num_valid, int topk, int h) {
+                                    const int* __restrict__ num_valid, int topk, int h, const HcPostArgs hc) {
   pdl_entry();
   const int t = blockIdx.x;
   const bool valid = !num_valid || t < *num_valid;
@@ -574,7 +576,10 @@ __global__ void moe_finalize_kernel(const __nv_bfloat16* __restrict__ yr, const 
         po[j] = __floats2bfloat162_rn(r2.x + s2.x, r2.y + s2.y);
       }
     }
-    *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = o;
+    if (hc.res)
+      hc_post_store8(o, hc, t, h, i);
+    else
+      *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = o;
   }
 }
 
@@ -585,7 +590,7 @@ __global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat1
                                                               const __nv_bfloat16* __restrict__ shared,
                                                               __nv_bfloat16* __restrict__ out,
                                                               const int* __restrict__ num_valid, int topk, int h,
-                                                              int t_rows, const CommCtx comm) {
+                                                              int t_rows, const HcPostArgs hc, const CommCtx comm) {
   pdl_entry();
   __shared__ int ok;
   const uint32_t epoch = comm_epoch(comm);
@@ -622,24 +627,38 @@ __global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat1
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    comm_publish(comm, blockIdx.x, epoch);
-    ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
-  }
-  __syncthreads();
-  if (ok) {
-    for (int t = blockIdx.x; t < t_rows; t += gridDim.x)
-      for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 16) {
-        const int i1 = i + blockDim.x * 8;
-        uint4 o0, o1;
-        if (i1 < h) {
-          comm_reduce16x2(comm, parity, (size_t)t * h + i, (size_t)t * h + i1, o0, o1);
-          *reinterpret_cast<uint4*>(out + (size_t)t * h + i1) = o1;
-        } else {
-          o0 = comm_reduce16(comm, parity, (size_t)t * h + i);
+  auto emit_row = [&](int t) {
+    return [&, t](int col, const uint4& v) {
+      if (hc.res)
+        hc_post_store8(v, hc, t, h, col);
+      else
+        *reinterpret_cast<uint4*>(out + (size_t)t * h + col) = v;
+    };
+  };
+  if (comm_use_two_shot(comm, t_rows, h)) {
+    if ((int)blockIdx.x < t_rows) comm_row_two_shot(comm, epoch, blockIdx.x, h, &ok, emit_row(blockIdx.x));
+  } else {
+    if (threadIdx.x == 0) {
+      comm_publish(comm, blockIdx.x, epoch);
+      ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
+    }
+    __syncthreads();
+    if (ok) {
+      for (int t = blockIdx.x; t < t_rows; t += gridDim.x) {
+        auto emit = emit_row(t);
+        for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 16) {
+          const int i1 = i + blockDim.x * 8;
+          uint4 o0, o1;
+          if (i1 < h) {
+            comm_reduce16x2(comm, parity, (size_t)t * h + i, (size_t)t * h + i1, o0, o1);
+            emit(i1, o1);
+          } else {
+            o0 = comm_reduce16(comm, parity, (size_t)t * h + i);
+          }
+          emit(i, o0);
         }
-        *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = o0;
       }
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) comm_finish(comm, gridDim.x);
@@ -722,23 +741,31 @@ DSV4_API int dsv4_moe_gemm(int mode, int nt, const void* w, const void* scales, 
   return 221;
 }
 
+// res / post / comb / xout (all null, or all given): apply the hyper-connection post mix to the combined output and
+// write the new residual streams xout [t, 4, h] instead of out.
 DSV4_API int dsv4_moe_finalize(const void* yr, const int* plan, int routes, int max_tiles, const void* shared, void* out,
-                               const int* num_valid, int t, int topk, int h, cudaStream_t st) {
+                               const int* num_valid, int t, int topk, int h, const void* res, const float* post,
+                               const float* comb, void* xout, cudaStream_t st) {
   if (t <= 0) return 0;
+  if (xout && (!res || !post || !comb)) return 231;
   const int* route_pos = plan + 4 + 3 * max_tiles + routes;
   dsv4_launch(moe_finalize_kernel, t, 256, 0, st, (const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
-                                         (__nv_bfloat16*)out, num_valid, topk, h);
+              (__nv_bfloat16*)out, num_valid, topk, h,
+              HcPostArgs{xout ? (const __nv_bfloat16*)res : nullptr, post, comb, (__nv_bfloat16*)xout});
   return (int)cudaGetLastError();
 }
 
 DSV4_API int dsv4_moe_finalize_allreduce(const void* yr, const int* plan, int routes, int max_tiles, const void* shared,
-                                         void* out, const int* num_valid, int t, int topk, int h, const CommCtx* comm,
+                                         void* out, const int* num_valid, int t, int topk, int h, const void* res,
+                                         const float* post, const float* comb, void* xout, const CommCtx* comm,
                                          cudaStream_t st) {
   if (t <= 0) return 0;
   if (h % 8 || (long long)t * h * 2 > comm->data_bytes) return 230;
+  if (xout && (!res || !post || !comb)) return 231;
   const int* route_pos = plan + 4 + 3 * max_tiles + routes;
   const int grid = t < 1024 ? t : 1024;
-  dsv4_launch(moe_finalize_ar_kernel, grid, 256, 0, st, (const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
-                                               (__nv_bfloat16*)out, num_valid, topk, h, t, *comm);
+  dsv4_launch(moe_finalize_ar_kernel, grid, 256, 0, st, (const __nv_bfloat16*)yr, route_pos,
+              (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, num_valid, topk, h, t,
+              HcPostArgs{xout ? (const __nv_bfloat16*)res : nullptr, post, comb, (__nv_bfloat16*)xout}, *comm);
   return (int)cudaGetLastError();
 }

@@ -299,10 +299,17 @@ def moe_routed(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
     return rows, plan, max_tiles
 
 
-def moe_finalize(rows, plan, max_tiles, shared, num_valid, t, topk, h):
+def moe_finalize(rows, plan, max_tiles, shared, num_valid, t, topk, h, hc=None):
+    """hc = (residual [t,4,h], post, comb): returns the new residual streams (post mix fused), else the layer output."""
+    if hc is not None:
+        res, post, comb = hc
+        xout = torch.empty_like(res)
+        nv.call("moe_finalize", nv.ptr(rows), nv.ptr(plan), I(t * topk), I(max_tiles), nv.ptr(shared), nv.ptr(None),
+                nv.ptr(num_valid), I(t), I(topk), I(h), nv.ptr(res), nv.ptr(post), nv.ptr(comb), nv.ptr(xout))
+        return xout
     out = torch.empty(t, h, dtype=rows.dtype, device=rows.device)
     nv.call("moe_finalize", nv.ptr(rows), nv.ptr(plan), I(t * topk), I(max_tiles), nv.ptr(shared), nv.ptr(out),
-            nv.ptr(num_valid), I(t), I(topk), I(h))
+            nv.ptr(num_valid), I(t), I(topk), I(h), nv.ptr(None), nv.ptr(None), nv.ptr(None), nv.ptr(None))
     return out
 
 

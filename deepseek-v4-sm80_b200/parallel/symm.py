@@ -35,8 +35,8 @@ MAX_RANKS = 8
 
 class CommCtx(ctypes.Structure):
     _fields_ = [("peer", ctypes.c_void_p * MAX_RANKS), ("rank", ctypes.c_int), ("world", ctypes.c_int),
-                ("channel", ctypes.c_int), ("data_bytes", ctypes.c_longlong), ("epoch", ctypes.c_void_p),
-                ("done", ctypes.c_void_p)]
+                ("channel", ctypes.c_int), ("data_bytes", ctypes.c_longlong), ("small_bytes", ctypes.c_longlong),
+                ("epoch", ctypes.c_void_p), ("done", ctypes.c_void_p)]
 
 
 class SymmComm(Comm):
@@ -59,7 +59,9 @@ class SymmComm(Comm):
         assert mr.value == MAX_RANKS
         self.flags_bytes, self.channels, self.slots = fb.value, ch.value, sl.value
         self.data_bytes = (max_rows * hidden * 2 + 255) // 256 * 256
-        total = self.flags_bytes + self.channels * 2 * self.data_bytes
+        # result buffers of the two-shot path (row counts of a decode batch): the owner of a row writes its sum here
+        self.small_bytes = (min(max_rows, 256) * hidden * 2 + 255) // 256 * 256
+        total = self.flags_bytes + self.channels * 2 * self.data_bytes + self.channels * 2 * self.small_bytes
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self.handle = symm_mem.rendezvous(self.buf, self.group)
         self.buf.zero_()
@@ -74,6 +76,7 @@ class SymmComm(Comm):
             for r in range(self.size):
                 x.peer[r] = ptrs[r]
             x.rank, x.world, x.channel, x.data_bytes = self.rank, self.size, c, self.data_bytes
+            x.small_bytes = self.small_bytes
             x.epoch = self.state.data_ptr()
             x.done = self.state.data_ptr() + 4 * self.channels
             self.ctx.append(x)
@@ -84,22 +87,45 @@ class SymmComm(Comm):
         assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 2
         self.counters["all_reduce"] += 1
         out = torch.empty_like(x)
-        nv.call("allreduce", nv.ptr(x), nv.ptr(out), I(x.shape[0]), I(x.shape[1]),
-                ctypes.byref(self.ctx[self.CH_GENERIC]))
+        nv.call("allreduce", nv.ptr(x), nv.ptr(out), I(x.shape[0]), I(x.shape[1]), nv.ptr(None), nv.ptr(None),
+                nv.ptr(None), nv.ptr(None), ctypes.byref(self.ctx[self.CH_GENERIC]))
         return out
 
-    def gemm_fp8_allreduce(self, xq, sx, w, ws, bn: int = 0) -> torch.Tensor:
-        """out = all_reduce(xq @ w^T) with the reduction done by the GEMM's epilogue."""
+    def gemm_fp8_allreduce(self, xq, sx, w, ws, bn: int = 0, hc=None) -> torch.Tensor:
+        """out = all_reduce(xq @ w^T).  Up to 256 rows (decode) the GEMM deposits its partial product in the channel's
+        symmetric buffer and the row-wise all-reduce kernel follows (its peer reads are whole rows; the GEMM
+        epilogue's would be 64-byte pieces of 128 x 32 tiles); above, the reduction runs in the GEMM's epilogue.
+        hc = (residual, post, comb): the hyper-connection post mix is applied to the reduced rows by the same kernel
+        and the new residual streams [m, 4, n] are returned."""
         m, k = xq.shape
         n = w.shape[0]
         self.counters["gemm_allreduce"] += 1
         if _SKIP_EXCHANGE:
             from ..ops import api as O
 
-            return O.gemm_fp8(xq, sx, w, ws)
+            y = O.gemm_fp8(xq, sx, w, ws)
+            return O.hc_post(y, *hc) if hc is not None else y
+        ctx = ctypes.byref(self.ctx[self.CH_ATTN])
+        if m <= 256:
+            nv.call("gemm_fp8_allreduce", nv.ptr(xq), nv.ptr(w), nv.ptr(None), nv.ptr(sx), nv.ptr(ws), I(m), I(n), I(k),
+                    I(xq.stride(0)), I(w.stride(0)), ctx, I(bn), I(1))
+            if hc is not None:
+                res, post, comb = hc
+                xout = torch.empty_like(res)
+                nv.call("allreduce", nv.ptr(None), nv.ptr(None), I(m), I(n), nv.ptr(res), nv.ptr(post), nv.ptr(comb),
+                        nv.ptr(xout), ctx)
+                return xout
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=xq.device)
+            nv.call("allreduce", nv.ptr(None), nv.ptr(out), I(m), I(n), nv.ptr(None), nv.ptr(None), nv.ptr(None),
+                    nv.ptr(None), ctx)
+            return out
         out = torch.empty(m, n, dtype=torch.bfloat16, device=xq.device)
         nv.call("gemm_fp8_allreduce", nv.ptr(xq), nv.ptr(w), nv.ptr(out), nv.ptr(sx), nv.ptr(ws), I(m), I(n), I(k),
-                I(xq.stride(0)), I(w.stride(0)), ctypes.byref(self.ctx[self.CH_ATTN]), I(bn))
+                I(xq.stride(0)), I(w.stride(0)), ctx, I(bn), I(0))
+        if hc is not None:
+            from ..ops import api as O
+
+            return O.hc_post(out, *hc)
         return out
 
     def gemm_bf16_allreduce(self, x, w, bn: int = 0, channel: Optional[int] = None) -> torch.Tensor:
@@ -110,12 +136,21 @@ class SymmComm(Comm):
                 I(w.stride(0)), ctypes.byref(self.ctx[self.CH_ATTN if channel is None else channel]), I(bn))
         return out
 
-    def moe_finalize_allreduce(self, rows, plan, max_tiles, shared, num_valid, t, topk, h) -> torch.Tensor:
+    def moe_finalize_allreduce(self, rows, plan, max_tiles, shared, num_valid, t, topk, h, hc=None) -> torch.Tensor:
+        """hc = (residual, post, comb): the hyper-connection post mix is applied to the reduced rows in the same
+        kernel and the new residual streams [t, 4, h] are returned."""
         self.counters["moe_allreduce"] += 1
         if _SKIP_EXCHANGE:
             from ..ops import cuda as C
 
-            return C.moe_finalize(rows, plan, max_tiles, shared, num_valid, t, topk, h)
+            return C.moe_finalize(rows, plan, max_tiles, shared, num_valid, t, topk, h, hc)
+        if hc is not None:
+            res, post, comb = hc
+            xout = torch.empty_like(res)
+            nv.call("moe_finalize_allreduce", nv.ptr(rows), nv.ptr(plan), I(t * topk), I(max_tiles), nv.ptr(shared),
+                    nv.ptr(None), nv.ptr(num_valid), I(t), I(topk), I(h), nv.ptr(res), nv.ptr(post), nv.ptr(comb),
+                    nv.ptr(xout), ctypes.byref(self.ctx[self.CH_MOE]))
+            return xout
         out = torch.empty(t, h, dtype=rows.dtype, device=rows.device)
         nv.call("moe_finalize_allreduce", nv.ptr(rows), nv.ptr(plan), I(t * topk), I(max_tiles), nv.ptr(shared),
                 nv.ptr(out), nv.ptr(num_valid), I(t), I(topk), I(h), ctypes.byref(self.ctx[self.CH_MOE]))
