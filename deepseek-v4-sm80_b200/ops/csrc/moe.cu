@@ -40,20 +40,8 @@ __global__ void moe_topk_kernel(const float* __restrict__ scores, const float* _
                                 long long part_stride) {
   pdl_entry();
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  // scores may come as n_part split-K partial products (spaced part_stride floats apart), added here in order
-  auto score_at = [&](int j) {
-    float a = 0.f;
-    const float* sp = scores + (size_t)row * e + j;
-    int q = 0;
-    for (; q + 4 <= n_part; q += 4) {  // four loads in flight, added in split order
-      const float v0 = __ldg(sp + (size_t)q * part_stride), v1 = __ldg(sp + (size_t)(q + 1) * part_stride);
-      const float v2 = __ldg(sp + (size_t)(q + 2) * part_stride), v3 = __ldg(sp + (size_t)(q + 3) * part_stride);
-      a = (((a + v0) + v1) + v2) + v3;
-    }
-    for (; q < n_part; ++q) a += __ldg(sp + (size_t)q * part_stride);
-    return a;
-  };
-  if (row >= t_rows) return;
+  // scores may come as n_part split-K partial products (spaced part_stride floats apart); score_all() adds them in
+  // split order with the loads of all of a lane's experts in flight together
   if (num_valid && row >= *num_valid) {
     if (lane < k) idx[row * k + lane] = -1, wts[row * k + lane] = 0.f;
     return;
@@ -61,11 +49,27 @@ __global__ void moe_topk_kernel(const float* __restrict__ scores, const float* _
   constexpr int MAXPER = 16;  // e <= 512
   float p[MAXPER], sel[MAXPER];
   const int per = (e + 31) / 32;
+  float sc[MAXPER];
+#pragma unroll
+  for (int i = 0; i < MAXPER; ++i) sc[i] = 0.f;
+  {
+    const float* sp = scores + (size_t)row * e + lane;
+#pragma unroll 2
+    for (int q = 0; q < n_part; ++q) {
+      float tmp[MAXPER];
+#pragma unroll
+      for (int i = 0; i < MAXPER; ++i)
+        tmp[i] = (i < per && lane + i * 32 < e) ? __ldg(sp + (size_t)q * part_stride + i * 32) : 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXPER; ++i) sc[i] += tmp[i];
+    }
+  }
   float smax = -INFINITY;
   if (scoring == 2) {
-    for (int i = 0; i < per; ++i) {
+#pragma unroll
+    for (int i = 0; i < MAXPER; ++i) {
       const int j = lane + i * 32;
-      if (j < e) smax = fmaxf(smax, score_at(j));
+      if (i < per && j < e) smax = fmaxf(smax, sc[i]);
     }
     smax = warp_max(smax);
   }
@@ -76,7 +80,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ scores, const float* _
     p[i] = 0.f;
     sel[i] = -INFINITY;
     if (i < per && j < e) {
-      const float s = score_at(j);
+      const float s = sc[i];
       float v;
       if (scoring == 0) {
         const float sp = s > 20.f ? s : log1pf(expf(s));

@@ -38,11 +38,17 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
     """(tile width, K splits) that put roughly one CTA on every SM."""
     mt = (m + 127) // 128 * batches
     if bn == 0:
-        # the widest tile that still gives about one CTA per SM (a second, partial wave costs more than the
-        # narrower tile saves): 128 (bf16 only), 64, else 32
         fill = NUM_SMS_HINT * 2 // 3
-        if mt * ((n + 127) // 128) >= fill and not fp8:
-            bn = 128
+        if mt == 1:
+            # one row tile (decode): every column tile re-reads the whole activation from L2, so take the widest tile
+            # that, together with up to 8 K splits, still yields enough CTAs
+            smax = max(min(8, k_tiles // 4), 1)
+            for cand in ((64, 32) if fp8 else (128, 64, 32)):
+                bn = cand
+                if ((n + cand - 1) // cand) * smax >= fill:
+                    break
+        elif mt * ((n + 127) // 128) >= fill and not fp8:
+            bn = 128  # the widest tile that still gives about one CTA per SM
         elif mt * ((n + 63) // 64) >= fill:
             bn = 64
         else:
