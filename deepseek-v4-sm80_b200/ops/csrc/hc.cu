@@ -56,9 +56,16 @@ __global__ void __launch_bounds__(256) hc_pre_kernel(const __nv_bfloat16* __rest
     // (a fixed tree, so the result does not depend on timing)
     __shared__ float part_s[8][32];
     float a = 0.f;
-    if (lane < MIX)
-      for (int p = warp; p < n_part; p += 8)
-        a += __ldg(mixes_in + (size_t)p * part_stride + (size_t)t * ld_mix + lane);
+    for (int p0 = warp; p0 < n_part; p0 += 64) {  // eight loads in flight per thread
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int p = p0 + 8 * u;
+        v[u] = (lane < MIX && p < n_part) ? __ldg(mixes_in + (size_t)p * part_stride + (size_t)t * ld_mix + lane) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a += v[u];
+    }
     part_s[warp][lane] = a;
     __syncthreads();
     if (tid < MIX) {

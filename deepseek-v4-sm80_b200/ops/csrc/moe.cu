@@ -264,15 +264,16 @@ __device__ __forceinline__ uint32_t scale_mul2(uint32_t sc) {
 
 template <int MODE, int NT>
 struct MoeSmem {
-  static constexpr int kMats = MODE == 1 ? 2 : 1;
+  static constexpr int kMats = 1;  // GEMM1 packs 64 gate rows and the 64 matching up rows into one 128-row tile
   static constexpr int kPackedBytes = kMats * kRowsTile * 128;  // per packed stage (256 K elements)
   static constexpr int kBBytes = 2 * NT * 128;                  // route rows of one 128-wide K chunk (two swizzle atoms)
   // A chunk (128 K elements, half a packed stage) is the unit handed from the builders to the MMA issuers.  Its
   // dequantised weights live in tensor memory ([128 lanes x 128 fp16] = 64 columns per matrix); only the packed
   // stages and the route rows use shared memory.  The packed ring keeps >= 64 KiB per SM in flight (HBM latency).
-  static constexpr int kPStages = MODE == 1 ? 4 : 8;
-  static constexpr int kOBufs = MODE == 1 ? (NT == 64 ? 2 : 3) : 4;
-  static constexpr int kTotal = kPStages * kPackedBytes + kOBufs * kBBytes + 1024 + 512;
+  static constexpr int kPStages = 8;
+  static constexpr int kOBufs = 4;
+  static constexpr int kXchBytes = MODE == 1 ? 2 * 64 * NT * 4 : 0;  // GEMM1 epilogue: up rows handed to the gate warps
+  static constexpr int kTotal = kPStages * kPackedBytes + kOBufs * kBBytes + kXchBytes + 1024 + 512;
   static_assert(kTotal <= 227 * 1024, "shared memory budget");
   // Two accumulators per tile in both modes (gate/up, or the even/odd chunks of GEMM2), one per MMA issuer, and
   // two such pairs so that the epilogue of one tile overlaps the MMAs of the next.  NT = 64 is the widest tile for
@@ -287,7 +288,9 @@ struct MoeSmem {
   static_assert(kUsedCols <= 512, "tensor memory budget");
 };
 
-// MODE 1: D_gate, D_up -> act[pos, j] = fp16(bf16(silu(min(g,L)) * clamp(u,+-L))), weights w13 [E, 2I, K/2].
+// MODE 1: a work item is (route tile, 64 intermediate indices): TMEM lanes 0..63 hold the gate rows, lanes 64..127 the
+//         up rows of the same indices, so GEMM1 has as many MMAs per byte as GEMM2 and twice as many (half-size) work
+//         items to balance over the SMs.  act[pos, j] = fp16(bf16(silu(min(g,L)) * clamp(u,+-L))), w13 [E, 2I, K/2].
 // MODE 2: D -> out[route, h] = bf16(bf16(acc) * bf16(w_route)), weights w2 [E, H, K/2].
 //
 // Why this shape.  A tcgen05.mma with M = 128, K = 16 costs about 64 cycles whatever N <= 128 is (it streams the
@@ -317,18 +320,20 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(moe_smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* packed = smem;
   uint8_t* bbuf = smem + kPStages * S::kPackedBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(bbuf + kOBufs * S::kBBytes);
+  float* xch = reinterpret_cast<float*>(bbuf + kOBufs * S::kBBytes);  // GEMM1 epilogue exchange (kXchBytes)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bbuf + kOBufs * S::kBBytes + S::kXchBytes);
   uint64_t* pfull = bars;               // [kPStages]  packed stage landed
   uint64_t* pempty = pfull + kPStages;  // [kPStages]  packed stage read by every builder warp
   uint64_t* ofull = pempty + kPStages;  // [kOBufs]    chunk operands ready: weights in tensor memory + route rows landed
   uint64_t* oempty = ofull + kOBufs;    // [kOBufs]    the chunk's MMAs retired
   uint64_t* tfull = oempty + kOBufs;    // [2]         accumulators complete (one commit per issuer)
   uint64_t* tempty = tfull + 2;         // [2]         accumulators drained by the epilogue
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* xfull = tempty + 2;         // [2]         GEMM1: the up warps' sums are in the exchange buffer
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(xfull + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row_tiles = rows_per_expert / kRowsTile;
+  const int row_tiles = rows_per_expert / (MODE == 1 ? 64 : kRowsTile);
   const int kstages = K / 256;
   const int nchunks = kstages * 2;
   const int scale_ld = K / 32;  // scale bytes per weight row
@@ -336,8 +341,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   if (threadIdx.x == 0) {
     for (int i = 0; i < kPStages; ++i) mbar_init(&pfull[i], 1), mbar_init(&pempty[i], kBuilders / 32);
     for (int i = 0; i < kOBufs; ++i)
-      mbar_init(&ofull[i], kBuilders / 64 + 1), mbar_init(&oempty[i], (MODE == 1 && kDual) ? 2 : 1);
-    for (int i = 0; i < 2; ++i) mbar_init(&tfull[i], kDual ? 2 : 1), mbar_init(&tempty[i], 4);
+      mbar_init(&ofull[i], kBuilders / 64 + 1), mbar_init(&oempty[i], 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&tfull[i], kDual ? 2 : 1), mbar_init(&tempty[i], 4), mbar_init(&xfull[i], 2);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
@@ -361,15 +366,15 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       for (int wk = blockIdx.x; wk < total_work; wk += gridDim.x) {
         const int ct = wk / row_tiles, rt = wk % row_tiles;
         const int e = tiles[ct * 3];
-        const int wrow = e * (MODE == 1 ? 2 * rows_per_expert : rows_per_expert) + rt * kRowsTile;
+        const int wrow = MODE == 1 ? e * 2 * rows_per_expert + rt * 64 : e * rows_per_expert + rt * kRowsTile;
         bool ok = true;
         for (int ks = 0; ks < kstages; ++ks, ++ps) {
           const int s = ps % kPStages;
           if (!mbar_wait<kSleep>(&pempty[s], ((ps / kPStages) & 1) ^ 1, abort_flag, 11)) { ok = false; break; }
           mbar_expect_tx(&pfull[s], S::kPackedBytes);
           uint8_t* dst = packed + s * S::kPackedBytes;
-          tma_load_2d(dst, &tmW, &pfull[s], ks * 128, wrow);
-          if (MODE == 1) tma_load_2d(dst + kRowsTile * 128, &tmW, &pfull[s], ks * 128, wrow + rows_per_expert);
+          tma_load_2d(dst, &tmW, &pfull[s], ks * 128, wrow);  // MODE 1: box of 64 rows (gate), MODE 2: 128 rows
+          if (MODE == 1) tma_load_2d(dst + 64 * 128, &tmW, &pfull[s], ks * 128, wrow + rows_per_expert);  // up rows
         }
         if (!ok) break;
       }
@@ -394,7 +399,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     if (lane == 0) {
       // MMA issuer `iss`.  GEMM1: every chunk, matrix iss.  GEMM2: the chunks of parity iss, accumulator iss.
       const int iss = warp == 1 ? 0 : 1;
-      const int step = (MODE == 1 || !kDual) ? 1 : 2;
+      const int step = kDual ? 2 : 1;
       int it = 0;
       long long ob0 = 0;  // global index of the work item's first chunk
       bool ok = true;
@@ -402,14 +407,14 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const int acc = it % kAccBufs;
         if (!mbar_wait(&tempty[acc], ((it / kAccBufs) & 1) ^ 1, abort_flag, 13)) break;
         const uint32_t d = tmem_base + acc * 2 * NT + iss * NT;
-        const int ch0 = (MODE == 1 || !kDual) ? 0 : iss;
+        const int ch0 = kDual ? iss : 0;
         bool ready = false;
         for (int ch = ch0; ch < nchunks; ch += step) {
           const long long ob = ob0 + ch;
           const int b = (int)(ob % kOBufs);
           if (!ready && !mbar_wait(&ofull[b], (uint32_t)(ob / kOBufs) & 1, abort_flag, 14)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a = a_base + b * S::kACols + (MODE == 1 ? iss * 64 : 0);
+          const uint32_t a = a_base + b * S::kACols;
           const uint8_t* bt = bbuf + b * S::kBBytes;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
@@ -419,7 +424,6 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             }
             const uint64_t bd = umma_desc_k128(bt + (k >> 2) * (NT * 128), (k & 3) * 32);
             umma_f16_ta(d, a + k * 8, bd, kIdesc, (ch > ch0 || k > 0));
-            if (MODE == 1 && !kDual) umma_f16_ta(d + NT, a + 64 + k * 8, bd, kIdesc, (ch > ch0 || k > 0));
           }
           umma_commit(&oempty[b]);
         }
@@ -438,32 +442,75 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       if (!mbar_wait<256>(&tfull[acc], (it / kAccBufs) & 1, abort_flag, 15)) break;
       tc_fence_after();
       const uint32_t d0 = lane_addr + acc * 2 * NT;
-      const int orow = rt * kRowsTile + r;  // intermediate index (mode 1) / hidden index (mode 2)
+      // both accumulators (even / odd chunks) are added; then
+      //   GEMM2: row = hidden index, scaled by the route weight;
+      //   GEMM1: lanes 0..63 hold gate, lanes 64..127 up of the same 64 intermediate indices: the up warps hand their
+      //          (bf16-rounded) sums over through shared memory, the gate warps apply SwiGLU and store.
+      if (MODE == 2) {
+        const int orow = rt * kRowsTile + r;
 #pragma unroll 1
-      for (int c0 = 0; c0 < NT; c0 += 16) {
-        if (c0 >= ntok) break;
-        uint32_t g[16], u[16];
-        tmem_ld_32x16(d0 + c0, g);
-        tmem_ld_32x16(d0 + NT + c0, u);
-        tmem_ld_wait();
+        for (int c0 = 0; c0 < NT; c0 += 16) {
+          if (c0 >= ntok) break;
+          uint32_t g[16], u[16];
+          tmem_ld_32x16(d0 + c0, g);
+          tmem_ld_32x16(d0 + NT + c0, u);
+          tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          if (c0 + c < ntok) {
-            if (MODE == 1) {
-              float gv = bf2f(f2bf(__uint_as_float(g[c]))), uv = bf2f(f2bf(__uint_as_float(u[c])));
-              if (limit > 0.f) {
-                gv = fminf(gv, limit);
-                uv = fminf(fmaxf(uv, -limit), limit);
-              }
-              const float a = gv / (1.f + expf(-gv)) * uv;
-              // bf16 rounding of the activation, held as fp16 for the second GEMM's operand
-              reinterpret_cast<__half*>(out)[(size_t)(tok0 + c0 + c) * ld_out + orow] =
-                  __float2half_rn(bf2f(f2bf(a)));
-            } else {
+          for (int c = 0; c < 16; ++c) {
+            if (c0 + c < ntok) {
               const int pos = tok0 + c0 + c;
-              const __nv_bfloat16 y = f2bf(kDual ? __uint_as_float(g[c]) + __uint_as_float(u[c]) : __uint_as_float(g[c]));
+              const __nv_bfloat16 y = f2bf(__uint_as_float(g[c]) + __uint_as_float(u[c]));
               const __nv_bfloat16 wv = f2bf(sorted_w[pos]);
               out[(size_t)sorted_route[pos] * ld_out + orow] = __hmul(y, wv);
+            }
+          }
+        }
+      } else {
+        float* xq = xch + (size_t)acc * 64 * NT;  // [64 rows][NT], one buffer per accumulator pair
+        const bool is_up = r >= 64;
+        if (is_up) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < NT; c0 += 16) {
+            if (c0 >= ntok) break;
+            uint32_t g[16], u[16];
+            tmem_ld_32x16(d0 + c0, g);
+            tmem_ld_32x16(d0 + NT + c0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              xq[(size_t)(r - 64) * NT + ((c0 + c + (r & 15)) & (NT - 1))] =
+                  bf2f(f2bf(__uint_as_float(g[c]) + __uint_as_float(u[c])));
+          }
+        }
+        if (is_up) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xfull[acc]);
+        } else if (!mbar_wait(&xfull[acc], (it / kAccBufs) & 1, abort_flag, 19)) {
+          break;
+        }
+        if (!is_up) {
+          const int orow = rt * 64 + r;
+#pragma unroll 1
+          for (int c0 = 0; c0 < NT; c0 += 16) {
+            if (c0 >= ntok) break;
+            uint32_t g[16], u[16];
+            tmem_ld_32x16(d0 + c0, g);
+            tmem_ld_32x16(d0 + NT + c0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              if (c0 + c < ntok) {
+                float gv = bf2f(f2bf(__uint_as_float(g[c]) + __uint_as_float(u[c])));
+                float uv = xq[(size_t)r * NT + ((c0 + c + (r & 15)) & (NT - 1))];
+                if (limit > 0.f) {
+                  gv = fminf(gv, limit);
+                  uv = fminf(fmaxf(uv, -limit), limit);
+                }
+                const float a = gv / (1.f + expf(-gv)) * uv;
+                // bf16 rounding of the activation, held as fp16 for the second GEMM's operand
+                reinterpret_cast<__half*>(out)[(size_t)(tok0 + c0 + c) * ld_out + orow] =
+                    __float2half_rn(bf2f(f2bf(a)));
+              }
             }
           }
         }
@@ -482,11 +529,12 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const int quarter = warp & 3, half = j >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = a_base + ((uint32_t)(quarter * 32) << 16);
-    const size_t expert_rows = MODE == 1 ? 2 * (size_t)rows_per_expert : (size_t)rows_per_expert;
+
     auto scale_row = [&](int wk) -> const uint8_t* {
       const int ct = wk / row_tiles, rt = wk % row_tiles;
-      const size_t wrow = (size_t)tiles[ct * 3] * expert_rows + rt * kRowsTile + r +
-                          (MODE == 1 ? (size_t)half * rows_per_expert : 0);
+      const size_t e = (size_t)tiles[ct * 3];
+      const size_t wrow = MODE == 1 ? e * 2 * rows_per_expert + (r < 64 ? 0 : rows_per_expert) + rt * 64 + (r & 63)
+                                    : e * rows_per_expert + rt * kRowsTile + r;
       return scales + wrow * scale_ld;
     };
     long long ps = 0;
@@ -508,9 +556,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         if (!mbar_wait<kSleep>(&pfull[s], (uint32_t)(ps / kPStages) & 1, abort_flag, 16)) { ok = false; break; }
         // chunk `team` of the stage = bytes [64 team, 64 team + 64) of the 128-byte packed row = 16-byte pieces
         // 4 team .. 4 team + 3 (swizzled by row), one scale byte each
-        const uint8_t* prow = packed + s * S::kPackedBytes + (MODE == 1 ? half * kRowsTile * 128 : 0) + r * 128;
-        constexpr int kPieces = MODE == 1 ? 4 : 2;
-        const int piece0 = team * 4 + (MODE == 1 ? 0 : half * 2);
+        const uint8_t* prow = packed + s * S::kPackedBytes + r * 128;
+        constexpr int kPieces = 2;
+        const int piece0 = team * 4 + half * 2;
         uint4 p[kPieces];
 #pragma unroll
         for (int i = 0; i < kPieces; ++i)
@@ -519,10 +567,10 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const int b = (int)(ob % kOBufs);
         if (!mbar_wait<kSleep>(&oempty[b], ((uint32_t)(ob / kOBufs) & 1) ^ 1, abort_flag, 17)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t dst = lane_addr + b * S::kACols + (MODE == 1 ? half * 64 : half * 32);
+        const uint32_t dst = lane_addr + b * S::kACols + half * 32;
 #pragma unroll
         for (int i = 0; i < kPieces; ++i) {
-          const uint32_t sc = (sw >> (8 * ((MODE == 1 ? 0 : half * 2) + i))) & 0xff;
+          const uint32_t sc = (sw >> (8 * (half * 2 + i))) & 0xff;
           uint32_t v[16];
           dequant8x4(p[i], scale_mul2(sc), v);
           tmem_st_32x16(dst + i * 16, v);
@@ -675,7 +723,8 @@ int launch_moe_gemm(const void* w, const uint8_t* scales, const void* x, int x_r
   using S = MoeSmem<MODE, NT>;
   CUtensorMap tmW, tmX;
   const uint64_t wrows = (uint64_t)e_local * (MODE == 1 ? 2 : 1) * rows_per_expert;
-  if (dsv4_make_tmap_2d(&tmW, w, 0, (uint64_t)K / 2, wrows, (uint64_t)K / 2, 128, kRowsTile, 3)) return 201;
+  if (dsv4_make_tmap_2d(&tmW, w, 0, (uint64_t)K / 2, wrows, (uint64_t)K / 2, 128, MODE == 1 ? 64 : kRowsTile, 3))
+    return 201;
   if (dsv4_make_tmap_2d(&tmX, x, 1, (uint64_t)K, (uint64_t)x_rows, (uint64_t)K * 2, 64, NT, 3)) return 202;
   auto kern = moe_gemm_kernel<MODE, NT>;
   static bool set = false;
