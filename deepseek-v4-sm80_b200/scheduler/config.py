@@ -19,6 +19,8 @@ class SchedulerConfig(EngineConfig):
     offline_mode: bool = False
     stats_log_interval: float = 10.0
     disable_log_stats: bool = False
+    heartbeat_name: str = ""          # shared-memory heartbeat board created by the server launcher ("" = none)
+    heartbeat_timeout: float = 120.0  # seconds without a stamp, while busy, before a rank counts as wedged
     _unique_suffix: str = ""
 
     @property

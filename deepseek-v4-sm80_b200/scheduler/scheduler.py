@@ -74,6 +74,15 @@ class Scheduler:
         self.step_log: List[Dict[str, Any]] = []
         self.record_steps = False
         self.bytes_h2d = self.bytes_d2h = 0
+        self.heartbeat = None
+        if getattr(config, "heartbeat_name", ""):
+            from ..utils.heartbeat import HeartbeatBoard
+
+            self.heartbeat = HeartbeatBoard(config.heartbeat_name, self.tp.size, create=False)
+
+    def _beat(self, busy: bool) -> None:
+        if self.heartbeat is not None:
+            self.heartbeat.beat(self.tp.rank, busy)
 
     # ------------------------------------------------------------------ messages
     def _process_one_msg(self, msg) -> None:
@@ -266,6 +275,7 @@ class Scheduler:
 
     def overlap_loop(self, last: Optional[ForwardData]) -> Optional[ForwardData]:
         blocking = self._idle() and last is None
+        self._beat(busy=not blocking)  # an idle rank blocks in receive and is not expected to stamp
         for msg in self.receive_msg(blocking):
             self._process_one_msg(msg)
         if isinstance(self.engine.sampler, ReasoningSampler):
@@ -282,6 +292,7 @@ class Scheduler:
 
     def normal_loop(self) -> None:
         blocking = self._idle()
+        self._beat(busy=not blocking)
         for msg in self.receive_msg(blocking):
             self._process_one_msg(msg)
         nxt = self._schedule_next_batch()

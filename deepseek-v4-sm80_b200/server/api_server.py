@@ -229,6 +229,12 @@ class FrontendManager:
                 dead = self.supervisor.unexpected_exit()
                 if dead is not None:
                     self.mark_backend_unavailable(f"backend process {dead[0]} exited with code {dead[1]}")
+            board = getattr(self, "heartbeat", None)
+            if board is not None and self.available:
+                wedged = board.stale(self.heartbeat_timeout)
+                if wedged:
+                    self.mark_backend_unavailable(f"scheduler rank(s) {wedged} stopped making progress "
+                                                  f"(no heartbeat for {self.heartbeat_timeout:.0f} s while busy)")
 
     def mark_backend_unavailable(self, reason: str) -> None:
         """Terminal state: wake every waiter, refuse new work, stop the children."""
@@ -479,6 +485,8 @@ def run_api_server(args, start_backend: Callable[[], Any]) -> None:
     supervisor = start_backend()
     send = ZmqAsyncPushQueue(send_addr, create=False)
     frontend = FrontendManager(recv, send, supervisor)
+    frontend.heartbeat = getattr(supervisor, "heartbeat", None)
+    frontend.heartbeat_timeout = getattr(args, "heartbeat_timeout", 120.0)
     info = ServeInfo(args.model_names, args.model_path)
     app = create_app(frontend, info)
 

@@ -67,7 +67,12 @@ def backend_specs(args: ServerArgs) -> List[ProcessSpec]:
 
 
 def start_server_processes(args: ServerArgs) -> ServerProcessSupervisor:
+    from ..utils.heartbeat import HeartbeatBoard
+
+    board = HeartbeatBoard(None, args.tp_info.size, create=True)  # the schedulers attach by name and stamp it
+    args = dataclasses.replace(args, heartbeat_name=board.name)
     sup = ServerProcessSupervisor()
+    sup.heartbeat = board
     sup.start(backend_specs(args))
     return sup
 

@@ -97,6 +97,9 @@ class ServerProcessSupervisor:
         if self.shut_down:
             return
         self.shut_down = True
+        board = getattr(self, "heartbeat", None)
+        if board is not None:
+            board.close()
         if graceful is not None:
             try:
                 graceful()

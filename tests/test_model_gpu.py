@@ -39,3 +39,33 @@ def test_gpu_forward_matches_cpu_oracle():
     n4 = 300 // 4
     a, b = gpu.pool.c4[0][:n4 + 64].float().cpu(), cpu.pool.c4[0][:n4 + 64].float()
     assert rel(a, b) < 0.2, rel(a, b)
+
+
+def test_poisoned_caches_do_not_change_the_output():
+    """Stale-state proof: fill every cache, ring and checkpoint buffer with NaN (0xFF bytes for the FP8 rows) before
+    the first token.  Every kernel may only read rows that this run wrote, so prefill chunks and decode steps must
+    give bit-identical logits to a run that started from zeroed buffers."""
+    cfg = _cfg()
+    w = {k: v.cuda() for k, v in synth.random_weights(cfg, "cpu", seed=4).items()}
+    g = torch.Generator().manual_seed(2)
+    a_toks = torch.randint(0, cfg.vocab_size, (300,), generator=g).tolist()
+    b_toks = torch.randint(0, cfg.vocab_size, (140,), generator=g).tolist()
+    kw = dict(page_size=256, num_pages=8, num_slots=3, max_len=1024)
+
+    def run(poison):
+        r = MiniRunner(cfg, "cuda", weights=w, **kw)
+        if poison:
+            p = r.pool
+            for t in (p.swa, p.c4, p.c128, p.c4_ring, p.idx_ring, p.c128_ring, p.c4_ckpt, p.idx_ckpt, p.idx_scale):
+                t.fill_(float("nan"))
+            p.idx_vals.fill_(0xFF)
+        outs = [r.step([(0, a_toks[:200]), (1, b_toks[:100])]), r.step([(0, a_toks[200:]), (1, b_toks[100:])])]
+        for t in (5, 6, 7, 8, 9):
+            outs.append(r.step([(0, [t]), (1, [t + 20])]))
+        torch.cuda.synchronize()
+        return outs
+
+    clean, dirty = run(False), run(True)
+    for i, (c, d) in enumerate(zip(clean, dirty)):
+        assert torch.isfinite(d).all(), f"step {i}: NaN leaked from an unowned row"
+        assert torch.equal(c, d), f"step {i}: output depends on bytes this run never wrote"

@@ -262,3 +262,59 @@ def test_message_roundtrip():
     assert t.text == [{"role": "user", "content": "x"}]
     d = unpack(pack(DetokenizeMsg(3, 17, True, "stop")))
     assert (d.uid, d.next_token, d.finished, d.finish_reason) == (3, 17, True, "stop")
+
+
+def test_heartbeat_board_flags_a_wedged_rank_only_while_busy():
+    """Liveness of running schedulers: a rank that reported work and then stops stamping is flagged; an idle rank and
+    a rank that keeps stamping are not.  No GPU, no real hang: the clock is passed in."""
+    from minisgl.utils.heartbeat import HeartbeatBoard
+
+    board = HeartbeatBoard(None, 3, create=True)
+    try:
+        peer = HeartbeatBoard(board.name, 3, create=False)  # as a scheduler process attaches
+        assert board.stale(10.0, now=1000.0) == []           # nobody has stamped yet
+        peer.beat(0, busy=True, now=1000.0)
+        peer.beat(1, busy=False, now=1000.0)                 # idle: blocked in receive
+        peer.beat(2, busy=True, now=1000.0)
+        assert board.stale(10.0, now=1005.0) == []
+        peer.beat(2, busy=True, now=1050.0)                  # rank 2 keeps going, rank 0 went silent mid-work
+        assert board.stale(10.0, now=1055.0) == [0]
+        assert board.read(2)[0] == 2
+        peer.shm.close()
+    finally:
+        board.close()
+
+
+def test_frontend_marks_backend_unavailable_on_stale_heartbeat():
+    import asyncio
+
+    from minisgl.server.api_server import FrontendManager
+    from minisgl.utils.heartbeat import HeartbeatBoard
+
+    class Q:
+        async def get(self):
+            await asyncio.sleep(3600)
+
+        async def put(self, m):
+            pass
+
+    board = HeartbeatBoard(None, 1, create=True)
+    try:
+        board.beat(0, busy=True, now=1.0)  # stamped long ago (epoch time 1 s), still "busy"
+
+        async def run():
+            f = FrontendManager(Q(), Q(), None)
+            f.heartbeat, f.heartbeat_timeout = board, 5.0
+            f.start()
+            for _ in range(40):
+                if not f.available:
+                    break
+                await asyncio.sleep(0.1)
+            for t in f._tasks:
+                t.cancel()
+            return f
+
+        f = asyncio.run(run())
+        assert not f.available and "heartbeat" in f.unavailable_reason
+    finally:
+        board.close()
