@@ -99,9 +99,38 @@ def profile_report() -> dict:
     return dict(sorted(out.items(), key=lambda kv: -kv[1][1]))
 
 
+_ARITY = {}
+
+
+def _arity(name: str):
+    """Number of parameters of the exported ``dsv4_<name>`` as written in the CUDA sources (None if not found).
+    ctypes cannot check a call against the C prototype; a stale argument list would read garbage pointers, so
+    :func:`call` compares the count before every first call of an entry point."""
+    if not _ARITY:
+        import glob
+        import re
+
+        src_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
+        for path in glob.glob(os.path.join(src_dir, "*.cu")):
+            src = open(path, encoding="utf-8").read()
+            for m in re.finditer(r"DSV4_API\s+int\s+(dsv4_\w+)\s*\(([^)]*)\)", src):
+                params = m.group(2).strip()
+                _ARITY[m.group(1)] = 0 if params in ("", "void") else params.count(",") + 1
+        _ARITY["__loaded__"] = -1
+    return _ARITY.get("dsv4_" + name)
+
+
+_CHECKED = set()
+
+
 def call(name: str, *args) -> None:
     """Calls ``dsv4_<name>(*args, stream)`` and raises on a non-zero return code."""
     fn = getattr(cuda_lib(), "dsv4_" + name)
+    if name not in _CHECKED:
+        want = _arity(name)
+        if want is not None and want != len(args) + 1:
+            raise NativeError(f"dsv4_{name} takes {want} arguments (stream included), the caller passed {len(args) + 1}")
+        _CHECKED.add(name)
     _LAUNCHES[0] += 1
     if _PROFILE["on"]:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -153,7 +153,8 @@ class SymmComm(Comm):
             return xout
         out = torch.empty(t, h, dtype=rows.dtype, device=rows.device)
         nv.call("moe_finalize_allreduce", nv.ptr(rows), nv.ptr(plan), I(t * topk), I(max_tiles), nv.ptr(shared),
-                nv.ptr(out), nv.ptr(num_valid), I(t), I(topk), I(h), ctypes.byref(self.ctx[self.CH_MOE]))
+                nv.ptr(out), nv.ptr(num_valid), I(t), I(topk), I(h), nv.ptr(None), nv.ptr(None), nv.ptr(None),
+                nv.ptr(None), ctypes.byref(self.ctx[self.CH_MOE]))
         return out
 
     def all_gather_last(self, x: torch.Tensor) -> torch.Tensor:
