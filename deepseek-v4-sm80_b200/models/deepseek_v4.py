@@ -167,7 +167,8 @@ class DSV4Model:
             gu = O.gemm_fp8(yq[0], yq[1], w[p + "sh_gate_up.weight"], w[p + "sh_gate_up.scale"])
             aq = O.silu_mul_clamp_quant(gu, cfg.swiglu_limit)
             shared = O.gemm_fp8(aq[0], aq[1], w[p + "sh_down.weight"], w[p + "sh_down.scale"])
-        idx, wt = O.moe_gate(y, w[p + "gate.weight"], w.get(p + "gate.bias"), cfg.num_experts_per_tok,
+        gate_w = w[p + "gate.weight_bf16"] if y.is_cuda and (p + "gate.weight_bf16") in w else w[p + "gate.weight"]
+        idx, wt = O.moe_gate(y, gate_w, w.get(p + "gate.bias"), cfg.num_experts_per_tok,
                              cfg.routed_scaling_factor, cfg.scoring_func, w.get(p + "gate.tid2eid"), fb.input_ids,
                              fb.num_valid)
         if y.is_cuda:

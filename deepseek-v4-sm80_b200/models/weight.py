@@ -144,6 +144,7 @@ def build_layer(cfg: ModelConfig, l: int, raw: Dict[str, torch.Tensor], rank: in
         out[p + "attn.idx.comp.norm"] = g("attn.indexer.compressor.norm.weight").float().contiguous()
     # MoE
     out[p + "moe.gate.weight"] = g("ffn.gate.weight").float().contiguous()
+    out[p + "moe.gate.weight_bf16"] = g("ffn.gate.weight").to(torch.bfloat16).contiguous()  # tensor-core operand
     if "ffn.gate.tid2eid" in raw:
         out[p + "moe.gate.tid2eid"] = g("ffn.gate.tid2eid").to(torch.int32).contiguous()
     if "ffn.gate.bias" in raw:

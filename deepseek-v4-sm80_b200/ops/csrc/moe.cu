@@ -40,8 +40,9 @@ __global__ void moe_topk_kernel(const float* __restrict__ scores, const float* _
                                 long long part_stride) {
   pdl_entry();
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  // scores may come as n_part split-K partial products (spaced part_stride floats apart); score_all() adds them in
-  // split order with the loads of all of a lane's experts in flight together
+  if (row >= t_rows) return;  // the last CTA may hold a warp past the last token
+  // scores come as n_part split-K partial products (spaced part_stride floats apart); they are added below in split
+  // order, with the loads of all of a lane's experts in flight together
   if (num_valid && row >= *num_valid) {
     if (lane < k) idx[row * k + lane] = -1, wts[row * k + lane] = 0.f;
     return;

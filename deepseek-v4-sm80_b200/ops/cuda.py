@@ -254,17 +254,14 @@ _NO_ROPE = RopeSpec.make(64, 10000.0, 0, 1.0, 32, 1)
 
 # --------------------------------------------------------------------------- MoE
 _SCORING = {"sqrtsoftplus": 0, "sigmoid": 1, "softmax": 2}
-_GATE_BF16 = {}
 
 
 def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid=None):
     from .gemm import gemm_bf16_partials
 
-    key = gate_w.data_ptr()
-    wb = _GATE_BF16.get(key)
-    if wb is None:  # the router weight is bf16 in the checkpoint; its fp32 copy converts back losslessly
-        wb = gate_w.to(torch.bfloat16)
-        _GATE_BF16[key] = wb
+    # the router weight is bf16 in the checkpoint (its fp32 copy converts back losslessly); the model passes the bf16
+    # tensor it keeps next to the fp32 one.  No cache keyed by address here: a later model may reuse the address.
+    wb = gate_w if gate_w.dtype == torch.bfloat16 else gate_w.to(torch.bfloat16)
     t, e = y.shape[0], gate_w.shape[0]
     scores = gemm_bf16_partials(y, wb)  # [S, T, E]; the selection kernel adds the splits
     idx = torch.empty(t, topk, dtype=torch.int32, device=y.device)
