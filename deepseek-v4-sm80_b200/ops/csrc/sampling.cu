@@ -15,7 +15,9 @@ __device__ __forceinline__ uint32_t okey(float f) {
   const uint32_t u = __float_as_uint(f);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
-__device__ __forceinline__ unsigned long long fx(float p) { return (unsigned long long)((double)p * 1099511627776.0); }
+// p * 2^40 truncated.  Multiplying a float by a power of two is exact, so the single-precision product equals the
+// double-precision one the oracle computes; the FP64 pipe (slow on this part) stays out of the per-element path.
+__device__ __forceinline__ unsigned long long fx(float p) { return __float2ull_rz(p * 1099511627776.0f); }
 
 __device__ __forceinline__ unsigned long long block_scan_u64(unsigned long long v, unsigned long long* wt,
                                                              unsigned long long& total) {
@@ -116,12 +118,39 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int i = tid; i < 256; i += 1024) hcnt[i] = 0, hmass[i] = 0ull;
     __syncthreads();
-    for (int i = tid; i < v; i += 1024) {
-      const float x = val(i);
-      const uint32_t key = okey(x);
-      if ((key & mask) == prefix) {
-        atomicAdd(&hcnt[(key >> shift) & 0xff], 1);
-        atomicAdd(&hmass[(key >> shift) & 0xff], fx(expf((x - mx) * inv_t)));
+    // Histogram of the candidates' next key byte.  The top bytes of nearly all logits agree, so per-element atomics
+    // would serialise on a handful of addresses: a warp whose active lanes all hit one bin adds once (the masses are
+    // fixed point, so any order gives the same sums).
+    for (int i0 = 0; i0 < v; i0 += 1024) {
+      const int i = i0 + tid;
+      bool act = false;
+      uint32_t bin = 0;
+      unsigned long long m = 0;
+      if (i < v) {
+        const float x = val(i);
+        const uint32_t key = okey(x);
+        if ((key & mask) == prefix) {
+          act = true;
+          bin = (key >> shift) & 0xff;
+          m = fx(expf((x - mx) * inv_t));
+        }
+      }
+      // one pair of atomics per distinct bin of the warp: 64-bit shared atomics under same-address contention are
+      // what made the first version of this loop take milliseconds
+      unsigned todo = __ballot_sync(0xffffffffu, act);
+      while (todo) {  // `todo` is warp-uniform
+        const int leader = __ffs(todo) - 1;
+        const uint32_t bin0 = __shfl_sync(0xffffffffu, bin, leader);
+        const bool mine = act && bin == bin0;
+        const unsigned grp = __ballot_sync(0xffffffffu, mine);
+        unsigned long long sm = mine ? m : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+        if (lane == leader) {
+          atomicAdd(&hcnt[bin0], __popc(grp));
+          atomicAdd(&hmass[bin0], sm);
+        }
+        todo &= ~grp;
       }
     }
     __syncthreads();
@@ -149,47 +178,49 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
     mass_above = sh_mass_above;
     __syncthreads();
   }
-  // kept: key > prefix, plus threshold ties in id order while count < k and mass before < p
-  // pass A: total kept mass ; pass B: walk to u * kept
+  // kept: key > prefix, plus threshold ties in id order while count < k and mass before < p.
+  // Every thread owns a contiguous range of ids, so "in id order" needs three block scans in total (ties before the
+  // thread, tie mass before it, kept mass before it) and sequential walks inside the thread's own range.
   const float u = uniform ? uniform[b] : 0.5f;
-  unsigned long long kept_total = 0, target = 0;
-  for (int pass = 0; pass < 2; ++pass) {
-    unsigned long long run = 0;          // kept mass so far (id order)
-    int eq_cnt = 0;                      // threshold ties kept so far
-    unsigned long long eq_mass = 0;
-    int found = -1;
-    for (int c0 = 0; c0 < v; c0 += 1024) {
-      const int i = c0 + tid;
-      float x = -INFINITY;
-      uint32_t key = 0;
-      if (i < v) x = val(i), key = okey(x);
-      const unsigned long long pm = i < v ? fx(expf((x - mx) * inv_t)) : 0ull;
-      const int eq = i < v && key == prefix;
-      unsigned long long eqm_tot, dummy;
-      const unsigned long long eqm_before = eq_mass + block_scan_u64(eq ? pm : 0ull, wt, eqm_tot);
-      unsigned long long eqc_tot;
-      const int eqc_before = eq_cnt + (int)block_scan_u64(eq ? 1ull : 0ull, wt, eqc_tot);
-      const bool keep = i < v && (key > prefix || (eq && cnt_above + eqc_before < k_limit &&
-                                                   mass_above + eqm_before < p_limit));
-      const unsigned long long before = run + block_scan_u64(keep ? pm : 0ull, wt, dummy);
-      if (pass == 1 && keep && before + pm > target && before <= target) found = i;
-      run += dummy;
-      eq_cnt += (int)eqc_tot;
-      eq_mass += eqm_tot;
-      if (pass == 1) {
-        __syncthreads();
-        if (found >= 0) si[1] = found;
-        __syncthreads();
+  const int per = (v + 1023) / 1024;
+  const int i_lo = min(tid * per, v), i_hi = min(i_lo + per, v);
+  unsigned long long my_eq_mass = 0;
+  int my_eq_cnt = 0;
+  for (int i = i_lo; i < i_hi; ++i) {
+    const float x = val(i);
+    if (okey(x) == prefix) ++my_eq_cnt, my_eq_mass += fx(expf((x - mx) * inv_t));
+  }
+  unsigned long long tot;
+  const int eqc_before = (int)block_scan_u64((unsigned long long)my_eq_cnt, wt, tot);
+  const unsigned long long eqm_before = block_scan_u64(my_eq_mass, wt, tot);
+  auto walk = [&](unsigned long long start, unsigned long long target, bool find) -> unsigned long long {
+    // returns the kept mass of this thread's range, or (find) the id at which the running kept mass passes target
+    unsigned long long run = start, em = eqm_before;
+    int ec = eqc_before;
+    for (int i = i_lo; i < i_hi; ++i) {
+      const float x = val(i);
+      const uint32_t key = okey(x);
+      const unsigned long long pm = fx(expf((x - mx) * inv_t));
+      const bool eq = key == prefix;
+      const bool keep = key > prefix || (eq && cnt_above + ec < k_limit && mass_above + em < p_limit);
+      if (eq) ++ec, em += pm;
+      if (keep) {
+        if (find && run + pm > target && run <= target) return (unsigned long long)i;
+        run += pm;
       }
     }
-    if (pass == 0) {
-      kept_total = run;
-      double tt = (double)u * (double)kept_total;
-      target = (unsigned long long)tt;
-      if (target >= kept_total && kept_total > 0) target = kept_total - 1;
-      if (tid == 0) si[1] = amax;
-      __syncthreads();
-    }
+    return find ? ~0ull : run - start;
+  };
+  const unsigned long long my_kept = walk(0ull, 0ull, false);
+  unsigned long long kept_total;
+  const unsigned long long kept_before = block_scan_u64(my_kept, wt, kept_total);
+  unsigned long long target = (unsigned long long)((double)u * (double)kept_total);
+  if (target >= kept_total && kept_total > 0) target = kept_total - 1;
+  if (tid == 0) si[1] = amax;  // fallback (empty kept set cannot happen: the maximum is always kept)
+  __syncthreads();
+  if (my_kept > 0 && target >= kept_before && target < kept_before + my_kept) {
+    const unsigned long long id = walk(kept_before, target, true);
+    if (id != ~0ull) si[1] = (int)id;
   }
   __syncthreads();
   if (tid == 0) out[b] = si[1];
