@@ -40,13 +40,22 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
     if bn == 0:
         fill = NUM_SMS_HINT * 2 // 3
         if mt == 1:
-            # one row tile (decode): every column tile re-reads the whole activation from L2, so take the widest tile
-            # that, together with up to 8 K splits, still yields enough CTAs
-            smax = max(min(8, k_tiles // 4), 1)
-            for cand in ((64, 32) if fp8 else (128, 64, 32)):
-                bn = cand
-                if ((n + cand - 1) // cand) * smax >= fill:
-                    break
+            # One row tile (decode).  Every column tile re-reads the whole activation from L2, so wider tiles are
+            # cheaper per byte; but a split costs a cluster launch and two cluster barriers (about 4 us measured, 8 us
+            # for 8-way), so: no split when 32-wide tiles alone fill the GPU, else the widest tile that fills it with
+            # at most 4 splits.
+            # FP8 stays at 32 columns: its epilogue warps promote every 128-wide K block out of tensor memory, work
+            # that grows with the tile width and is the per-k-tile bottleneck (0.33 us at 32 columns, 0.8 at 64).
+            if fp8:
+                bn = 32
+            elif (n + 31) // 32 >= fill:
+                bn = 128 if (n + 127) // 128 >= fill else 64 if (n + 63) // 64 >= fill else 32
+            else:
+                smax = max(min(4, k_tiles // 4), 1)
+                for cand in (128, 64, 32):
+                    bn = cand
+                    if ((n + cand - 1) // cand) * smax >= fill:
+                        break
         elif mt * ((n + 127) // 128) >= fill and not fp8:
             bn = 128  # the widest tile that still gives about one CTA per SM
         elif mt * ((n + 63) // 64) >= fill:
@@ -60,7 +69,7 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
         splits = 1
         if ctas <= NUM_SMS_HINT // 2 and k_tiles >= 8:
             # the splits of a tile form one thread-block cluster (2, 4 or 8 CTAs) that reduces in shared memory
-            want = max(min(NUM_SMS_HINT // ctas, k_tiles // 4, 8), 1)
+            want = max(min(NUM_SMS_HINT // ctas, k_tiles // 4, 4 if mt == 1 else 8), 1)
             splits = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1
     if mt * ((n + bn - 1) // bn) > (1 << 16):
         splits = 1
