@@ -11,8 +11,9 @@ full model's shapes:
                         per-token route sum + shared expert + all-reduce in one kernel vs unfused finalize + NCCL
 Times are per call inside a CUDA graph of `--iters` calls (no host launch gaps), with an L2 flush before every call
 whose own cost is subtracted, reduced with MAX over ranks.  The roofline of a
-fused call is the slower of FLOPs / measured GEMM peak and NVLink bytes / 770 GB/s (one-shot all-reduce: each GPU
-pulls (N-1) * M * 4096 * 2 bytes).
+fused call is the slower of FLOPs / measured GEMM peak and NVLink bytes / 770 GB/s, the bytes being those of the
+one-shot exchange ((N-1) * M * 4096 * 2 pulled by each GPU); above 256 rows the block-wise two-shot path moves
+2 * (N-1)/N * M * 4096 * 2 instead and can therefore read above 1.
 """
 from __future__ import annotations
 
@@ -117,7 +118,7 @@ def main(argv=None):
         nccl_buf = x.clone()
         link_bytes = (world - 1) * m * H * 2
         t_link = link_bytes / (NVLINK_GBS * 1e3)  # us
-        res = {"rows": m, "world": world}
+        res = {"rows": m, "world": world, "block_two_shot": bool(getattr(comm, "big", False) and m > 256)}
         res["allreduce_nccl_us"] = _time(lambda: dist.all_reduce(nccl_buf), a.iters, True)
         res["allreduce_ours_us"] = _time(lambda: comm.all_reduce(x), a.iters, True)
 

@@ -84,9 +84,25 @@ def main(argv=None):
     slots = _Slots(model, pool, cfg, dev, ps, a.batch, ((a.context + 128) // ps + 2) * ps)
     g = torch.Generator().manual_seed(0)
     per = max(1, 8192 // a.context)
-    for s0 in range(0, a.batch, per):
-        model.forward(slots.batch([(s, torch.randint(0, cfg.vocab_size, (a.context,), generator=g).tolist())
-                                   for s in range(s0, min(s0 + per, a.batch))]))
+    starts = list(range(0, a.batch, per))
+    prefill_ms, prefill_share = [], None
+    for s0 in starts:
+        fb = slots.batch([(s, torch.randint(0, cfg.vocab_size, (a.context,), generator=g).tolist())
+                          for s in range(s0, min(s0 + per, a.batch))])
+        torch.cuda.synchronize()
+        last = a.profile and s0 == starts[-1]
+        if last:  # per-launcher share of the last prefill forward (all its chunks' caches are warm by then)
+            native.enable_profile(True)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        model.forward(fb)
+        e1.record()
+        torch.cuda.synchronize()
+        prefill_ms.append(e0.elapsed_time(e1))
+        if last:
+            rep = native.profile_report()
+            native.enable_profile(False)
+            prefill_share = {k: round(t, 3) for k, (c, t) in list(rep.items())[:14]}
     torch.cuda.synchronize()
     n0 = native.launch_count()
     if a.profile:
@@ -96,7 +112,11 @@ def main(argv=None):
         model.forward(fb)
     torch.cuda.synchronize()
     launches = (native.launch_count() - n0) / a.steps
-    out = {"layers": a.layers, "tp": a.tp, "batch": a.batch, "context": a.context, "launches_per_step": launches}
+    out = {"layers": a.layers, "tp": a.tp, "batch": a.batch, "context": a.context, "launches_per_step": launches,
+           "prefill_tokens_per_forward": min(per, a.batch) * a.context,
+           "prefill_ms_per_forward": round(sorted(prefill_ms)[len(prefill_ms) // 2], 3)}
+    if prefill_share is not None:
+        out["prefill_share_ms"] = prefill_share
     if a.profile:
         rep = native.profile_report()
         native.enable_profile(False)

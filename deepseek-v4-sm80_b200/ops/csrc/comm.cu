@@ -7,49 +7,71 @@
 
 namespace {
 
-__global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
-                                                        int rows, int cols, const HcPostArgs hc, const CommCtx comm) {
+// BIG: the block-wise two-shot path for tensors of more than 256 rows (own instantiation: the row-wise paths of a
+// decode step keep their register allocation).
+template <bool BIG>
+__global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __restrict__ x,
+                                                        __nv_bfloat16* __restrict__ out, int rows, int cols,
+                                                        const HcPostArgs hc, const CommCtx comm) {
   pdl_entry();
   __shared__ int ok;
   const uint32_t epoch = comm_epoch(comm);
   const int parity = epoch & 1;
   __nv_bfloat16* mine = comm_data(comm, comm.rank, parity);
   const int c8 = cols / 8;
-  if (x) {  // x == null: the producer (a GEMM in deposit mode) already wrote this rank's partial into `mine`
-    for (int r = blockIdx.x; r < rows; r += gridDim.x)
-      for (int i = threadIdx.x; i < c8; i += blockDim.x)
-        reinterpret_cast<uint4*>(mine + (size_t)r * cols)[i] = reinterpret_cast<const uint4*>(x + (size_t)r * cols)[i];
-  }
-  __syncthreads();
-  auto emit_row = [&](int r) {
-    return [&, r](int col, const uint4& v) {
-      if (hc.res)
-        hc_post_store8(v, hc, r, cols, col);
-      else
-        *reinterpret_cast<uint4*>(out + (size_t)r * cols + col) = v;
-    };
-  };
-  if (comm_use_two_shot(comm, rows, cols)) {
-    if ((int)blockIdx.x < rows) comm_row_two_shot(comm, epoch, blockIdx.x, cols, &ok, emit_row(blockIdx.x));
-  } else {
-    if (threadIdx.x == 0) {
-      comm_publish(comm, blockIdx.x, epoch);
-      ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
+  // x == null: the producer (a GEMM in deposit mode) already wrote this rank's partial into `mine`
+  auto deposit = [&](int r0, int r1) {  // rows [r0, r1) are contiguous; four loads in flight per thread
+    if (!x) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)r0 * cols);
+    uint4* dst = reinterpret_cast<uint4*>(mine + (size_t)r0 * cols);
+    const int n8 = (r1 - r0) * c8;
+    for (int i = threadIdx.x; i < n8; i += blockDim.x * 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = i + u * (int)blockDim.x;
+        if (j < n8) v[u] = src[j];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = i + u * (int)blockDim.x;
+        if (j < n8) dst[j] = v[u];
+      }
     }
+  };
+  auto emit = [&](int r, int col, const uint4& v) {
+    if (hc.res)
+      hc_post_store8(v, hc, r, cols, col);
+    else
+      *reinterpret_cast<uint4*>(out + (size_t)r * cols + col) = v;
+  };
+  if constexpr (BIG) {
+    comm_big_two_shot(comm, epoch, rows, cols, &ok, deposit, emit);
+  } else {
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) deposit(r, r + 1);
     __syncthreads();
-    if (ok) {
-      for (int r = blockIdx.x; r < rows; r += gridDim.x) {
-        auto emit = emit_row(r);
-        for (int i = threadIdx.x; i < c8; i += 2 * blockDim.x) {
-          const int i1 = i + blockDim.x;
-          uint4 o0, o1;
-          if (i1 < c8) {
-            comm_reduce16x2(comm, parity, (size_t)r * cols + i * 8, (size_t)r * cols + i1 * 8, o0, o1);
-            emit(i1 * 8, o1);
-          } else {
-            o0 = comm_reduce16(comm, parity, (size_t)r * cols + i * 8);
+    if (comm_use_two_shot(comm, rows, cols)) {
+      const int r = blockIdx.x;
+      if (r < rows) comm_row_two_shot(comm, epoch, r, cols, &ok, [&](int col, const uint4& v) { emit(r, col, v); });
+    } else {
+      if (threadIdx.x == 0) {
+        comm_publish(comm, blockIdx.x, epoch);
+        ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
+      }
+      __syncthreads();
+      if (ok) {
+        for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+          for (int i = threadIdx.x; i < c8; i += 2 * blockDim.x) {
+            const int i1 = i + blockDim.x;
+            uint4 o0, o1;
+            if (i1 < c8) {
+              comm_reduce16x2(comm, parity, (size_t)r * cols + i * 8, (size_t)r * cols + i1 * 8, o0, o1);
+              emit(r, i1 * 8, o1);
+            } else {
+              o0 = comm_reduce16(comm, parity, (size_t)r * cols + i * 8);
+            }
+            emit(r, i * 8, o0);
           }
-          emit(i * 8, o0);
         }
       }
     }
@@ -95,9 +117,13 @@ DSV4_API int dsv4_allreduce(const void* x, void* out, int rows, int cols, const 
   if (cols % 8) return 500;
   if ((long long)rows * cols * 2 > comm->data_bytes) return 501;
   if (xout && (!res || !post || !comb)) return 502;
-  int grid = rows < 1024 ? rows : 1024;
   HcPostArgs hc{xout ? (const __nv_bfloat16*)res : nullptr, post, comb, (__nv_bfloat16*)xout};
-  dsv4_launch(allreduce_kernel, grid, 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, cols, hc, *comm);
+  if (comm_host_use_big(*comm, rows))
+    dsv4_launch(allreduce_kernel<true>, comm_big_grid(rows), 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out,
+                rows, cols, hc, *comm);
+  else
+    dsv4_launch(allreduce_kernel<false>, rows < 1024 ? rows : 1024, 256, 0, st, (const __nv_bfloat16*)x,
+                (__nv_bfloat16*)out, rows, cols, hc, *comm);
   return (int)cudaGetLastError();
 }
 

@@ -22,6 +22,7 @@ struct CommCtx {
   uint8_t* peer[kMaxRanks];   // symmetric base of every rank (peer[rank] is local)
   int rank, world;
   int channel;
+  int big;                    // 1: tensors of more than 256 rows use the block-wise two-shot path
   long long data_bytes;       // bytes of one parity buffer of one channel
   long long small_bytes;      // bytes of one result buffer of the two-shot path (0: none)
   int* epoch;                 // local [kCommChannels] device ints
@@ -224,6 +225,118 @@ __device__ __forceinline__ void comm_row_two_shot(const CommCtx& c, uint32_t epo
 __device__ __forceinline__ bool comm_use_two_shot(const CommCtx& c, int rows, int cols) {
   return c.world >= 4 && c.small_bytes > 0 && rows <= 256 && rows <= (int)gridDim.x &&
          (long long)rows * cols * 2 <= c.small_bytes;
+}
+
+// Two-shot all-reduce of a LARGE tensor (prefill: thousands of rows) by blocks of rows.  All CTAs of the grid call it
+// with all threads.  Block b = rows [b * R, (b + 1) * R) belongs to CTA b % grid in its pass b / grid, on every rank
+// alike, and is owned by rank (b % grid + b / grid) % world, which spreads each CTA's owned blocks over the ranks.
+//   phase A, per block: deposit(r0, r1) puts this rank's partial rows into its parity buffer (a no-op when an earlier
+//     kernel did that); a non-owner then raises flag[b] at the owner; the owner waits for the world-1 flags, sums the
+//     partials in rank order, stores the result rows IN PLACE into every peer's parity buffer (only the owner ever
+//     reads a block's partials, and each 16-byte piece is read before it is overwritten), emits them locally and
+//     raises flag[half + b] at every peer.
+//   phase B, per block not owned: wait for the owner's second flag, emit the rows from the own parity buffer.
+// Phase A never waits for a phase B, and a block's partials only need pass k of the same CTA index on the peers, so
+// the exchange makes progress whenever the grid is co-resident (the launchers size it so); every wait is bounded.
+// Per rank this moves 2 * (world-1)/world of the tensor over NVLink; the one-shot form moves (world-1) times it.
+// emit(row, col, v) receives 8 reduced bf16 values.
+__device__ __forceinline__ int comm_big_block_rows(int rows) {
+  int r = 8;
+  while ((rows + r - 1) / r > kTwoShotSlot) r *= 2;
+  return r;
+}
+inline bool comm_host_use_big(const CommCtx& c, int rows) { return c.world > 1 && c.big && rows > 256; }
+template <class Deposit, class Emit>
+__device__ __forceinline__ void comm_big_two_shot(const CommCtx& c, uint32_t epoch, int rows, int cols, int* sh_ok,
+                                                  Deposit deposit, Emit emit) {
+  const int parity = epoch & 1, G = gridDim.x, R = comm_big_block_rows(rows), nblk = (rows + R - 1) / R;
+  __nv_bfloat16* mine = comm_data(c, c.rank, parity);
+  for (int b = blockIdx.x, k = 0; b < nblk; b += G, ++k) {
+    const int r0 = b * R, r1 = min(rows, r0 + R), owner = (int)((blockIdx.x + k) % c.world);
+    deposit(r0, r1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      if (owner != c.rank) {
+        __threadfence_system();
+        st_relaxed_sys(comm_flag(c, owner, c.rank, b), epoch);
+      } else {
+        ok = comm_wait(c, b, epoch) ? 1 : 0;
+      }
+      *sh_ok = ok;
+    }
+    __syncthreads();
+    const int ok = *sh_ok;
+    if (owner == c.rank && ok) {
+      for (int r = r0; r < r1; ++r) {
+        const size_t off = (size_t)r * cols;
+        for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 16) {
+          const int i1 = i + blockDim.x * 8;
+          uint4 v0, v1 = make_uint4(0, 0, 0, 0);
+          if (i1 < cols)
+            comm_reduce16x2(c, parity, off + i, off + i1, v0, v1);
+          else
+            v0 = comm_reduce16(c, parity, off + i);
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p) {
+            if (p < c.world && p != c.rank) {
+              __nv_bfloat16* dst = comm_data(c, p, parity) + off;
+              st_peer16(dst + i, v0);
+              if (i1 < cols) st_peer16(dst + i1, v1);
+            }
+          }
+          emit(r, i, v0);
+          if (i1 < cols) emit(r, i1, v1);
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p)
+          if (p < c.world && p != c.rank) st_relaxed_sys(comm_flag(c, p, c.rank, kTwoShotSlot + b), epoch);
+      }
+    }
+    __syncthreads();  // *sh_ok is rewritten by the next pass
+    if (!ok) return;  // uniform over the CTA; the status word already holds the timeout
+  }
+  for (int b = blockIdx.x, k = 0; b < nblk; b += G, ++k) {
+    const int r0 = b * R, r1 = min(rows, r0 + R), owner = (int)((blockIdx.x + k) % c.world);
+    if (owner == c.rank) continue;
+    if (threadIdx.x == 0) *sh_ok = comm_wait_one(c, owner, kTwoShotSlot + b, epoch) ? 1 : 0;
+    __syncthreads();
+    const int ok = *sh_ok;
+    if (ok) {
+      // the block's rows are contiguous: four independent 16-byte loads per thread and trip
+      const int c8 = cols / 8, n8 = (r1 - r0) * c8;
+      const uint4* src = reinterpret_cast<const uint4*>(mine + (size_t)r0 * cols);
+      for (int i = threadIdx.x; i < n8; i += blockDim.x * 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = i + u * (int)blockDim.x;
+          if (j < n8) v[u] = ld_peer16(src + j);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = i + u * (int)blockDim.x;
+          if (j < n8) emit(r0 + j / c8, (j % c8) * 8, v[u]);
+        }
+      }
+    }
+    __syncthreads();
+    if (!ok) return;
+  }
+}
+// Grid of a kernel on the block-wise path: one CTA of 256 threads per SM at most, so that all of them are co-resident.
+inline int comm_big_grid(int rows) {
+  int r = 8;
+  while ((rows + r - 1) / r > kTwoShotSlot) r *= 2;
+  const int nblk = (rows + r - 1) / r;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return nblk < sms ? nblk : sms;
 }
 
 // Last CTA of the grid advances the channel epoch (call once per CTA, by one thread, at the very end).

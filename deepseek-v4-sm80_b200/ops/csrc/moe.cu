@@ -638,6 +638,8 @@ __global__ void moe_finalize_kernel(const __nv_bfloat16* __restrict__ yr, const 
 
 // Fused combine: the per-token sum of the local routes (+ the shared expert) is this rank's partial of the layer
 // output; it goes to the symmetric buffer and is reduced across ranks in the same kernel (protocol in comm.cuh).
+// BIG: block-wise two-shot exchange for more than 256 tokens (prefill), see comm_big_two_shot.
+template <bool BIG>
 __global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat16* __restrict__ yr,
                                                               const int* __restrict__ route_pos,
                                                               const __nv_bfloat16* __restrict__ shared,
@@ -650,65 +652,71 @@ __global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat1
   const int parity = epoch & 1;
   __nv_bfloat16* mine = comm_data(comm, comm.rank, parity);
   const int nv = num_valid ? *num_valid : t_rows;
-  for (int t = blockIdx.x; t < t_rows; t += gridDim.x) {
-    const bool valid = t < nv;
-    for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      uint4 o = make_uint4(0, 0, 0, 0);
-      if (valid) {
-        for (int k = 0; k < topk; ++k) {
-          if (route_pos[t * topk + k] < 0) continue;
-          const uint4 u = *reinterpret_cast<const uint4*>(yr + ((size_t)t * topk + k) * h + i);
-          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+  // this rank's partial of rows [t0, t1): routes summed in fp32, rounded, + shared expert, into the parity buffer
+  auto combine = [&](int t0, int t1) {
+    for (int t = t0; t < t1; ++t) {
+      const bool valid = t < nv;
+      for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (valid) {
+          for (int k = 0; k < topk; ++k) {
+            if (route_pos[t * topk + k] < 0) continue;
+            const uint4 u = *reinterpret_cast<const uint4*>(yr + ((size_t)t * topk + k) * h + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(p[j]);
+              acc[2 * j] += f.x, acc[2 * j + 1] += f.y;
+            }
+          }
+          const uint4 su = *reinterpret_cast<const uint4*>(shared + (size_t)t * h + i);
+          const __nv_bfloat162* sp = reinterpret_cast<const __nv_bfloat162*>(&su);
+          __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(p[j]);
-            acc[2 * j] += f.x, acc[2 * j + 1] += f.y;
+            const float2 r2 = __bfloat1622float2(__floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]));
+            const float2 s2 = __bfloat1622float2(sp[j]);
+            po[j] = __floats2bfloat162_rn(r2.x + s2.x, r2.y + s2.y);
           }
         }
-        const uint4 su = *reinterpret_cast<const uint4*>(shared + (size_t)t * h + i);
-        const __nv_bfloat162* sp = reinterpret_cast<const __nv_bfloat162*>(&su);
-        __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 r2 = __bfloat1622float2(__floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]));
-          const float2 s2 = __bfloat1622float2(sp[j]);
-          po[j] = __floats2bfloat162_rn(r2.x + s2.x, r2.y + s2.y);
-        }
+        *reinterpret_cast<uint4*>(mine + (size_t)t * h + i) = o;
       }
-      *reinterpret_cast<uint4*>(mine + (size_t)t * h + i) = o;
     }
-  }
-  __syncthreads();
-  auto emit_row = [&](int t) {
-    return [&, t](int col, const uint4& v) {
-      if (hc.res)
-        hc_post_store8(v, hc, t, h, col);
-      else
-        *reinterpret_cast<uint4*>(out + (size_t)t * h + col) = v;
-    };
   };
-  if (comm_use_two_shot(comm, t_rows, h)) {
-    if ((int)blockIdx.x < t_rows) comm_row_two_shot(comm, epoch, blockIdx.x, h, &ok, emit_row(blockIdx.x));
+  auto emit = [&](int t, int col, const uint4& v) {
+    if (hc.res)
+      hc_post_store8(v, hc, t, h, col);
+    else
+      *reinterpret_cast<uint4*>(out + (size_t)t * h + col) = v;
+  };
+  if constexpr (BIG) {
+    comm_big_two_shot(comm, epoch, t_rows, h, &ok, combine, emit);
   } else {
-    if (threadIdx.x == 0) {
-      comm_publish(comm, blockIdx.x, epoch);
-      ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
-    }
+    for (int t = blockIdx.x; t < t_rows; t += gridDim.x) combine(t, t + 1);
     __syncthreads();
-    if (ok) {
-      for (int t = blockIdx.x; t < t_rows; t += gridDim.x) {
-        auto emit = emit_row(t);
-        for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 16) {
-          const int i1 = i + blockDim.x * 8;
-          uint4 o0, o1;
-          if (i1 < h) {
-            comm_reduce16x2(comm, parity, (size_t)t * h + i, (size_t)t * h + i1, o0, o1);
-            emit(i1, o1);
-          } else {
-            o0 = comm_reduce16(comm, parity, (size_t)t * h + i);
+    if (comm_use_two_shot(comm, t_rows, h)) {
+      const int t = blockIdx.x;
+      if (t < t_rows) comm_row_two_shot(comm, epoch, t, h, &ok, [&](int col, const uint4& v) { emit(t, col, v); });
+    } else {
+      if (threadIdx.x == 0) {
+        comm_publish(comm, blockIdx.x, epoch);
+        ok = comm_wait(comm, blockIdx.x, epoch) ? 1 : 0;
+      }
+      __syncthreads();
+      if (ok) {
+        for (int t = blockIdx.x; t < t_rows; t += gridDim.x) {
+          for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 16) {
+            const int i1 = i + blockDim.x * 8;
+            uint4 o0, o1;
+            if (i1 < h) {
+              comm_reduce16x2(comm, parity, (size_t)t * h + i, (size_t)t * h + i1, o0, o1);
+              emit(t, i1, o1);
+            } else {
+              o0 = comm_reduce16(comm, parity, (size_t)t * h + i);
+            }
+            emit(t, i, o0);
           }
-          emit(i, o0);
         }
       }
     }
@@ -817,9 +825,12 @@ DSV4_API int dsv4_moe_finalize_allreduce(const void* yr, const int* plan, int ro
   if (h % 8 || (long long)t * h * 2 > comm->data_bytes) return 230;
   if (xout && (!res || !post || !comb)) return 231;
   const int* route_pos = plan + 4 + 3 * max_tiles + routes;
-  const int grid = t < 1024 ? t : 1024;
-  dsv4_launch(moe_finalize_ar_kernel, grid, 256, 0, st, (const __nv_bfloat16*)yr, route_pos,
-              (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, num_valid, topk, h, t,
-              HcPostArgs{xout ? (const __nv_bfloat16*)res : nullptr, post, comb, (__nv_bfloat16*)xout}, *comm);
+  const HcPostArgs hc{xout ? (const __nv_bfloat16*)res : nullptr, post, comb, (__nv_bfloat16*)xout};
+  if (comm_host_use_big(*comm, t))
+    dsv4_launch(moe_finalize_ar_kernel<true>, comm_big_grid(t), 256, 0, st, (const __nv_bfloat16*)yr, route_pos,
+                (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, num_valid, topk, h, t, hc, *comm);
+  else
+    dsv4_launch(moe_finalize_ar_kernel<false>, t < 1024 ? t : 1024, 256, 0, st, (const __nv_bfloat16*)yr, route_pos,
+                (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, num_valid, topk, h, t, hc, *comm);
   return (int)cudaGetLastError();
 }

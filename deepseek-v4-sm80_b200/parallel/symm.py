@@ -29,13 +29,16 @@ from .info import DistributedInfo
 import os as _os
 
 _SKIP_EXCHANGE = _os.environ.get("MINISGL_SKIP_EXCHANGE", "0") == "1"
+# MINISGL_BIG_ALLREDUCE=0 keeps tensors of more than 256 rows (prefill) on the one-shot exchange.
+_BIG = _os.environ.get("MINISGL_BIG_ALLREDUCE", "1") == "1"
 
 MAX_RANKS = 8
 
 
 class CommCtx(ctypes.Structure):
     _fields_ = [("peer", ctypes.c_void_p * MAX_RANKS), ("rank", ctypes.c_int), ("world", ctypes.c_int),
-                ("channel", ctypes.c_int), ("data_bytes", ctypes.c_longlong), ("small_bytes", ctypes.c_longlong),
+                ("channel", ctypes.c_int), ("big", ctypes.c_int), ("data_bytes", ctypes.c_longlong),
+                ("small_bytes", ctypes.c_longlong),
                 ("epoch", ctypes.c_void_p), ("done", ctypes.c_void_p)]
 
 
@@ -81,6 +84,37 @@ class SymmComm(Comm):
             x.done = self.state.data_ptr() + 4 * self.channels
             self.ctx.append(x)
         self.counters = {"all_reduce": 0, "gemm_allreduce": 0, "moe_allreduce": 0, "all_gather": 0}
+        self.big = False
+        if _BIG and self.size > 1 and not _SKIP_EXCHANGE and max_rows >= 512:
+            self._enable_big(hidden)
+
+    def _set_big(self, on: bool) -> None:
+        self.big = on
+        for x in self.ctx:
+            x.big = 1 if on else 0
+
+    def _enable_big(self, hidden: int) -> None:
+        """Switch the block-wise two-shot path on, reduce one 512-row tensor with it and with NCCL, and keep it only
+        if every rank saw the same sums and no wait ran out (otherwise all ranks fall back to the one-shot exchange
+        together)."""
+        from ..utils.logger import init_logger
+
+        g = torch.Generator(device="cpu").manual_seed(1234 + self.rank)
+        x = torch.randn(512, hidden, generator=g).to(self.device, torch.bfloat16)
+        want = x.float()
+        dist.all_reduce(want, group=self.group)
+        self._set_big(True)
+        got = self.all_reduce(x)
+        torch.cuda.synchronize(self.device)
+        status = nv.read_status(clear=True)
+        good = status[0] == 0 and bool(torch.isfinite(got).all()) and float((got.float() - want).abs().max()) < 0.25
+        flag = torch.tensor([1 if good else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self._set_big(False)
+            init_logger(__name__).warning("block-wise two-shot all-reduce failed its start-up check "
+                                          f"(status {status[:4]}); prefill uses the one-shot exchange")
+        self.counters["all_reduce"] = 0
 
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, x: torch.Tensor, tag: str = "") -> torch.Tensor:
@@ -92,9 +126,11 @@ class SymmComm(Comm):
         return out
 
     def gemm_fp8_allreduce(self, xq, sx, w, ws, bn: int = 0, hc=None) -> torch.Tensor:
-        """out = all_reduce(xq @ w^T).  Up to 256 rows (decode) the GEMM deposits its partial product in the channel's
-        symmetric buffer and the row-wise all-reduce kernel follows (its peer reads are whole rows; the GEMM
-        epilogue's would be 64-byte pieces of 128 x 32 tiles); above, the reduction runs in the GEMM's epilogue.
+        """out = all_reduce(xq @ w^T).  The GEMM deposits its partial product in the channel's symmetric buffer and the
+        all-reduce kernel follows as its programmatic dependent: row-wise up to 256 rows (decode; its peer reads are
+        whole rows, the GEMM epilogue's would be 64-byte pieces of 128 x 32 tiles), block-wise two-shot above
+        (prefill; 2 * (world-1)/world of the tensor crosses NVLink per rank instead of world-1 times the tensor).
+        With the block-wise path off, large tensors are reduced in the GEMM's epilogue.
         hc = (residual, post, comb): the hyper-connection post mix is applied to the reduced rows by the same kernel
         and the new residual streams [m, 4, n] are returned."""
         m, k = xq.shape
@@ -106,7 +142,7 @@ class SymmComm(Comm):
             y = O.gemm_fp8(xq, sx, w, ws)
             return O.hc_post(y, *hc) if hc is not None else y
         ctx = ctypes.byref(self.ctx[self.CH_ATTN])
-        if m <= 256:
+        if m <= 256 or self.big:
             nv.call("gemm_fp8_allreduce", nv.ptr(xq), nv.ptr(w), nv.ptr(None), nv.ptr(sx), nv.ptr(ws), I(m), I(n), I(k),
                     I(xq.stride(0)), I(w.stride(0)), ctx, I(bn), I(1))
             if hc is not None:

@@ -52,13 +52,15 @@ def main():
         dev = torch.device("cuda", torch.cuda.current_device())
         cfg = dataclasses.replace(ModelConfig.flash().with_layers(4), n_routed_experts=16, vocab_size=4096,
                                   n_hash_layers=1)
-        _, comm = init_distributed(info, dev, vocab_size=cfg.vocab_size, max_rows=1024, hidden=cfg.hidden_size)
+        _, comm = init_distributed(info, dev, vocab_size=cfg.vocab_size, max_rows=2048, hidden=cfg.hidden_size)
         from minisgl.ops import native, quant
         from minisgl.parallel.symm import SymmComm
 
         assert isinstance(comm, SymmComm), type(comm)
+        assert comm.big, "the block-wise two-shot path failed its start-up check"
         # 1) stand-alone all-reduce vs NCCL, several sizes, repeated (epochs / parity buffers)
-        for rows in (1, 8, 128, 1000):
+        # (2000 rows: more blocks than CTAs, i.e. several passes of the block-wise path)
+        for rows in (1, 8, 128, 257, 1000, 2000):
             for it in range(3):
                 x = (torch.randn(rows, 4096, device=dev, generator=None) * (rank + 1)).to(torch.bfloat16)
                 ref = x.float().clone()
@@ -69,7 +71,7 @@ def main():
         # 2) fused FP8 GEMM + all-reduce vs separate GEMM + NCCL
         from minisgl.ops import api as O
 
-        for m in (1, 8, 128, 300):
+        for m in (1, 8, 128, 300, 1500):
             xx = torch.randn(m, 1024, device=dev).to(torch.bfloat16)
             ww = torch.randn(4096, 1024, device=dev) * 0.02
             wq, wsc = quant.fp8_weight_quant(ww)
@@ -87,7 +89,8 @@ def main():
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         assert float(lo) == float(hi)
         # 3) whole model: tensor/expert parallel vs single rank
-        toks = torch.randint(0, cfg.vocab_size, (200,), generator=g).tolist()
+        # (600 prompt tokens: the prefill's collectives take the block-wise path, the decode steps the row-wise one)
+        toks = torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist()
         kw = dict(page_size=256, num_pages=8, num_slots=2, max_len=1024)
         tp = MiniRunner(cfg, dev, comm=comm, moe_mode=args.moe_mode, rank=rank, size=world, seed=2, **kw)
         l_tp = tp.step([(0, toks)])
