@@ -95,7 +95,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   using Cfg = GemmCfg<BN>;
   constexpr int S = Cfg::kStages;
   constexpr int BK = FP8 ? 128 : 64;  // elements per k-tile (= 128 bytes)
-  constexpr uint32_t kTmemCols = FP8 ? (2 * BN < 32 ? 32 : 2 * BN) : (BN < 32 ? 32 : BN);
+  // FP8: every 128-wide k-tile gets an accumulator of its own, promoted by the epilogue warps with the tile's scales.
+  // kAcc of them rotate (256 tensor-memory columns, 512 for the widest tile), so that the MMA issuer runs several
+  // tiles ahead of the promotion instead of waiting for a round trip through two buffers.
+  constexpr uint32_t kTmemCols = FP8 ? (BN <= 128 ? 256 : 2 * BN) : (BN < 32 ? 32 : BN);
+  constexpr int kAcc = FP8 ? (int)kTmemCols / BN : 1;
+  static_assert((kAcc & (kAcc - 1)) == 0 && kAcc <= 8, "accumulator ring");
   constexpr uint32_t kIdesc = FP8 ? umma_idesc(kBM, BN, 0, 0) : umma_idesc(kBM, BN, 1, 1);
 
   extern __shared__ uint8_t smem_raw[];
@@ -103,9 +108,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint8_t* tiles = smem;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
   uint64_t* empty = full + S;
-  uint64_t* tfull = empty + S;   // [2]
-  uint64_t* tempty = tfull + 2;  // [2]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* tfull = empty + S;   // [8]
+  uint64_t* tempty = tfull + 8;  // [8]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   volatile int* sh_flag = reinterpret_cast<volatile int*>(tmem_holder + 2);
 
@@ -125,10 +130,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
-    mbar_init(&tfull[0], 1);
-    mbar_init(&tfull[1], 1);
-    mbar_init(&tempty[0], 128);
-    mbar_init(&tempty[1], 128);
+    for (int i = 0; i < 8; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 128);
+    }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -180,8 +185,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t ph = (i / S) & 1;
         uint32_t d = tmem_base;
         if (FP8) {
-          const int b = i & 1;
-          if (!mbar_wait(&tempty[b], ((i >> 1) & 1) ^ 1, abort_flag, 2)) break;
+          const int b = i & (kAcc - 1);
+          if (!mbar_wait(&tempty[b], ((i / kAcc) & 1) ^ 1, abort_flag, 2)) break;
           d = tmem_base + b * BN;
         }
         if (!mbar_wait(&full[s], ph, abort_flag, 3)) break;
@@ -199,7 +204,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             umma_f16(d, ad, bd, kIdesc, acc);
         }
         umma_commit(&empty[s]);
-        if (FP8) umma_commit(&tfull[i & 1]);
+        if (FP8) umma_commit(&tfull[i & (kAcc - 1)]);
       }
       if (!FP8 && nkt > 0) umma_commit(&tfull[0]);
     }
@@ -241,8 +246,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const size_t sb_row = (size_t)((batch * g.b_row_pb + n0) >> 7) * g.sb_ld;
       const int kblocks = k_tiles;
       for (int i = 0; i < nkt; ++i) {
-        const int b = i & 1;
-        if (!mbar_wait(&tfull[b], (i >> 1) & 1, abort_flag, 5)) {
+        const int b = i & (kAcc - 1);
+        if (!mbar_wait(&tfull[b], (i / kAcc) & 1, abort_flag, 5)) {
           ok = false;
           break;
         }
