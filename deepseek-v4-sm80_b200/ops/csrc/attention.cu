@@ -92,7 +92,7 @@ template <int HL>
 __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnArgs a) {
   pdl_entry();
   using C = AttnCfg<HL>;
-  constexpr int HP = C::HP, MT = C::MT, G = C::G, KT = C::KT, NT = C::NT, TPR = C::TPR, PCH = C::PCH;
+  constexpr int HP = C::HP, MT = C::MT, KT = C::KT, NT = C::NT, TPR = C::TPR, PCH = C::PCH;
   constexpr int NTHR = C::NW * 32;
   extern __shared__ __align__(128) uint8_t attn_smem[];
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(attn_smem);   // [HP][D] swizzled

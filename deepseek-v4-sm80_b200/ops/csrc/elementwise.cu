@@ -16,16 +16,6 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
   t = warp_sum(t);
   return t;
 }
-__device__ __forceinline__ float block_max(float v, float* sh) {
-  v = warp_max(v);
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (l == 0) sh[w] = v;
-  __syncthreads();
-  float t = (l < nw) ? sh[l] : -INFINITY;
-  t = warp_max(t);
-  return t;
-}
 
 // ------------------------------------------------------------------ embedding
 __global__ void embed_kernel(const int* __restrict__ ids, const uint4* __restrict__ w, uint4* __restrict__ out, int m,
