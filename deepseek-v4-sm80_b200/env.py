@@ -44,6 +44,7 @@ class _Env:
     DISABLE_FUSED_COMM = EnvVar("DISABLE_FUSED_COMM", False, _bool)
     DISABLE_MULTIMEM = EnvVar("DISABLE_MULTIMEM", False, _bool)
     NVTX = EnvVar("NVTX", False, _bool)
+    DEBUG_BOUNDS = EnvVar("DEBUG_BOUNDS", False, _bool)
 
 
 ENV = _Env()

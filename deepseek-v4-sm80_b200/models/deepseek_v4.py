@@ -77,6 +77,9 @@ class DSV4Model:
             # the weights of this model are never written after loading: let the GEMMs fetch them ahead of the
             # dependent-launch wait
             native.check(native.cuda_lib().dsv4_gemm_set_weight_prefetch(1), "dsv4_gemm_set_weight_prefetch")
+        from ..env import ENV
+
+        self._debug_bounds = bool(ENV.DEBUG_BOUNDS)  # audit every gathered index tensor before use
         self._side = None  # second CUDA stream for branches that do not depend on each other (created on first use)
 
     # ------------------------------------------------------------------ independent branches on a second stream
@@ -149,6 +152,8 @@ class DSV4Model:
             qc, wf = O.indexer_q_encode(iq, iw, fb.positions, rope, cfg.index_head_dim ** -0.5,
                                         cfg.index_n_heads ** -0.5)
             topk_idx, topk_len = O.indexer_select(qc, wf, kvv["idx_vals"], kvv["idx_scale"], fb, ps, cfg.index_topk)
+            if self._debug_bounds:
+                O.check_index(topk_idx, -1, max(fb.max_context // 4, 1), "indexer_topk")
         o = O.attention(q, fb, kvv["swa"], self.pool.swa_map, kvv.get("comp"), ratio, topk_idx, topk_len,
                         w[p + "sink"], cfg.head_dim ** -0.5, ps, cfg.window_size, out_rope=rope)
         o2 = O.gemm_bf16_grouped(o.reshape(t, self.h_local * cfg.head_dim), w[p + "wo_a.weight_bf16"], self.g_local)
@@ -171,6 +176,8 @@ class DSV4Model:
         idx, wt = O.moe_gate(y, gate_w, w.get(p + "gate.bias"), cfg.num_experts_per_tok,
                              cfg.routed_scaling_factor, cfg.scoring_func, w.get(p + "gate.tid2eid"), fb.input_ids,
                              fb.num_valid)
+        if self._debug_bounds:
+            O.check_index(idx, -1, cfg.n_routed_experts, "expert_ids")
         if y.is_cuda:
             # routed rows stay per route; the combine kernel sums them with the shared expert (and, with fused
             # communication, all-reduces the result in the same kernel)
@@ -205,9 +212,24 @@ class DSV4Model:
         return x
 
     # ------------------------------------------------------------------ forward
+    def audit_inputs(self, fb: ForwardBatch) -> None:
+        """Checked runs (MINISGL_DEBUG_BOUNDS=1): every index tensor the kernels gather with is audited against its
+        range before use; a violation is recorded in the device status word (CPU: raised) instead of being
+        dereferenced.  The sanitizer-free counterpart of the reference's fail-closed wrappers
+        (python/minisgl/kernel/deepseek_v4.py of the reference validates shapes and dtypes, not values)."""
+        cfg = self.cfg
+        locs = self.pool.sizes.num_pages * self.pool.page_size
+        O.check_index(fb.input_ids, 0, cfg.vocab_size, "input_ids")
+        O.check_index(fb.positions, 0, fb.page_table.shape[1], "positions")
+        O.check_index(fb.slots, 0, fb.page_table.shape[0], "slots")
+        O.check_index(fb.out_loc, -1, locs, "out_loc")
+        O.check_index(fb.page_table, 0, locs, "page_table")
+
     def forward(self, fb: ForwardBatch) -> torch.Tensor:
         """Returns fp32 logits [B, vocab] for the rows ``fb.last_idx``."""
         cfg, w = self.cfg, self.w
+        if self._debug_bounds:
+            self.audit_inputs(fb)
         x = O.embed(fb.input_ids, w["embed.weight"], cfg.hc_mult)
         for l in range(cfg.num_layers):
             x = self.layer(l, x, fb)

@@ -51,6 +51,20 @@ def comp_rows_from_idx(fb, idx, ps: int, ratio: int):
     return torch.where(loc >= 0, ref.comp_row(loc.clamp_min(0), ps, ratio), torch.full_like(loc, -1))
 
 
+# --------------------------------------------------------------------------- index audit (MINISGL_DEBUG_BOUNDS=1)
+INDEX_TAGS = {"input_ids": 1, "positions": 2, "slots": 3, "out_loc": 4, "page_table": 5, "expert_ids": 6,
+              "indexer_topk": 7}
+
+
+def check_index(idx, lo: int, hi: int, what: str) -> None:
+    """Every entry of ``idx`` must lie in [lo, hi).  CUDA: a device kernel records a violation in the status word
+    (no synchronisation; ``native.assert_device_ok()`` raises it); CPU: raises at once."""
+    if idx.is_cuda:
+        return _cu().check_index(idx.contiguous(), lo, hi, INDEX_TAGS[what])
+    if idx.numel() and (int(idx.min()) < lo or int(idx.max()) >= hi):
+        raise IndexError(f"{what}: index outside [{lo}, {hi})")
+
+
 # --------------------------------------------------------------------------- elementwise
 def embed(ids, weight, m: int):
     if ids.is_cuda:

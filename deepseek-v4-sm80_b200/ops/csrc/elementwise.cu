@@ -331,6 +331,18 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
   }
 }
 
+// ------------------------------------------------------------------ index audit (checked runs)
+// Every index the forward gathers with (token ids, cache locations, page-table entries, expert ids) can be audited
+// before use: an entry outside [lo, hi) is recorded in the status word as DSV4_ERR_BAD_INDEX with the caller's tag and
+// the entry's position, and nothing is dereferenced with it here.  The audited kernels themselves stay unchanged.
+__global__ void index_check_kernel(const int* __restrict__ idx, long long n, int lo, int hi, int tag) {
+  pdl_entry();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int v = idx[i];
+    if (v < lo || v >= hi) dsv4_set_error(DSV4_ERR_BAD_INDEX, tag, (int)(i < 0x7fffffff ? i : 0x7fffffff));
+  }
+}
+
 }  // namespace
 
 DSV4_API int dsv4_embed(const int* ids, const void* w, void* out, int t, int m, int h, cudaStream_t st) {
@@ -408,5 +420,12 @@ DSV4_API int dsv4_q_kv_norm_rope_store(void* q, void* kv, int ldkv, const int* p
 DSV4_API int dsv4_argmax(const float* logits, long long* out, int rows, int v, cudaStream_t st) {
   if (rows <= 0) return 0;
   dsv4_launch(argmax_kernel, rows, 1024, 0, st, logits, out, v);
+  return (int)cudaGetLastError();
+}
+// Audits n int32 indices against [lo, hi); see index_check_kernel.  tag identifies the audited tensor in the status word.
+DSV4_API int dsv4_check_index(const int* idx, long long n, int lo, int hi, int tag, cudaStream_t st) {
+  if (n <= 0) return 0;
+  const long long blocks = (n + 255) / 256;
+  dsv4_launch(index_check_kernel, (unsigned)(blocks < 1184 ? blocks : 1184), 256, 0, st, idx, n, lo, hi, tag);
   return (int)cudaGetLastError();
 }

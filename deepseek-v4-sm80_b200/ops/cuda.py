@@ -48,6 +48,13 @@ def _i32(t):
 
 
 # --------------------------------------------------------------------------- elementwise
+def check_index(idx, lo: int, hi: int, tag: int) -> None:
+    """Audit int32 indices against [lo, hi) on the device; a violation lands in the status word (code 2, tag, position)
+    and is raised by the next ``native.assert_device_ok()``."""
+    assert idx.dtype == torch.int32 and idx.is_contiguous()
+    nv.call("check_index", nv.ptr(idx), ctypes.c_longlong(idx.numel()), I(lo), I(hi), I(tag))
+
+
 def embed(ids, weight, m: int):
     t, h = ids.shape[0], weight.shape[1]
     out = torch.empty(t, m, h, dtype=weight.dtype, device=weight.device)

@@ -57,3 +57,19 @@ def test_cache_state_matches_between_chunked_and_single_shot():
     assert same > 0.9, same
     close = ((a.pool.swa[1][:150].float() - b.pool.swa[1][:150].float()).abs() < 5e-2).float().mean()
     assert close > 0.98, close  # an e4m3 rounding flip in the QAT step moves a value by a full fp8 ulp
+
+
+def test_checked_run_audits_gathered_indices(monkeypatch):
+    """MINISGL_DEBUG_BOUNDS=1: a forward with valid indices passes the audit (and gives the same logits); a token id
+    outside the vocabulary is refused before anything is gathered with it."""
+    import pytest
+
+    cfg = ModelConfig.tiny()
+    toks = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(3)).tolist()
+    plain = MiniRunner(cfg, "cpu", seed=5).step([(0, toks)])
+    monkeypatch.setenv("MINISGL_DEBUG_BOUNDS", "1")
+    checked = MiniRunner(cfg, "cpu", seed=5)
+    assert checked.model._debug_bounds
+    assert torch.equal(checked.step([(0, toks)]), plain)
+    with pytest.raises(IndexError, match="input_ids"):
+        checked.step([(1, [cfg.vocab_size + 7])])

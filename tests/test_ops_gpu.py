@@ -349,3 +349,24 @@ def test_sampling():
     exp = O.sample(lg, temp, tk, tp, u, mask)
     assert torch.equal(out.cpu(), exp), (out.cpu(), exp)
     assert torch.equal(O.argmax(lg.to(DEV)).cpu(), lg.argmax(-1))
+
+
+@pytest.mark.gpu
+def test_index_audit_records_a_violation_without_touching_memory():
+    """The checked-run audit kernel: in-range indices leave the status word clear; an out-of-range entry is recorded
+    as code 2 with the caller's tag and the entry's position, nothing is dereferenced, and kernels still run after."""
+    from minisgl.ops import api as O
+    from minisgl.ops import native
+
+    native.read_status(clear=True)
+    idx = torch.randint(0, 1000, (5000,), device="cuda", dtype=torch.int32)
+    idx[17] = -1
+    O.check_index(idx, -1, 1000, "out_loc")
+    assert native.read_status()[0] == 0
+    idx[4321] = 1000
+    O.check_index(idx, -1, 1000, "out_loc")
+    st = native.read_status(clear=True)
+    assert st[0] == 2 and st[1] == O.INDEX_TAGS["out_loc"] and st[2] == 4321, st
+    O.check_index(idx[:4000].contiguous(), -1, 1000, "out_loc")
+    assert native.read_status()[0] == 0
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0
