@@ -85,7 +85,9 @@ struct AttnCfg {
   static constexpr int NT = DW / 8;                      // output n-tiles per warp
   static constexpr int TPR = NW * 32 / HP;               // softmax threads per head row
   static constexpr int PCH = KT / 8;                     // 16-byte chunks per probability row
-  static constexpr int SMEM = HP * D * 2 + 2 * KT * D * 2 + HP * KT * 4 + HP * KT * 2 + 3 * HP * 4 + 2 * KT * 4;
+  static constexpr int RB = 1024;                        // keys whose rows are resolved per pass (multiple of KT)
+  static constexpr int SMEM =
+      HP * D * 2 + 2 * KT * D * 2 + HP * KT * 4 + HP * KT * 2 + 3 * HP * 4 + 2 * KT * 4 + RB * 4;
 };
 
 template <int HL>
@@ -103,6 +105,9 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
   float* ms = alpha + HP;                                            // [HP]
   float* ls = ms + HP;                                               // [HP]
   int* valid = reinterpret_cast<int*>(ls + HP);                      // [2][KT]
+  int* rowsrc = valid + 2 * KT;                                      // [RB] resolved cache row per key, -1: masked
+  constexpr int RB = C::RB;
+  constexpr int kSwaBit = 1 << 30;                                   // set: row of the window cache, else compressed
 
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (a.num_valid && t >= *a.num_valid) {
@@ -129,26 +134,49 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
   }
   if (tid < HP) ms[tid] = tid < HL ? a.sink[tid] : 0.f, ls[tid] = 1.f;
 
+  // Rows of keys [base, base + RB) -> rowsrc.  A key's row hangs on a chain of two or three dependent loads
+  // (selected index -> page-table entry -> window slot); resolving a tile's keys right before its gather would put
+  // that chain in front of every tile, so all keys of a pass are resolved together, stage by stage, each thread
+  // keeping RB / NTHR independent chains in flight.  A decode token (at most 128 + 512 keys) needs one pass.
+  auto resolve = [&](int base) {
+    constexpr int PER = RB / NTHR;
+    int ppos[PER], loc[PER];
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int key = base + tid + u * NTHR;
+      ppos[u] = -1;
+      if (key < nc) {
+        const int j = a.mode == 1 ? a.topk_idx[(size_t)t * a.topk_width + key] : key;
+        if (j >= 0) ppos[u] = j * a.ratio + a.ratio - 1;
+      } else if (key < ntot) {
+        ppos[u] = p - ns + 1 + (key - nc);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < PER; ++u) loc[u] = ppos[u] >= 0 ? pt[ppos[u]] : -1;
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int key = base + tid + u * NTHR;
+      int e = -1;
+      if (loc[u] >= 0) {
+        if (key < nc) {
+          e = (loc[u] / a.ps) * rpp + (loc[u] % a.ps) / a.ratio;
+        } else {
+          const int sl = a.swa_map[loc[u] / a.ps];
+          if (sl >= 0) e = (sl * a.ps + loc[u] % a.ps) | kSwaBit;
+        }
+      }
+      rowsrc[tid + u * NTHR] = e;
+    }
+  };
+
   constexpr int TPK = NTHR / KT;       // threads cooperating on one key row
   constexpr int CPT = 64 / TPK;        // 16-byte chunks per thread
   auto issue_tile = [&](int tile, int buf) {
     const int kk = tid / TPK, part = tid % TPK;
-    const int key = tile * KT + kk;
+    const int e = rowsrc[(tile * KT + kk) % RB];
     const __nv_bfloat16* src = nullptr;
-    if (key < ntot) {
-      if (key < nc) {
-        const int j = a.mode == 1 ? a.topk_idx[(size_t)t * a.topk_width + key] : key;
-        if (j >= 0) {
-          const int loc = pt[j * a.ratio + a.ratio - 1];
-          src = a.comp + ((size_t)(loc / a.ps) * rpp + (loc % a.ps) / a.ratio) * D;
-        }
-      } else {
-        const int pp = p - ns + 1 + (key - nc);
-        const int loc = pt[pp];
-        const int sl = a.swa_map[loc / a.ps];
-        if (sl >= 0) src = a.swa + ((size_t)sl * a.ps + loc % a.ps) * D;
-      }
-    }
+    if (e >= 0) src = (e & kSwaBit) ? a.swa + (size_t)(e & (kSwaBit - 1)) * D : a.comp + (size_t)e * D;
     __nv_bfloat16* dst = kvs + ((size_t)buf * KT + kk) * D;
     const __nv_bfloat16* s0 = src ? src : a.swa;
 #pragma unroll
@@ -165,10 +193,14 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
 #pragma unroll
   for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-  if (ntiles > 0) issue_tile(0, 0);
-  for (int tile = 0; tile < ntiles; ++tile) {
+  for (int base = 0; base < ntot; base += RB) {
+  const int tile_lo = base / KT, tile_hi = min(ntiles, (base + RB) / KT);
+  resolve(base);
+  __syncthreads();
+  issue_tile(tile_lo, tile_lo & 1);
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int buf = tile & 1;
-    if (tile + 1 < ntiles) {
+    if (tile + 1 < tile_hi) {
       issue_tile(tile + 1, buf ^ 1);
       cp_async_wait<1>();
     } else {
@@ -261,6 +293,7 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
       }
     }
     __syncthreads();
+  }
   }
   __syncthreads();
   {
