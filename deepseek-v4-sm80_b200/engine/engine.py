@@ -98,6 +98,9 @@ class Engine:
         self.page_table[self.dummy_slot] = row.to(self.device)
         self.last_token = torch.zeros(config.max_running_req + 1, dtype=torch.int32, device=self.device)
         self.model = DSV4Model(cfg, self.weights, self.pool, self.comm, config.moe_mode)
+        self.model_prepare_report = self.model.prepare_report()
+        logger.info_rank0("model prepared: %s", {k: v for k, v in self.model_prepare_report.items()
+                                                 if k != "derived_bytes"})
         self.sampler: Sampler = Sampler(self.device, cfg.vocab_size, config.seed)
         self.reasoning_token_ids = None
         self.graph_runner = None

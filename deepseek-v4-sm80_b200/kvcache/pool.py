@@ -195,6 +195,26 @@ class DSV4KVPool:
         if drop:
             self.release_swa(drop)
 
+    def runtime_swa_counters(self) -> dict:
+        """Window-storage residency at this moment plus the lifetime counters: slots in use / free, pages whose
+        window rows were recycled while the page stayed valid (tombstoned), pins by owner, and how often the device
+        copy of the page -> slot map changed (python/minisgl/kvcache/deepseek_v4_pool.py:1206-1227 of the reference
+        reports the same residency figures)."""
+        live = sum(1 for p, s in enumerate(self._swa_map_host) if s >= 0 and p != self.dummy_page)
+        held = sum(1 for p in range(self.sizes.num_pages) if self.page_ref[p] > 0)
+        return {
+            "swa_slots_total": self.sizes.num_swa_slots,
+            "swa_slots_in_use": live,
+            "swa_slots_free": len(self.free_swa),
+            "pages_in_use": held,
+            "pages_without_window": held - sum(1 for p in range(self.sizes.num_pages)
+                                               if self.page_ref[p] > 0 and self._swa_map_host[p] >= 0),
+            "pages_pinned_by_tree": len(self._tree_pinned),
+            "pages_pinned": sum(1 for c in self.swa_pins if c > 0),
+            "swa_map_version": self.swa_version,
+            **self.counters,
+        }
+
     def has_swa(self, page: int) -> bool:
         return self._swa_map_host[page] >= 0
 

@@ -212,6 +212,33 @@ class DSV4Model:
         return x
 
     # ------------------------------------------------------------------ forward
+    def prepare_report(self) -> dict:
+        """What the loaded weights occupy on this rank, by storage format, and which derived tensors were built at
+        load time.  The reference rebuilds BF16 caches and a Marlin repack at every start and reports them in
+        ``model_prepare_report`` (python/minisgl/models/deepseek_v4.py:1718-1787); here FP8 / FP4 weights are consumed
+        in place, so the derived part is small: the dequantised ``wo_a``, the bf16 router weight and the stacked
+        compressor projection."""
+        by_fmt, derived = {}, {}
+        for k, v in self.w.items():
+            if not isinstance(v, torch.Tensor):
+                continue
+            n = v.numel() * v.element_size()
+            if k.endswith((".w13", ".w2")):
+                fmt = "fp4_packed"
+            elif k.endswith((".s13", ".s2")):
+                fmt = "e8m0_scales"
+            else:
+                fmt = str(v.dtype).replace("torch.", "")
+            by_fmt[fmt] = by_fmt.get(fmt, 0) + n
+            if k.endswith(("gate.weight_bf16", "comp_all.wkv_gate")) or ".wo_a." in k and v.dtype == torch.bfloat16:
+                derived[k.split(".", 1)[1]] = derived.get(k.split(".", 1)[1], 0) + n
+        return {"rank": self.comm.rank, "world": self.comm.size, "moe_mode": self.moe_mode,
+                "experts_local": int(self.w["L0.moe.w13"].shape[0]), "expert_base": self.expert_base,
+                "heads_local": self.h_local, "o_groups_local": self.g_local,
+                "bytes_by_format": by_fmt, "bytes_total": sum(by_fmt.values()),
+                "derived_bytes": derived, "repack": "none (FP4 experts and FP8 projections are read in place)",
+                "weight_prefetch_before_dependency_wait": bool(self.w["embed.weight"].is_cuda)}
+
     def audit_inputs(self, fb: ForwardBatch) -> None:
         """Checked runs (MINISGL_DEBUG_BOUNDS=1): every index tensor the kernels gather with is audited against its
         range before use; a violation is recorded in the device status word (CPU: raised) instead of being

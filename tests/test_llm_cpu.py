@@ -55,3 +55,11 @@ def test_prefix_reuse_gives_same_tokens():
     assert llm.cache.radix.metrics["hit_tokens"] - hit0 == 128  # 160 shared tokens -> the 128-aligned boundary
     assert second.token_ids == _reference_tokens(cfg, b, 4, 16)
     assert first.token_ids == _reference_tokens(cfg, a, 4, 16)
+    # structured reports: weight preparation and window-storage residency
+    rep = llm.engine.model_prepare_report
+    assert rep["bytes_total"] == sum(rep["bytes_by_format"].values()) > 0 and rep["experts_local"] == 8
+    assert {"fp4_packed", "e8m0_scales", "float8_e4m3fn"} <= set(rep["bytes_by_format"])
+    swa = llm.engine.pool.runtime_swa_counters()
+    assert swa["swa_slots_in_use"] + swa["swa_slots_free"] == swa["swa_slots_total"]
+    assert swa["swa_taken"] - swa["swa_released"] == swa["swa_slots_in_use"]
+    assert swa["pages_pinned_by_tree"] > 0  # the cached prefix keeps its window rows
