@@ -44,7 +44,9 @@ def parse():
     ap.add_argument("--moe-mode", default="ep", choices=["ep", "tp"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-fused-comm", action="store_true")
-    return ap.parse_args()
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)  # fewer than three untimed steps would leave clocks and caches cold
+    return args
 
 
 class ClockSampler:
