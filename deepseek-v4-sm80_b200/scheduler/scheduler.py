@@ -248,8 +248,12 @@ class Scheduler:
         req.lifecycle.commit_terminal(reason)
         self.pending_retire.append(req)
         self.finished_uids.add(req.uid)
-        if announce and reason != "abort":
-            self._reply(DetokenizeMsg(req.uid, 0, True, reason))
+        if announce:
+            msg = DetokenizeMsg(req.uid, 0, True, reason)
+            if reason != "abort":
+                self._reply(msg)
+            else:
+                self._on_reply(msg)  # nobody waits for an aborted request online; the offline collector does
         self._retire_ready()
 
     def _retire_ready(self) -> None:
