@@ -13,6 +13,7 @@ class UserReply:
     finished: bool
     finish_reason: Optional[str] = None
     num_tokens: int = 0
+    prompt_tokens: Optional[int] = None
 
 
 @message

@@ -28,6 +28,7 @@ class DetokenizeMsg:
     next_token: int
     finished: bool
     finish_reason: Optional[str] = None
+    prompt_tokens: Optional[int] = None   # set on a request's first reply (for the usage record)
 
 
 @message

@@ -230,7 +230,9 @@ class Scheduler:
             done_len = not req.can_commit_token
             finished = done_eos or done_len
             reason = "stop" if done_eos else ("length" if done_len else None)
-            replies.append(DetokenizeMsg(req.uid, tok, finished, reason))
+            # the first reply of a request (the one its last prefill chunk produces) carries the prompt length
+            replies.append(DetokenizeMsg(req.uid, tok, finished, reason,
+                                         req.prompt_len if batch.is_prefill else None))
             if batch.is_prefill:
                 self.cache.cache_req(req, finished=False)
             self.cache.release_swa_behind(req)

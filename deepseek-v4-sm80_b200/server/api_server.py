@@ -382,7 +382,7 @@ def create_app(frontend, info: ServeInfo) -> FastAPI:
 
         if req.stream:
             async def sse():
-                n_out, finish = 0, None
+                n_out, n_in, finish = 0, 0, None
                 try:
                     yield _chunk(cid, model, created, {"role": "assistant", "content": ""})
                     async for r in frontend.stream(uid):
@@ -394,6 +394,7 @@ def create_app(frontend, info: ServeInfo) -> FastAPI:
                             yield "data: [DONE]\n\n"
                             return
                         n_out = r.num_tokens or n_out
+                        n_in = r.prompt_tokens or n_in
                         rs, ct = parser.feed(r.incremental_output, final=r.finished)
                         if rs:
                             yield _chunk(cid, model, created, {"reasoning_content": rs})
@@ -403,7 +404,7 @@ def create_app(frontend, info: ServeInfo) -> FastAPI:
                             finish = "length" if r.finish_reason == "length" else "stop"
                     yield _chunk(cid, model, created, {}, finish or "stop")
                     if req.stream_options and req.stream_options.include_usage:
-                        yield _chunk(cid, model, created, {}, usage=usage_of(n_out), choices=False)
+                        yield _chunk(cid, model, created, {}, usage=usage_of(n_out, n_in), choices=False)
                     yield "data: [DONE]\n\n"
                 except BackendUnavailable as e:
                     yield f"data: {json.dumps({'error': {'message': str(e), 'type': 'server_error', 'param': None, 'code': 'backend_unavailable'}})}\n\n"
@@ -413,7 +414,7 @@ def create_app(frontend, info: ServeInfo) -> FastAPI:
 
             return StreamingResponse(sse(), media_type="text/event-stream")
 
-        reasoning, content, n_out, finish = [], [], 0, "stop"
+        reasoning, content, n_out, n_in, finish = [], [], 0, 0, "stop"
         try:
             async for r in frontend.stream(uid):
                 if await request.is_disconnected():
@@ -425,6 +426,7 @@ def create_app(frontend, info: ServeInfo) -> FastAPI:
                 if r.finished and r.finish_reason not in (None, "stop", "length", "abort"):
                     raise APIError(500, f"backend error: {r.finish_reason}", "backend_error", None, "server_error")
                 n_out = r.num_tokens or n_out
+                n_in = r.prompt_tokens or n_in
                 rs, ct = parser.feed(r.incremental_output, final=r.finished)
                 reasoning.append(rs)
                 content.append(ct)
@@ -437,7 +439,7 @@ def create_app(frontend, info: ServeInfo) -> FastAPI:
         if effort is not None:
             message["reasoning_content"] = "".join(reasoning)
         return {"id": cid, "object": "chat.completion", "created": created, "model": model,
-                "choices": [{"index": 0, "message": message, "finish_reason": finish}], "usage": usage_of(n_out)}
+                "choices": [{"index": 0, "message": message, "finish_reason": finish}], "usage": usage_of(n_out, n_in)}
 
     return app
 

@@ -83,6 +83,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--num-pages", dest="num_page_override", type=int, default=None)
     p.add_argument("--page-size", type=int, default=256)
     p.add_argument("--shell-mode", action="store_true")
+    p.add_argument("--device", choices=["cuda", "cpu"], default="cuda",
+                   help="cpu runs the PyTorch oracle of every operator: for trying the serving stack without a GPU")
     return p
 
 
@@ -118,7 +120,7 @@ def parse_args(argv: Optional[List[str]] = None, run_shell: bool = False) -> Ser
         max_extend_tokens=ns.max_extend_tokens, max_prefill_length=ns.max_extend_tokens,
         stats_log_interval=ns.stats_log_interval, disable_log_stats=ns.disable_log_stats,
         server_host=ns.server_host, server_port=ns.server_port, num_tokenizer=ns.num_tokenizer,
-        served_model_name=ns.served_model_name, shell_mode=shell, explicit_fields=explicit,
+        served_model_name=ns.served_model_name, shell_mode=shell, explicit_fields=explicit, device=ns.device,
         _unique_suffix=f".pid={os.getpid()}",
     )
     if shell:  # an interactive shell serves one request at a time and keeps the log quiet

@@ -32,7 +32,7 @@ def handle_batch(msgs: List[Any], tokenize_mgr, detokenize_mgr, counts) -> tuple
         for m, t in zip(detok, texts):
             n = counts.get(m.uid, 0) + (0 if m.finish_reason in ("length_rejected", "abort") else 1)
             counts[m.uid] = n
-            to_frontend.append(UserReply(m.uid, t, m.finished, m.finish_reason, n))
+            to_frontend.append(UserReply(m.uid, t, m.finished, m.finish_reason, n, m.prompt_tokens))
             if m.finished:
                 counts.pop(m.uid, None)
     if tok:
@@ -50,6 +50,12 @@ def tokenize_worker(*, tokenizer_path: str, addr: str, create: bool, backend_add
     from .detokenize import DetokenizeManager
     from .tokenize import TokenizeManager
 
+    import signal
+
+    def _terminate(signum, frame):  # the supervisor ends this worker with SIGTERM: leave through the finally below
+        raise KeyboardInterrupt
+
+    signal.signal(signal.SIGTERM, _terminate)
     tokenizer = load_tokenizer(tokenizer_path)
     tok_mgr, detok_mgr = TokenizeManager(tokenizer, tokenizer_path), DetokenizeManager(tokenizer)
     recv = ZmqPullQueue(addr, create=create)

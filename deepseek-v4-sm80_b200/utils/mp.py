@@ -22,7 +22,7 @@ class _Endpoint(Generic[T]):
     ASYNC = False
 
     def __init__(self, addr: str, create: bool, send_timeout_ms: Optional[int] = None):
-        self.addr = addr
+        self.addr, self.created = addr, create
         self.context = zmq.asyncio.Context() if self.ASYNC else zmq.Context()
         self.socket = self.context.socket(self.KIND)
         self.socket.setsockopt(zmq.LINGER, 1000)
@@ -38,6 +38,13 @@ class _Endpoint(Generic[T]):
             self.context.term()
         except Exception:  # pragma: no cover - best effort on shutdown
             pass
+        if self.created and self.addr.startswith("ipc://"):  # the binder owns the socket file
+            import os
+
+            try:
+                os.unlink(self.addr[len("ipc://"):])
+            except OSError:
+                pass
 
 
 class ZmqPushQueue(_Endpoint[T]):
