@@ -1,7 +1,8 @@
 """The whole serving stack as processes, on CPU: ``python -m minisgl --device cpu`` on a synthetic checkpoint (tiny
 model, word-level tokenizer written to the same folder) spawns the scheduler and the detokenizer under the
 supervisor; the test talks to it over HTTP like an OpenAI client -- model list, a completion, a streamed completion,
-a rejected parameter -- and stops it with SIGINT."""
+a rejected parameter -- and stops it with SIGINT.  With ``--tp-size 2`` two scheduler ranks run (gloo collectives,
+rank 0 republishing the requests to rank 1)."""
 import json
 import os
 import signal
@@ -52,8 +53,8 @@ def _http(url, body=None, timeout=120):
         return e.code, e.read().decode()
 
 
-@pytest.fixture(scope="module")
-def server(tmp_path_factory):
+@pytest.fixture(scope="module", params=[1, 2], ids=["tp1", "tp2"])
+def server(request, tmp_path_factory):
     cfg = ModelConfig.tiny()
     folder = str(tmp_path_factory.mktemp("model"))
     synth.write_checkpoint(cfg, folder, seed=11)
@@ -64,7 +65,7 @@ def server(tmp_path_factory):
     proc = subprocess.Popen(
         [sys.executable, "-m", "minisgl", "--model", folder, "--device", "cpu", "--port", str(port), "--page-size", "16",
          "--num-pages", "64", "--max-running-requests", "4", "--context-length", "512", "--served-model-name", "tiny",
-         "--disable-log-stats"], cwd=ROOT, env=env, stdout=log, stderr=subprocess.STDOUT)
+         "--disable-log-stats", "--tp-size", str(request.param)], cwd=ROOT, env=env, stdout=log, stderr=subprocess.STDOUT)
     base = f"http://127.0.0.1:{port}"
     deadline = time.time() + 180
     up = False
