@@ -142,3 +142,23 @@ def test_concurrent_requests_are_all_answered(server):
     for code, body in results.values():
         assert code == 200 and json.loads(body)["usage"]["completion_tokens"] <= 8
     assert proc.poll() is None
+
+
+def test_shell_mode_chats_over_stdin(tmp_path):
+    """``--shell-mode``: the same backend processes behind a line-oriented chat on stdin / stdout."""
+    cfg = ModelConfig.tiny()
+    folder = str(tmp_path / "model")
+    synth.write_checkpoint(cfg, folder, seed=11)
+    _write_tokenizer(folder, cfg.vocab_size)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), LOG_LEVEL="ERROR",
+               MINISGL_SHELL_MAX_TOKENS="5", MINISGL_SHELL_TEMPERATURE="0.0")
+    proc = subprocess.run(
+        [sys.executable, "-m", "minisgl", "--model", folder, "--device", "cpu", "--shell-mode", "--page-size", "16",
+         "--num-pages", "64", "--context-length", "512"],
+        cwd=ROOT, env=env, input="w10 w11 w12\n\n/reset\nw20 w21\n/exit\n", capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    out = proc.stdout
+    assert "minisgl shell" in out and out.count("> ") >= 4
+    answers = [l for l in out.split("> ") if l.strip() and "minisgl shell" not in l]
+    words = [w for a in answers for w in a.split()]
+    assert 2 <= len(words) <= 10 and all(w.startswith("w") or w.startswith("<") for w in words), out
