@@ -22,6 +22,8 @@ The last page id and the last table slot are reserved for the dummy request that
 """
 from __future__ import annotations
 
+from collections import OrderedDict
+
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -96,7 +98,10 @@ class DSV4KVPool:
         self.swa_pins = [0] * P          # users of a page's window storage (running requests + the radix tree)
         self._tree_pinned = set()
         self.swa_version = 0
-        self.counters = {"swa_taken": 0, "swa_released": 0, "pages_taken": 0, "pages_released": 0}
+        # pages nobody pins any more but that still own a window slot, oldest first: their rows stay readable (a later
+        # prefix hit can resume on them) until another page needs the slot
+        self._reclaimable: "OrderedDict[int, None]" = OrderedDict()
+        self.counters = {"swa_taken": 0, "swa_released": 0, "swa_reclaimed": 0, "pages_taken": 0, "pages_released": 0}
 
     # ------------------------------------------------------------------ pages
     @property
@@ -105,12 +110,13 @@ class DSV4KVPool:
 
     @property
     def num_free_swa(self) -> int:
-        return len(self.free_swa)
+        """Window slots a new page can get: unused ones plus those of unpinned pages (reclaimed on demand)."""
+        return len(self.free_swa) + len(self._reclaimable)
 
     def alloc_pages(self, n: int, with_swa: bool = True) -> List[int]:
-        if n > len(self.free_pages) or (with_swa and n > len(self.free_swa)):
+        if n > len(self.free_pages) or (with_swa and n > self.num_free_swa):
             raise RuntimeError(f"KV pool exhausted: want {n} pages, free {len(self.free_pages)} pages / "
-                               f"{len(self.free_swa)} SWA slots")
+                               f"{self.num_free_swa} SWA slots")
         pages = [self.free_pages.pop() for _ in range(n)]
         for p in pages:
             assert self.page_ref[p] == 0, f"page {p} handed out while referenced"
@@ -142,7 +148,20 @@ class DSV4KVPool:
             self.counters["pages_released"] += len(freed)
 
     # ------------------------------------------------------------------ SWA slots
+    def reclaim_swa(self, n: int) -> int:
+        """Takes the window slots of up to n unpinned pages back, least recently unpinned first."""
+        victims = []
+        while len(victims) < n and self._reclaimable:
+            victims.append(self._reclaimable.popitem(last=False)[0])
+        if victims:
+            self.counters["swa_reclaimed"] += len(victims)
+            self.release_swa(victims)
+        return len(victims)
+
     def attach_swa(self, pages) -> None:
+        need = sum(1 for p in pages if self._swa_map_host[p] < 0)
+        if need > len(self.free_swa):
+            self.reclaim_swa(need - len(self.free_swa))
         upd_p, upd_s = [], []
         for p in pages:
             if self._swa_map_host[p] >= 0:
@@ -162,6 +181,7 @@ class DSV4KVPool:
         upd = []
         for p in pages:
             s = self._swa_map_host[p]
+            self._reclaimable.pop(p, None)
             if s >= 0 and p != self.dummy_page:
                 self.free_swa.append(s)
                 self._swa_map_host[p] = -1
@@ -179,9 +199,11 @@ class DSV4KVPool:
                     continue
                 self._tree_pinned.add(p)
             self.swa_pins[p] += 1
+            self._reclaimable.pop(p, None)
 
     def unpin_swa(self, pages, owner: str = "req") -> None:
-        """Drops a user; window storage of a page nobody uses any more is recycled (the page itself stays)."""
+        """Drops a user.  A page nobody pins any more keeps its window rows for as long as no other page needs the
+        slot (it becomes reclaimable), so that a prefix hit ending on it can still resume there."""
         drop = []
         for p in pages:
             if owner == "tree":
@@ -192,8 +214,10 @@ class DSV4KVPool:
                 self.swa_pins[p] -= 1
                 if self.swa_pins[p] == 0:
                     drop.append(p)
-        if drop:
-            self.release_swa(drop)
+        for p in drop:
+            if self._swa_map_host[p] >= 0 and p != self.dummy_page:
+                self._reclaimable[p] = None
+                self._reclaimable.move_to_end(p)
 
     def runtime_swa_counters(self) -> dict:
         """Window-storage residency at this moment plus the lifetime counters: slots in use / free, pages whose
@@ -206,6 +230,7 @@ class DSV4KVPool:
             "swa_slots_total": self.sizes.num_swa_slots,
             "swa_slots_in_use": live,
             "swa_slots_free": len(self.free_swa),
+            "swa_slots_reclaimable": len(self._reclaimable),
             "pages_in_use": held,
             "pages_without_window": held - sum(1 for p in range(self.sizes.num_pages)
                                                if self.page_ref[p] > 0 and self._swa_map_host[p] >= 0),

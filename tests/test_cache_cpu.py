@@ -83,13 +83,18 @@ def test_identical_prompt_leaves_at_least_one_token_for_the_model():
     cm.adopt_prefix(a, cm.match_req(a.input_ids))
     _prefill_done(cm, a)
     cm.cache_req(a, finished=True)
-    # the match runs on input_ids[:-1]: 255 tokens -> 15 whole pages -> aligned boundary 128; a retired path keeps
-    # window rows only for its tail (the 128 tokens before its last aligned boundary, 256), so the hit backs off
+    # the match runs on input_ids[:-1]: 255 tokens -> 15 whole pages -> aligned boundary 128
     m = cm.match_req(torch.tensor(toks, dtype=torch.int32))
-    assert m.raw_length == 240 and m.length == 0 and cm.radix.metrics["swa_backoff_tokens"] == 240
+    assert m.raw_length == 240 and m.length == 128
     # one token more and the whole cached prompt is reused
     m = cm.match_req(torch.tensor(toks + [3], dtype=torch.int32))
     assert m.raw_length == 256 and m.length == 256 and len(m.pages) == 16
+    # under pressure the unpinned window rows go; a retired path keeps them only for its tail (the 128 tokens before
+    # its last aligned boundary, 256): the hit at 128 backs off, the one at 256 survives
+    assert pool.reclaim_swa(100) == 8
+    m = cm.match_req(torch.tensor(toks, dtype=torch.int32))
+    assert m.raw_length == 240 and m.length == 0 and cm.radix.metrics["swa_backoff_tokens"] >= 240
+    assert cm.match_req(torch.tensor(toks + [3], dtype=torch.int32)).length == 256
     assert cm.match_req(torch.tensor(toks[:1], dtype=torch.int32)).length == 0
     cm.radix.reset()
     pool.assert_no_leak()
@@ -105,12 +110,24 @@ def test_window_storage_is_released_behind_a_running_request():
         cm.allocate(r, n)
         r.device_len = n
         cm.release_swa_behind(r)
-    # positions [0, 300-128) are out of reach: 172 // 16 = 10 whole pages lost their window rows, the pages stay
+    # positions [0, 300-128) are out of reach: 172 // 16 = 10 whole pages are unpinned; their slots can be taken
     assert r.swa_pin_frontier == 10 and r.swa_evicted_seqlen == 160 and cm.counters["swa_unpinned"] == 10
-    assert [pool.has_swa(p) for p in r.pages] == [False] * 10 + [True] * 9
     c = pool.runtime_swa_counters()
-    assert c["pages_in_use"] == 19 and c["pages_without_window"] == 10 and c["swa_slots_in_use"] == 9
+    assert c["pages_in_use"] == 19 and c["swa_slots_reclaimable"] == 10 and c["pages_without_window"] == 0
+    assert pool.num_free_swa == 32 - 19 + 10
     assert cm.release_swa_behind(r) == 0                     # idempotent
+    other = _req(list(range(7000, 7100)), slot=1, uid=1, out=300)
+    cm.adopt_prefix(other, cm.match_req(other.input_ids))
+    cm.allocate(other, 16 * 13)                               # 13 pages: all that are free; slots: 13 unused
+    assert pool.counters["swa_reclaimed"] == 0
+    cm.cache_req(other, finished=True)
+    pool2_need = pool.alloc_pages(13, with_swa=False)         # pages without window rows do not touch the slots
+    pool.attach_swa(pool2_need)                               # 13 unused slots again, still nothing reclaimed
+    assert pool.counters["swa_reclaimed"] == 0 and pool.reclaim_swa(4) == 4
+    assert [pool.has_swa(p) for p in r.pages] == [False] * 4 + [True] * 15     # oldest unpinned first
+    c = pool.runtime_swa_counters()
+    assert c["pages_without_window"] == 4 and c["swa_slots_reclaimable"] == 6 and c["swa_reclaimed"] == 4
+    pool.unref_pages(pool2_need)
     cm.cache_req(r, finished=True)
     pool.assert_no_leak()
 

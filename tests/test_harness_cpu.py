@@ -31,3 +31,17 @@ def test_perf_matrix_catalogue():
     assert {"P1K_M128", "P4K_M256", "MIXED_ARRIVAL", "LONG_RESIDENT_64K", "PRESSURE_1M"} <= set(cat)
     assert len(cat["P1K_M128"].prompt_lens) == 128 and cat["P1K_M128"].prompt_lens[0] == 1024
     assert sum(cat["PRESSURE_1M"].prompt_lens) == 1 << 20
+
+
+def test_perf_matrix_runs_scenarios_on_the_cpu_model(capsys):
+    """Scaled-down scenarios through the instrumented offline engine (tiny model, PyTorch oracle): identical prompts
+    arriving over time hit the prefix cache; one long prompt beside short ones is chunked while the short ones finish."""
+    common = ["--tiny", "--device", "cpu", "--page-size", "16", "--num-pages", "640", "--max-running", "32"]
+    sp = perf_matrix.main(common + ["--scale", "0.125", "--scenarios", "SHARED_PREFIX"])[0]
+    assert sp["requests"] == 32 and sp["output_tokens"] == 32 * 8
+    # 256-token prompts: every arrival after the first prompt was cached resumes at the 128-token boundary
+    assert sp["prefix"]["hit_tokens"] >= 128 * 16 and sp["prefix"]["hit_rate"] > 0.25
+    lr = perf_matrix.main(common + ["--scale", "0.0625", "--scenarios", "LONG_RESIDENT_64K"])[0]
+    assert lr["requests"] == 32 and lr["prompt_tokens"] == 4096 + 31 * 32 and lr["output_tokens"] == 32 * 8
+    assert lr["steps"]["prefill"] >= 1 and lr["steps"]["decode"] >= 7
+    assert '"scenario": "SHARED_PREFIX"' in capsys.readouterr().out

@@ -160,8 +160,18 @@ def test_pool_refcounts_swa_lifetime_and_leak_check():
     pool.pin_swa(a)
     pool.ref_pages(a[:1])               # the radix tree takes a reference
     pool.unpin_swa(a[:2])               # the window moved past the first two pages
-    assert not pool.has_swa(a[0]) and not pool.has_swa(a[1]) and pool.has_swa(a[2]) and pool.num_free_swa == 7
+    # nobody pins them: their window rows stay readable until another page needs the slots
+    assert all(pool.has_swa(p) for p in a) and pool.num_free_swa == 7
+    assert pool.runtime_swa_counters()["swa_slots_reclaimable"] == 2
+    b = pool.alloc_pages(6)             # 5 unused slots + the least recently unpinned page's slot
+    assert not pool.has_swa(a[0]) and pool.has_swa(a[1]) and pool.counters["swa_reclaimed"] == 1
     assert int(pool.swa_map[a[0]]) == -1 and int(pool.swa_map[a[2]]) >= 0
+    with pytest.raises(RuntimeError):
+        pool.alloc_pages(2)             # one reclaimable slot left, pages would be there
+    pool.pin_swa(a[1:2])                # pinned again: not reclaimable any more
+    assert pool.num_free_swa == 0
+    pool.unpin_swa(a[1:2])
+    pool.unref_pages(b)
     pool.unref_pages(a)                 # request retires
     assert pool.num_free_pages == 15    # page a[0] survives through the tree's reference
     pool.unref_pages(a[:1])
@@ -183,7 +193,10 @@ def test_radix_match_insert_split_evict():
     assert canon == pages and rc.metrics["inserted_pages"] == 6
     m = rc.match(toks[:95])
     assert m.length == 80 and m.pages == pages[:5]
-    pool.unpin_swa(pages)                # the request moved on: only the tree's tail page keeps window storage
+    pool.unpin_swa(pages)                # the request moved on: only the tree still pins its tail page
+    assert all(pool.has_swa(p) for p in pages) and pool.runtime_swa_counters()["swa_slots_reclaimable"] == 5
+    assert rc.match(toks[:95]).length == 80  # unpinned window rows are still there: the hit resumes on them
+    assert pool.reclaim_swa(100) == 5        # ... until other pages need the slots
     assert [pool.has_swa(p) for p in pages] == [False] * 5 + [True]
     assert rc.match(toks[:100]).length == 96
     assert rc.match(toks[:95]).length == 0   # boundary 80 has no live window storage: the hit backs off
