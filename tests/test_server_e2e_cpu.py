@@ -35,6 +35,12 @@ def _write_tokenizer(folder: str, vocab_size: int) -> None:
     fast.chat_template = ("{% for m in messages %}{{ m['role'] }} {{ m['content'] }} {% endfor %}"
                           "{% if add_generation_prompt %}assistant{% endif %}")
     fast.save_pretrained(folder)
+    # the checkpoint's own chat formatter (thinking requests open the reasoning block)
+    os.makedirs(os.path.join(folder, "encoding"), exist_ok=True)
+    with open(os.path.join(folder, "encoding", "encoding_dsv4.py"), "w") as f:
+        f.write("def encode_messages(messages, thinking_mode, reasoning_effort):\n"
+                "    text = ' '.join(m['content'] for m in messages)\n"
+                "    return text + (' <think>' if thinking_mode == 'thinking' else '')\n")
 
 
 def _free_port() -> int:
@@ -65,7 +71,8 @@ def server(request, tmp_path_factory):
     proc = subprocess.Popen(
         [sys.executable, "-m", "minisgl", "--model", folder, "--device", "cpu", "--port", str(port), "--page-size", "16",
          "--num-pages", "64", "--max-running-requests", "4", "--context-length", "512", "--served-model-name", "tiny",
-         "--disable-log-stats", "--tp-size", str(request.param)], cwd=ROOT, env=env, stdout=log, stderr=subprocess.STDOUT)
+         "--disable-log-stats", "--tp-size", str(request.param)]
+        + (["--enable-reasoning-sampler-contract"] if request.param == 1 else []), cwd=ROOT, env=env, stdout=log, stderr=subprocess.STDOUT)
     base = f"http://127.0.0.1:{port}"
     deadline = time.time() + 180
     up = False
@@ -101,7 +108,7 @@ def test_models_completion_stream_and_errors(server):
     out = json.loads(body)
     choice = out["choices"][0]
     assert choice["finish_reason"] in ("length", "stop") and isinstance(choice["message"]["content"], str)
-    assert out["usage"]["completion_tokens"] <= 6 and out["usage"]["prompt_tokens"] >= 6
+    assert out["usage"]["completion_tokens"] <= 6 and out["usage"]["prompt_tokens"] == 4
     first = choice["message"]["content"]
     # greedy decoding of the same prompt is repeatable through the whole stack (and hits the prefix cache path)
     assert json.loads(_http(base + "/v1/chat/completions", req)[1])["choices"][0]["message"]["content"] == first
@@ -119,6 +126,25 @@ def test_models_completion_stream_and_errors(server):
     assert code == 400 and json.loads(body)["error"]["param"] == "n"
     code, body = _http(base + "/v1/chat/completions", dict(req, model="other"))
     assert code == 404
+    assert proc.poll() is None
+
+
+def test_thinking_request_returns_reasoning_content(server):
+    """reasoning_effort: the prompt goes through the checkpoint's formatter, the request starts in the THINKING state
+    (with the sampler contract on: <think> never sampled, EOS masked while thinking) and what it generates before a
+    closing delimiter is returned as reasoning_content."""
+    base, proc, _ = server
+    req = {"model": "tiny", "messages": [{"role": "user", "content": "w30 w31 w32"}], "max_tokens": 6,
+           "temperature": 0.8, "reasoning_effort": "high"}
+    code, body = _http(base + "/v1/chat/completions", req)
+    assert code == 200, body
+    msg = json.loads(body)["choices"][0]["message"]
+    assert "reasoning_content" in msg and isinstance(msg["content"], str)
+    words = (msg["reasoning_content"] + " " + msg["content"]).split()
+    assert 1 <= len(words) <= 6 and "<think>" not in words and "</s>" not in msg["reasoning_content"].split()
+    assert json.loads(body)["usage"]["prompt_tokens"] == 4          # three words + the opening delimiter
+    plain = json.loads(_http(base + "/v1/chat/completions", dict(req, reasoning_effort="none"))[1])
+    assert "reasoning_content" not in plain["choices"][0]["message"]
     assert proc.poll() is None
 
 
