@@ -10,8 +10,15 @@ import os
 
 def load_tokenizer(model_path: str):
     from transformers import AutoTokenizer
+    from transformers.utils import logging as hf_logging
 
-    tok = AutoTokenizer.from_pretrained(model_path, trust_remote_code=False)
+    # transformers does not know the deepseek_v4 model type and says so at length while it only loads the tokenizer
+    level = hf_logging.get_verbosity()
+    hf_logging.set_verbosity_error()
+    try:
+        tok = AutoTokenizer.from_pretrained(model_path, trust_remote_code=False)
+    finally:
+        hf_logging.set_verbosity(level)
     tmpl = os.path.join(model_path, "chat_template.json")
     if getattr(tok, "chat_template", None) is None and os.path.exists(tmpl):
         data = json.load(open(tmpl))
