@@ -148,6 +148,27 @@ def test_thinking_request_returns_reasoning_content(server):
     assert proc.poll() is None
 
 
+def test_online_benchmark_client_measures_the_running_server(server, capsys):
+    """The public online benchmark (async streaming client, per-token timestamps) against the live server."""
+    import asyncio
+
+    from minisgl.benchmark import client as C
+    from minisgl.benchmark.online import bench_simple
+
+    base, proc, _ = server
+    items = [C.TraceItem(0.05 * i, " ".join(f"w{40 + i + k}" for k in range(10)), 5) for i in range(5)]
+    s = asyncio.run(C.benchmark_trace(base, "tiny", items))
+    assert s["requests"] == 5 and s["failed"] == 0
+    assert s["ttft"]["p50"] > 0 and s["tpot"]["p50"] > 0 and s["e2e"]["max"] >= s["ttft"]["max"]
+    assert s["output_tok_s"] > 0 and s["req_s"] > 0
+    bad = asyncio.run(C.benchmark_trace(base, "no-such-model", items[:2]))
+    assert bad["failed"] == 2
+    bench_simple.main(["--url", base, "--model", "tiny", "--batch", "3", "--input-words", "8", "--output-len", "4"])
+    out = json.loads(capsys.readouterr().out)
+    assert out["requests"] == 3 and out["failed"] == 0
+    assert proc.poll() is None
+
+
 def test_concurrent_requests_are_all_answered(server):
     import threading
 
