@@ -16,6 +16,10 @@ def main(argv=None) -> dict:
     ap.add_argument("--input-len", type=int, default=1024)
     ap.add_argument("--output-len", type=int, default=1024)
     ap.add_argument("--recipe", default="default_m128")
+    ap.add_argument("--tiny", action="store_true", help="tiny architecture (CPU-sized); implies --dummy")
+    ap.add_argument("--device", default="cuda")
+    ap.add_argument("--page-size", type=int, default=256)
+    ap.add_argument("--num-pages", type=int, default=0, help="override the KV page count (CPU runs need it)")
     a = ap.parse_args(argv)
     import torch
 
@@ -24,10 +28,12 @@ def main(argv=None) -> dict:
     from minisgl.models.config import ModelConfig
 
     kw = {}
-    if a.dummy or not a.model:
-        cfg = ModelConfig.flash()
+    if a.tiny or a.dummy or not a.model:
+        cfg = ModelConfig.tiny() if a.tiny else ModelConfig.flash()
         kw = dict(model_config=cfg.with_layers(a.layers) if a.layers else cfg, use_dummy_weight=True)
-    llm = LLM(a.model, recipe=a.recipe, max_running_req=a.batch, **kw)
+    if a.num_pages:
+        kw["num_page_override"] = a.num_pages
+    llm = LLM(a.model, recipe=a.recipe, max_running_req=a.batch, device=a.device, page_size=a.page_size, **kw)
     vocab = llm.engine.model_config.vocab_size
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, vocab, (a.input_len,), generator=g, dtype=torch.int32) for _ in range(a.batch)]

@@ -45,3 +45,15 @@ def test_perf_matrix_runs_scenarios_on_the_cpu_model(capsys):
     assert lr["requests"] == 32 and lr["prompt_tokens"] == 4096 + 31 * 32 and lr["output_tokens"] == 32 * 8
     assert lr["steps"]["prefill"] >= 1 and lr["steps"]["decode"] >= 7
     assert '"scenario": "SHARED_PREFIX"' in capsys.readouterr().out
+
+
+def test_offline_benchmarks_run_on_the_cpu_model(tmp_path):
+    """The public offline benchmarks (fixed wave; mixed-length prompts with temperature sampling) through
+    ``LLM.generate`` on the tiny model."""
+    from minisgl.benchmark.offline import bench, bench_wildchat
+
+    cpu = ["--tiny", "--device", "cpu", "--page-size", "16", "--num-pages", "256"]
+    res = bench.main(cpu + ["-M", "6", "--input-len", "48", "--output-len", "5"])
+    assert res["requests"] == 6 and res["output_tok_s"] > 0 and res["prefix"]["queries"] == 6
+    wc = bench_wildchat.main(cpu + ["-n", "8", "--max-tokens", "4", "--max-prompt", "200"])
+    assert wc["requests"] == 8 and set(wc["finish_reasons"]) <= {"length", "stop"}
