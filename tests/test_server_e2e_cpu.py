@@ -209,3 +209,22 @@ def test_shell_mode_chats_over_stdin(tmp_path):
     answers = [l for l in out.split("> ") if l.strip() and "minisgl shell" not in l]
     words = [w for a in answers for w in a.split()]
     assert 2 <= len(words) <= 10 and all(w.startswith("w") or w.startswith("<") for w in words), out
+
+
+def test_offline_example_on_two_cpu_ranks(tmp_path):
+    """examples/offline_dsv4.py: a chat prompt through ``LLM.generate`` on two tensor-parallel ranks (gloo), with the
+    checkpoint's tokenizer and formatter, printing the decoded text from rank 0."""
+    cfg = ModelConfig.tiny()
+    folder = str(tmp_path / "model")
+    synth.write_checkpoint(cfg, folder, seed=11)
+    _write_tokenizer(folder, cfg.vocab_size)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), LOG_LEVEL="ERROR")
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "examples", "offline_dsv4.py"), folder, "--tp", "2", "--device", "cpu",
+         "--page-size", "16", "--num-pages", "64", "--prompt", "w50 w51 w52", "--max-tokens", "6"],
+        cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    lines = [l for l in proc.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1                                   # only rank 0 prints
+    words = lines[0].split()
+    assert 1 <= len(words) <= 6 and all(w.startswith(("w", "<")) for w in words)
