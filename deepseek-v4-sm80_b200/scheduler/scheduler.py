@@ -104,6 +104,11 @@ class Scheduler:
             raise TypeError(f"unexpected backend message {type(msg).__name__}")
 
     def _abort(self, uid: int) -> None:
+        if any(p.uid == uid for p in self.prefill.pending):
+            # not admitted yet: nothing to release, but whoever collects results must learn that it ended
+            self.prefill.abort(uid)
+            self._on_reply(DetokenizeMsg(uid, 0, True, "abort"))
+            return
         req = self.prefill.abort(uid)
         if req is None:
             req = next((r for r in self.decode.running if r.uid == uid), None)

@@ -88,3 +88,60 @@ def test_over_long_prompt_is_rejected_and_output_budget_is_clipped():
     assert outs[0].finish_reason == "length_rejected" and outs[0].token_ids == []
     assert outs[1].finish_reason == "length" and len(outs[1].token_ids) == 5   # clipped to the sequence limit
     _idle(llm)
+
+
+def test_random_load_under_page_pressure_is_token_exact_and_leak_free():
+    """Twenty requests of random lengths (some sharing a prefix), more than the 4 request slots and more tokens than
+    the 40-page pool holds at once, released a few polls apart, two of them aborted in flight: every surviving
+    request must produce exactly the tokens it produces alone, and afterwards nothing may be left allocated."""
+    import random
+
+    from helpers import MiniRunner
+
+    rng = random.Random(7)
+    g = torch.Generator().manual_seed(7)
+    shared = torch.randint(0, 1024, (144,), generator=g).tolist()
+    prompts, budgets = [], []
+    for i in range(20):
+        n = rng.choice([5, 17, 40, 90, 130, 200])
+        body = torch.randint(0, 1024, (n,), generator=g).tolist()
+        prompts.append((shared + body) if i % 4 == 0 else body)
+        budgets.append(rng.randint(1, 10))
+    cfg = ModelConfig.tiny()
+
+    def alone(prompt, n_out):
+        r = MiniRunner(cfg, page_size=16, num_pages=40, seed=0)
+        out, logits = [], r.step([(0, prompt)])
+        for _ in range(n_out):
+            out.append(int(logits.argmax(-1)[0]))
+            logits = r.step([(0, [out[-1]])])
+        return out
+
+    llm = _llm(num_page_override=40, max_extend_tokens=128)
+    polls, aborted = {"n": 0}, {3: 9, 11: 30}                  # uid -> poll at which the abort arrives
+    real = llm.receive_msg
+
+    def receive(blocking):
+        polls["n"] += 1
+        msgs = list(real(blocking))
+        msgs += [AbortBackendMsg(u) for u, at in aborted.items() if at == polls["n"]]
+        return msgs
+
+    llm.receive_msg = receive
+    sps = [SamplingParams(max_tokens=b, ignore_eos=True) for b in budgets]
+    outs = llm.generate(prompts, sps, arrival_gap_steps=2)
+    reasons = [o.finish_reason for o in outs]
+    assert set(reasons) <= {"length", "abort"} and reasons.count("abort") <= 2
+    checked = 0
+    for i, o in enumerate(outs):
+        if o.finish_reason == "length":
+            assert len(o.token_ids) == budgets[i]
+            if i % 3 == 0 or i % 4 == 0:                      # a sample of them, and every prefix sharer
+                assert o.token_ids == alone(prompts[i], budgets[i]), i
+                checked += 1
+    assert checked >= 8
+    assert llm.cache.radix.metrics["hit_tokens"] >= 128       # later sharers resumed on the cached prefix
+    assert llm.cache.counters["evictions"] >= 1               # the pool was too small to keep everything cached
+    _idle(llm)
+    llm.cache.radix.reset()
+    llm.engine.pool.assert_no_leak()
