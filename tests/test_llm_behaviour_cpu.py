@@ -145,3 +145,46 @@ def test_random_load_under_page_pressure_is_token_exact_and_leak_free():
     _idle(llm)
     llm.cache.radix.reset()
     llm.engine.pool.assert_no_leak()
+
+
+def test_reasoning_sampler_path_is_batch_invariant():
+    """With the reasoning sampler the scheduler commits the previous sample before it schedules (the mask depends on
+    it).  Requests in THINKING and CHAT state, batched and staggered, must give the tokens they give one at a time,
+    and never a masked structural token."""
+    from minisgl.reasoning import ReasoningTokenIds
+
+    ids = ReasoningTokenIds(bos=0, eos=1, think_start=2, think_end=3)
+
+    def make():
+        llm = _llm()
+        llm.engine.enable_reasoning_sampler(ids)
+        llm.think_end_token_id = ids.think_end
+        llm.eos_token_id = ids.eos
+        return llm
+
+    prompts = _prompts(6, 30, seed=8)
+    sp = SamplingParams(max_tokens=10)
+    efforts = ["high", None, "high", None, "max", None]
+
+    def run(llm, idx, **kw):
+        # one generate() call per reasoning effort (the call takes one effort for all its prompts)
+        out = {}
+        for eff in ("high", "max", None):
+            sel = [i for i in idx if efforts[i] == eff]
+            if sel:
+                for i, o in zip(sel, llm.generate([prompts[i] for i in sel], sp, reasoning_effort=eff, **kw)):
+                    out[i] = o
+        return out
+
+    together = run(make(), range(6), arrival_gap_steps=2)
+    single = make()
+    for i in range(6):
+        alone = run(single, [i])[i]
+        assert together[i].token_ids == alone.token_ids, i
+        assert together[i].finish_reason == alone.finish_reason
+    for i, o in together.items():
+        assert ids.think_start not in o.token_ids
+        if efforts[i] is None:
+            assert ids.think_end not in o.token_ids          # closing delimiter only exists inside a reasoning block
+        elif ids.think_end not in o.token_ids:
+            assert ids.eos not in o.token_ids                # still thinking: the request cannot end with EOS
