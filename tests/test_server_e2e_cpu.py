@@ -68,6 +68,8 @@ def server(request, tmp_path_factory):
     port = _free_port()
     log = open(os.path.join(folder, "server.log"), "w")
     env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), LOG_LEVEL="WARNING")
+    if request.param == 2:  # the two-rank server also runs the non-overlapped scheduler loop
+        env["MINISGL_DISABLE_OVERLAP_SCHEDULING"] = "1"
     proc = subprocess.Popen(
         [sys.executable, "-m", "minisgl", "--model", folder, "--device", "cpu", "--port", str(port), "--page-size", "16",
          "--num-pages", "64", "--max-running-requests", "4", "--context-length", "512", "--served-model-name", "tiny",
