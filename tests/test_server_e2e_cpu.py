@@ -193,6 +193,29 @@ def test_concurrent_requests_are_all_answered(server):
     assert proc.poll() is None
 
 
+def test_zz_a_dead_backend_process_turns_the_api_unavailable(server):
+    """Failure detection, host side: one backend child is killed (exact pid, SIGKILL); the health watcher notices
+    within seconds, new requests get 503 ``backend_unavailable`` instead of hanging, and the API process survives to
+    say so.  Runs last on each server instance."""
+    import psutil
+
+    base, proc, _ = server
+    kids = [c for c in psutil.Process(proc.pid).children(recursive=True)
+            if "resource_tracker" not in " ".join(c.cmdline())]
+    assert kids, "the server has backend children"
+    victim = max(kids, key=lambda c: c.memory_info().rss)      # a scheduler rank (it holds the weights)
+    victim.kill()
+    req = {"model": "tiny", "messages": [{"role": "user", "content": "w10 w11"}], "max_tokens": 3, "temperature": 0}
+    deadline, code, body = time.time() + 30, None, ""
+    while time.time() < deadline:
+        code, body = _http(base + "/v1/chat/completions", req, timeout=20)
+        if code == 503:
+            break
+        time.sleep(0.5)
+    assert code == 503 and json.loads(body)["error"]["code"] == "backend_unavailable", (code, body[:300])
+    assert proc.poll() is None and _http(base + "/v1/models")[0] == 200
+
+
 def test_shell_mode_chats_over_stdin(tmp_path):
     """``--shell-mode``: the same backend processes behind a line-oriented chat on stdin / stdout."""
     cfg = ModelConfig.tiny()
