@@ -94,6 +94,16 @@ class LLM(Scheduler):
             r.finish_reason = msg.finish_reason
             self._open -= 1
 
+    def abort(self, uid: int) -> None:
+        """Ends request ``uid`` wherever it is: still queued here, waiting for admission, prefilling or decoding.  Its
+        RequestOutput keeps the tokens produced so far and gets finish_reason ``abort``."""
+        for m in self._queue:
+            if m.uid == uid:
+                self._queue.remove(m)
+                self._on_reply(DetokenizeMsg(uid, 0, True, "abort"))
+                return
+        self._abort(uid)
+
     def _encode(self, prompt, reasoning_effort) -> torch.Tensor:
         if isinstance(prompt, torch.Tensor):
             return prompt.to(torch.int32).cpu()

@@ -188,3 +188,31 @@ def test_reasoning_sampler_path_is_batch_invariant():
             assert ids.think_end not in o.token_ids          # closing delimiter only exists inside a reasoning block
         elif ids.think_end not in o.token_ids:
             assert ids.eos not in o.token_ids                # still thinking: the request cannot end with EOS
+
+
+def test_public_abort_reaches_a_request_in_every_stage():
+    """LLM.abort(uid) on a request that is still queued in the offline feeder, on one waiting for a request slot and
+    on one that is decoding: all three end with ``abort``, the rest finish, nothing leaks."""
+    llm = _llm(max_running_req=2)
+    prompts = _prompts(5, 40, seed=9)
+    polls = {"n": 0}
+    real = llm.receive_msg
+
+    def receive(blocking):
+        polls["n"] += 1
+        if polls["n"] == 2:
+            llm.abort(4)          # not released yet (one request every 3 polls)
+        msgs = real(blocking)
+        if polls["n"] == 8:
+            llm.abort(2)          # released, both request slots taken: waiting for admission
+            llm.abort(0)          # decoding
+        return msgs
+
+    llm.receive_msg = receive
+    outs = llm.generate(prompts, SamplingParams(max_tokens=30, ignore_eos=True), arrival_gap_steps=3)
+    assert [o.finish_reason for o in outs] == ["abort", "length", "abort", "length", "abort"]
+    assert outs[4].token_ids == [] and outs[2].token_ids == [] and 0 < len(outs[0].token_ids) < 30
+    assert len(outs[1].token_ids) == len(outs[3].token_ids) == 30
+    _idle(llm)
+    llm.cache.radix.reset()
+    llm.engine.pool.assert_no_leak()
