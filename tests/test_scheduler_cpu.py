@@ -252,3 +252,49 @@ def test_reasoning_states_and_stats():
     t[0] = 10.0
     line = st.maybe_report(1, 2, 0.5)
     assert "prompt 100.0 tok/s" in line and "generation 5.0 tok/s" in line and "KV 50.0%" in line
+
+
+def test_graph_runner_selects_bucket_and_context_class_without_a_gpu():
+    """The replay decision of the graph runner, built with object.__new__ (no capture): which decode batches have a
+    captured graph, which bucket they are padded to, which context class they replay, and the status counters."""
+    from types import SimpleNamespace
+
+    from minisgl.engine.graph import GraphRunner
+
+    class FakeGraph:
+        def __init__(self):
+            self.n = 0
+
+        def replay(self):
+            self.n += 1
+
+    r = object.__new__(GraphRunner)
+    r.buckets, r.classes = [1, 2, 4, 8], [2048, 32768, 1 << 20]
+    r.capture_status = {"captured": 12, "replays": 0, "eager_decode": 0, "unsupported_bs": 0, "context_overflow": 0}
+    r.graphs = {(b, c): FakeGraph() for b in r.buckets for c in range(3)}
+    r.logits = {k: f"logits{k}" for k in r.graphs}
+    r.launches = {k: 100 + k[0] for k in r.graphs}
+    copies = []
+    r.buffer = SimpleNamespace(copy_from=lambda batch, bs: copies.append(bs))
+
+    def batch(size, ctx, phase="decode", padded=None):
+        n = padded if padded is not None else size
+        return SimpleNamespace(is_decode=phase == "decode", size=size, max_context=ctx,
+                               positions=torch.zeros(n, dtype=torch.int32))
+
+    assert [r.padded_size(n) for n in (1, 3, 5, 8, 9)] == [1, 4, 8, 8, 9]
+    assert [r._class_of(c) for c in (1, 2048, 2049, 32768, 1 << 20, (1 << 20) + 1)] == [0, 0, 1, 1, 2, None]
+    assert not r.can_replay(batch(4, 100, phase="prefill"))
+    assert not r.can_replay(batch(9, 100)) and r.capture_status["unsupported_bs"] == 1
+    assert not r.can_replay(batch(4, (1 << 20) + 1)) and r.capture_status["context_overflow"] == 1
+    b = batch(3, 5000, padded=4)
+    assert r.can_replay(b)
+    from minisgl.ops import native
+
+    n0 = native.launch_count()
+    assert r.replay(b) == "logits(4, 1)" and r.graphs[(4, 1)].n == 1 and copies == [4]
+    assert native.launch_count() - n0 == 104 and r.capture_status["replays"] == 1
+    with pytest.raises(AssertionError, match="padded"):
+        r.replay(batch(3, 5000))                      # not padded to its bucket
+    with pytest.raises(RuntimeError, match="no captured graph"):
+        r.replay(batch(9, 100, padded=9))
