@@ -78,6 +78,9 @@ def generate_prompt(tokenizer, n_tokens: int, seed: int = 0) -> str:
         if len(got) == n_tokens:
             return text
         ids = (got + [rng.randrange(1000, max(vocab - 1000, 1001)) for _ in range(n_tokens)])[:n_tokens]
+    # no fixed point within the rounds (a tokenizer whose merges keep shifting): never return more than asked for
+    while ids and len(tokenizer.encode(tokenizer.decode(ids), add_special_tokens=False)) > n_tokens:
+        ids = ids[:-1]
     return tokenizer.decode(ids)
 
 

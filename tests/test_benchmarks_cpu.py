@@ -139,3 +139,13 @@ def test_root_bench_and_example_compile():
     for f in ("bench.py", "__graft_entry__.py", os.path.join("examples", "offline_dsv4.py")):
         py_compile.compile(os.path.join(root, f), doraise=True)
     assert not math.isnan(C.percentile([1.0], 99))
+
+
+def test_generate_prompt_never_exceeds_the_count_with_an_unstable_tokenizer():
+    class Growing(_WordTok):                               # multiples of 7 double on every round trip: no fixed point
+        def decode(self, ids):
+            return " ".join(f"t{i} t{i}" if i % 7 == 0 else f"t{i}" for i in ids)
+
+    tok = Growing()
+    for n in (17, 64):
+        assert len(tok.encode(C.generate_prompt(tok, n, seed=n))) <= n
