@@ -113,7 +113,9 @@ class PrefillManager:
         m = self.cache.match_req(p.input_ids)
         total_pages = div_ceil(p.input_len + p.output_len, self.ps)
         need = total_pages - m.length // self.ps
-        if need + self._claimed_pages() > self.cache.available_pages:
+        # the matched pages may be counted as evictable right now; once adopted they are locked, so they cannot pay
+        # for anybody's future pages
+        if need + self._claimed_pages() > self.cache.available_pages - len(m.pages):
             return None
         slot = self.table.allocate()
         req = Req(input_ids=p.input_ids, table_idx=slot, cached_len=m.length, output_len=p.output_len, uid=p.uid,

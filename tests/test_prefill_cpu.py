@@ -13,11 +13,11 @@ from minisgl.scheduler.table import TableManager
 PS = 16
 
 
-def _setup(pages=64, slots=4):
+def _setup(pages=64, slots=4, prefix=False):
     cfg = ModelConfig.tiny()
     pool = DSV4KVPool(cfg, PoolSizes(pages, pages, slots, PS), "cpu")
     table = torch.zeros(slots + 1, 2048, dtype=torch.int32)
-    cache = CacheManager(pool, table, PS, 128, enable_prefix_cache=False)
+    cache = CacheManager(pool, table, PS, 128, enable_prefix_cache=prefix)
     tm, dm = TableManager(slots), DecodeManager(PS)
     return PrefillManager(cache, tm, dm, PS, 2048), cache, tm, dm, pool
 
@@ -116,3 +116,36 @@ def test_abort_of_pending_and_resident_requests():
     tm.free(r2.table_idx)
     assert not pm.runnable and tm.available_size == 4
     pool.assert_no_leak()
+
+
+def test_adopted_prefix_pages_do_not_pay_for_other_requests():
+    """A cached prefix counts as evictable capacity until a request adopts (and thereby locks) it.  Admission must
+    not promise those pages twice: with 8 free pages, 8 cached ones and a request that already claims 8, a second
+    request that would lock the cached 8 and need 8 more has to wait."""
+    pm, cache, tm, dm, pool = _setup(pages=16, slots=4, prefix=True)
+    pm.add_one_req(_pending(1, 129, out=1))
+    b = pm.schedule_next_batch(512)
+    _ran(b)
+    x = b.reqs[0]
+    cache.cache_req(x, finished=False)
+    cache.cache_req(x, finished=True)
+    tm.free(x.table_idx)
+    assert pool.num_free_pages == 8 and cache.available_pages == 16
+    pm.add_one_req(_pending(2, 100, out=28, base=5000))                     # 8 pages, no shared prefix
+    sharer = PendingReq(3, torch.cat([torch.arange(0, 128, dtype=torch.int32), torch.tensor([7, 8], dtype=torch.int32)]),
+                        SamplingParams(max_tokens=126))                     # 16 pages, 8 of them the cached prefix
+    pm.add_one_req(sharer)
+    b = pm.schedule_next_batch(512)
+    assert [r.uid for r in b.reqs] == [2] and [p.uid for p in pm.pending] == [3]
+    _ran(b)
+    c = b.reqs[0]
+    dm.add(c)
+    assert pm.schedule_next_batch(512) is None                              # still claimed by the running request
+    cache.allocate(c, c.max_device_len)                                     # it really gets its 8 pages
+    dm.remove(c)
+    cache.cache_req(c, finished=True)
+    tm.free(c.table_idx)
+    b = pm.schedule_next_batch(512)
+    assert [r.uid for r in b.reqs] == [3] and b.reqs[0].cached_len == 128
+    cache.allocate(b.reqs[0], b.reqs[0].max_device_len)                     # and so does the sharer: 8 adopted + 8 new
+    assert len(b.reqs[0].pages) == 16
