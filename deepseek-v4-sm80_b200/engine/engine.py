@@ -42,12 +42,16 @@ class ForwardOutput:
 
 
 def swa_slot_plan(max_running_req: int, prefill_budget: int, page_size: int, window: int) -> int:
-    """Sliding-window slots to reserve.  A page holds a slot from allocation until it lies wholly behind its request's
-    window, so the live set is: the pages of one full prefill forward, a window tail plus the page being written per
-    running request, one more per request for the step that overlap scheduling keeps in flight, and one spare.
-    (The reference reserves at least 8 per request, python/minisgl/engine/engine.py:569-584; its pages keep their
-    window storage longer because release there is tied to the radix tree.)"""
-    return div_ceil(prefill_budget, page_size) + max_running_req * (div_ceil(window, page_size) + 2) + 1
+    """Sliding-window slots to reserve: the pages of one full prefill forward, one spare, and per running request its
+    hard share (:func:`minisgl.scheduler.cache.slots_per_request`: window pages, the page being written, the step
+    overlap scheduling keeps in flight) plus ``ceil(window / ps)`` for the tail of the cached path it locks in the
+    prefix tree.  Admission divides the pool by the hard share (``CacheManager.request_capacity``); the tree's part is
+    an allowance that keeps prefix-hit resume points alive and is given up first under pressure.
+    (The reference reserves at least 8 per request, python/minisgl/engine/engine.py:569-584.)"""
+    from ..scheduler.cache import slots_per_request
+
+    per_req = slots_per_request(window, page_size) + div_ceil(window, page_size)
+    return div_ceil(prefill_budget, page_size) + 1 + max_running_req * per_req
 
 
 class Engine:

@@ -96,7 +96,7 @@ class DSV4KVPool:
         self.free_swa: List[int] = list(range(sizes.num_swa_slots - 1, -1, -1))
         self.page_ref = [0] * P
         self.swa_pins = [0] * P          # users of a page's window storage (running requests + the radix tree)
-        self._tree_pinned = set()
+        self._tree_pinned: "OrderedDict[int, None]" = OrderedDict()   # pages the prefix tree pins, oldest pin first
         self.swa_version = 0
         # pages nobody pins any more but that still own a window slot, oldest first: their rows stay readable (a later
         # prefix hit can resume on them) until another page needs the slot
@@ -142,7 +142,7 @@ class DSV4KVPool:
         if freed:
             for p in freed:
                 self.swa_pins[p] = 0
-                self._tree_pinned.discard(p)
+                self._tree_pinned.pop(p, None)
             self.release_swa(freed)
             self.free_pages.extend(freed)
             self.counters["pages_released"] += len(freed)
@@ -197,7 +197,7 @@ class DSV4KVPool:
             if owner == "tree":
                 if p in self._tree_pinned:
                     continue
-                self._tree_pinned.add(p)
+                self._tree_pinned[p] = None
             self.swa_pins[p] += 1
             self._reclaimable.pop(p, None)
 
@@ -209,7 +209,7 @@ class DSV4KVPool:
             if owner == "tree":
                 if p not in self._tree_pinned:
                     continue
-                self._tree_pinned.discard(p)
+                del self._tree_pinned[p]
             if self.swa_pins[p] > 0:
                 self.swa_pins[p] -= 1
                 if self.swa_pins[p] == 0:
@@ -218,6 +218,21 @@ class DSV4KVPool:
             if self._swa_map_host[p] >= 0 and p != self.dummy_page:
                 self._reclaimable[p] = None
                 self._reclaimable.move_to_end(p)
+
+    def drop_tree_pins(self, n_slots: int) -> int:
+        """Makes the prefix tree give up pins, oldest first, until n_slots more window slots are obtainable (or no
+        tree pin is left).  Only pages that nobody else pins yield a slot.  The pages stay cached; a later prefix hit
+        that would resume on them backs off to an earlier boundary.  Returns the number of pins dropped."""
+        got = dropped = 0
+        for p in list(self._tree_pinned):
+            if got >= n_slots:
+                break
+            before = self.num_free_swa
+            self.unpin_swa([p], "tree")
+            dropped += 1
+            got += self.num_free_swa - before
+        self.counters["tree_pins_dropped"] = self.counters.get("tree_pins_dropped", 0) + dropped
+        return dropped
 
     def runtime_swa_counters(self) -> dict:
         """Window-storage residency at this moment plus the lifetime counters: slots in use / free, pages whose

@@ -76,6 +76,12 @@ class RadixPrefixCache:
         self.align = int(np.lcm(align, page_size))
         self.root = RadixNode(np.zeros(0, np.int32), [], None)
         self.root.lock_count = 1
+        # kept incrementally, so that admission checks and eviction never walk the tree: pages held by unlocked
+        # nodes, and a lazily cleaned heap of (last_access, uid, node) candidates (an entry is stale when its node
+        # left the tree, got children, got locked or was touched since)
+        self._evictable = 0
+        self._lru: list = []
+        self._nodes = 0
         self.metrics = {"queries": 0, "hit_tokens": 0, "query_tokens": 0, "evicted_pages": 0, "inserted_pages": 0,
                         "swa_backoff_tokens": 0}
 
@@ -89,6 +95,7 @@ class RadixPrefixCache:
         upper = RadixNode(node.tokens[:n_tokens], node.pages[:npg], node.parent)
         upper.lock_count = node.lock_count
         upper.last_access = node.last_access
+        self._nodes += 1
         node.parent.children[self._key(node.tokens)] = upper
         node.tokens, node.pages, node.parent = node.tokens[n_tokens:], node.pages[npg:], upper
         upper.children[self._key(node.tokens)] = node
@@ -105,6 +112,7 @@ class RadixPrefixCache:
             if n == 0:
                 break
             child.last_access = now
+            self._offer(child)
             if n < len(child.tokens):
                 if not split:
                     return child, done + n  # partial use of the child's run
@@ -146,8 +154,22 @@ class RadixPrefixCache:
             node, _ = self._walk(tokens[:length], split=True) if length else (self.root, 0)
         return MatchResult(length, pages[: length // self.ps], node if length else None, raw)
 
+    def _offer(self, node: RadixNode) -> None:
+        """Registers ``node`` as an eviction candidate if it is one right now."""
+        if node is not self.root and node.lock_count == 0 and node.is_leaf and node.parent is not None:
+            heapq.heappush(self._lru, (node.last_access, node.uid, node))
+            if len(self._lru) > 64 + 8 * self._nodes:   # drop stale entries
+                live = {}
+                for t, u, nd in self._lru:
+                    if nd.parent is not None and nd.lock_count == 0 and nd.is_leaf and t == nd.last_access:
+                        live[u] = (t, u, nd)
+                self._lru = list(live.values())
+                heapq.heapify(self._lru)
+
     def lock(self, node: Optional[RadixNode]) -> None:
         while node is not None and node is not self.root:
+            if node.lock_count == 0:
+                self._evictable -= len(node.pages)
             node.lock_count += 1
             node = node.parent
 
@@ -155,6 +177,9 @@ class RadixPrefixCache:
         while node is not None and node is not self.root:
             assert node.lock_count > 0, "unlock of an unlocked radix node"
             node.lock_count -= 1
+            if node.lock_count == 0:
+                self._evictable += len(node.pages)
+                self._offer(node)
             node = node.parent
 
     def insert(self, tokens, pages: List[int]) -> Tuple[List[int], RadixNode]:
@@ -169,6 +194,9 @@ class RadixPrefixCache:
             new_pages = pages[done // self.ps:]
             child = RadixNode(tokens[done:].copy(), list(new_pages), node)
             node.children[self._key(child.tokens)] = child
+            self._nodes += 1
+            self._evictable += len(new_pages)
+            self._offer(child)
             self.pool.ref_pages(new_pages)
             self.metrics["inserted_pages"] += len(new_pages)
             # the previous tail of this path is no longer a tail
@@ -184,7 +212,8 @@ class RadixPrefixCache:
         pages = self._path_pages(node, n)
         boundary = n // self.align * self.align
         first = max(boundary - self.window, 0) // self.ps
-        return pages[first:]
+        # a hit never resumes past the last aligned boundary, so the pages after it need no window storage
+        return pages[first: boundary // self.ps]
 
     def _retire_tail(self, node: RadixNode) -> None:
         if node is self.root or not node.pages:
@@ -198,6 +227,11 @@ class RadixPrefixCache:
         self.pool.pin_swa(self._tail_pages(node), owner="tree")
 
     def evictable_pages(self) -> int:
+        """Pages held by unlocked nodes (kept incrementally)."""
+        return self._evictable
+
+    def _count_evictable(self) -> int:
+        """The same figure from a full walk (tests compare the two)."""
         total, stack = 0, [self.root]
         while stack:
             nd = stack.pop()
@@ -208,26 +242,21 @@ class RadixPrefixCache:
 
     def evict(self, n_pages: int) -> int:
         """Frees at least n_pages pages from unlocked leaves in LRU order (if available)."""
-        heap = []
-        stack = [self.root]
-        while stack:
-            nd = stack.pop()
-            stack.extend(nd.children.values())
-            if nd is not self.root and nd.is_leaf and nd.lock_count == 0:
-                heapq.heappush(heap, (nd.last_access, nd.uid, nd))
         freed = 0
-        while heap and freed < n_pages:
-            _, _, nd = heapq.heappop(heap)
-            if nd.lock_count or not nd.is_leaf or nd.parent is None:
-                continue
+        while self._lru and freed < n_pages:
+            t, _, nd = heapq.heappop(self._lru)
+            if nd.parent is None or nd.lock_count or not nd.is_leaf or t != nd.last_access:
+                continue  # stale entry
             parent = nd.parent
             del parent.children[self._key(nd.tokens)]
             self.pool.unpin_swa(nd.pages, owner="tree")
             self.pool.unref_pages(nd.pages)
             freed += len(nd.pages)
+            self._evictable -= len(nd.pages)
+            self._nodes -= 1
             nd.parent = None
-            if parent is not self.root and parent.is_leaf and parent.lock_count == 0:
-                heapq.heappush(heap, (parent.last_access, parent.uid, parent))
+            if parent is not self.root:
+                self._offer(parent)
         self.metrics["evicted_pages"] += freed
         return freed
 

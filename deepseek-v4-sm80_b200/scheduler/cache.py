@@ -22,12 +22,26 @@ from ..kvcache.radix_cache import MatchResult, RadixPrefixCache
 from ..utils.misc import div_ceil
 
 
+class KVExhausted(RuntimeError):
+    """No page (or no sliding-window slot) could be freed for an allocation.  The scheduler never lets it escape its
+    loop: a prefill chunk that cannot get storage is deferred, a decoding request that cannot is ended."""
+
+
+def slots_per_request(window: int, page_size: int) -> int:
+    """Window slots one admitted request can need at the same time outside a prefill chunk: the pages its window
+    reaches (``ceil(window / ps)`` plus the page being written) and one more for the step that overlap scheduling
+    keeps in flight.  Slots pinned by the prefix tree are not part of it: under pressure the tree gives them up
+    (``DSV4KVPool.drop_tree_pins``), which only costs later prefix hits their resume point."""
+    return div_ceil(window, page_size) + 2
+
+
 class CacheManager:
     def __init__(self, pool, page_table: torch.Tensor, page_size: int, window: int, enable_prefix_cache: bool = True):
         self.pool, self.page_table, self.ps, self.window = pool, page_table, page_size, window
         self.radix: Optional[RadixPrefixCache] = RadixPrefixCache(pool, page_size, window) if enable_prefix_cache else None
         self.device = page_table.device
-        self.counters = {"alloc_pages": 0, "evictions": 0, "swa_unpinned": 0}
+        self.counters = {"alloc_pages": 0, "evictions": 0, "swa_unpinned": 0, "alloc_failures": 0, "dedup_pages": 0,
+                         "tree_pins_dropped": 0}
 
     # ------------------------------------------------------------------ capacity
     @property
@@ -38,14 +52,29 @@ class CacheManager:
     def pages_still_needed(self, req: Req) -> int:
         return max(div_ceil(req.max_device_len, self.ps) - len(req.pages), 0)
 
-    def _ensure(self, n: int) -> None:
-        short = max(n - self.pool.num_free_pages, n - self.pool.num_free_swa, 0)
-        if short > 0 and self.radix is not None:
+    def request_capacity(self, prefill_budget: int) -> int:
+        """How many requests the window-slot pool can carry at once: what is left of the pool after one prefill
+        forward's pages (at most half of it) and a spare, divided by each request's share; never less than one (a
+        lone request always fits: its chunk shrinks to what the pool can hold)."""
+        total = self.pool.sizes.num_swa_slots
+        chunk = min(div_ceil(prefill_budget, self.ps) + 1, total // 2)
+        return max((total - chunk) // slots_per_request(self.window, self.ps), 1)
+
+    def _ensure(self, n: int) -> bool:
+        """Frees storage until n pages AND n window slots are available: evicts unlocked cached paths oldest first (a
+        path's pages and the slots its tail pins come back together), then, for slots only, makes the prefix tree give
+        up tail pins of paths that running requests keep locked.  Returns whether it succeeded."""
+        pool = self.pool
+        evicted = False
+        while (pool.num_free_pages < n or pool.num_free_swa < n) and self.radix is not None:
+            if self.radix.evict(max(n - pool.num_free_pages, 1)) == 0:
+                break
+            evicted = True
+        if evicted:
             self.counters["evictions"] += 1
-            self.radix.evict(short)
-        if n > self.pool.num_free_pages or n > self.pool.num_free_swa:
-            raise RuntimeError(f"out of KV pages: need {n}, free pages {self.pool.num_free_pages}, "
-                               f"free SWA slots {self.pool.num_free_swa}")
+        if pool.num_free_swa < n:
+            self.counters["tree_pins_dropped"] += pool.drop_tree_pins(n - pool.num_free_swa)
+        return pool.num_free_pages >= n and pool.num_free_swa >= n
 
     # ------------------------------------------------------------------ prefix reuse
     def match_req(self, input_ids: torch.Tensor) -> MatchResult:
@@ -69,12 +98,26 @@ class CacheManager:
         self._write_rows(req.table_idx, 0, m.pages)
 
     # ------------------------------------------------------------------ allocation
+    def try_allocate(self, req: Req, upto_len: int) -> bool:
+        """``allocate`` that reports exhaustion instead of raising (nothing is allocated then)."""
+        try:
+            self.allocate(req, upto_len)
+            return True
+        except KVExhausted:
+            self.counters["alloc_failures"] += 1
+            return False
+
     def allocate(self, req: Req, upto_len: int) -> None:
-        """Makes req.pages cover positions [0, upto_len)."""
+        """Makes req.pages cover positions [0, upto_len); raises :class:`KVExhausted` (and allocates nothing) when
+        neither free storage nor eviction can supply the pages and their window slots."""
         need = div_ceil(upto_len, self.ps) - len(req.pages)
         if need <= 0:
             return
-        self._ensure(need)
+        if (len(req.pages) + need) * self.ps > self.page_table.shape[1]:
+            raise RuntimeError("request exceeds the page table width (max sequence length)")
+        if not self._ensure(need):
+            raise KVExhausted(f"out of KV pages: need {need}, free pages {self.pool.num_free_pages}, "
+                              f"free SWA slots {self.pool.num_free_swa}")
         new = self.pool.alloc_pages(need)
         self.pool.pin_swa(new, "req")
         self.counters["alloc_pages"] += need
@@ -95,8 +138,11 @@ class CacheManager:
 
     # ------------------------------------------------------------------ window storage
     def release_swa_behind(self, req: Req) -> int:
-        """Unpins pages that lie wholly behind the request's sliding window; returns how many."""
-        target = max(req.device_len - self.window, 0) // self.ps
+        """Unpins pages that lie wholly behind the window of every position the request still has to run; returns
+        how many.  The next forward of the request starts at ``cached_len`` (the next prefill chunk, or the next decode
+        token), whose window reaches back to ``cached_len - window + 1``.  ``device_len`` must not be used here:
+        while a prompt is prefilled in chunks it already is the full prompt length."""
+        target = max(req.cached_len - self.window, 0) // self.ps
         target = min(target, len(req.pages))
         frontier = getattr(req, "swa_pin_frontier", 0)
         if target <= frontier:
@@ -115,10 +161,12 @@ class CacheManager:
             valid = min(req.cached_len, len(req.input_ids))
             n = valid // self.ps * self.ps
             if n > 0:
-                _, node = self.radix.insert(req.input_ids[:n].numpy(), req.pages[: n // self.ps])
+                canon, node = self.radix.insert(req.input_ids[:n].numpy(), req.pages[: n // self.ps])
                 self.radix.lock(node)
                 self.radix.unlock(req.cache_handle)
                 req.cache_handle = node
+                if not finished:
+                    self._adopt_canonical(req, canon)
         if finished:
             frontier = getattr(req, "swa_pin_frontier", 0)
             self.pool.unpin_swa(req.pages[frontier:], "req")
@@ -128,6 +176,41 @@ class CacheManager:
             self.pool.unref_pages(req.pages)
             req.pages = []
             req.swa_pin_frontier = 0
+
+    def _adopt_canonical(self, req: Req, canon: List[int]) -> None:
+        """Where the tree already held a page for the same tokens (another request cached the same prefix first), the
+        request switches to the tree's page and gives its duplicate back, as the reference does when it repoints a
+        request to canonical prefix pages (python/minisgl/scheduler/cache.py:140-229).  A page that the request's
+        window still reaches is only switched if the tree's page still owns window rows; the pin moves with it."""
+        frontier = getattr(req, "swa_pin_frontier", 0)
+        for i, c in enumerate(canon):
+            own = req.pages[i]
+            if c == own:
+                continue
+            pinned = i >= frontier
+            if pinned and not self.pool.has_swa(c):
+                continue
+            self.pool.ref_pages([c])
+            if pinned:
+                self.pool.pin_swa([c], "req")
+                self.pool.unpin_swa([own], "req")
+            req.pages[i] = c
+            self.pool.unref_pages([own])
+            self._write_rows(req.table_idx, i, [c])
+            self.counters["dedup_pages"] += 1
+
+    def assert_window_resident(self, req: Req, first_pos: int, last_pos: int) -> None:
+        """Invariant of every forward: each page that the sliding windows of positions [first_pos, last_pos] reach
+        still owns window storage and is pinned by somebody.  Checked by the scheduler before each launch when
+        ``check_window`` is set (tests, MINISGL_DEBUG_BOUNDS=1)."""
+        lo = max(first_pos - self.window + 1, 0) // self.ps
+        hi = last_pos // self.ps
+        for i in range(lo, hi + 1):
+            p = req.pages[i]
+            if not self.pool.has_swa(p) or self.pool.swa_pins[p] <= 0:
+                raise AssertionError(
+                    f"request {req.uid}: page index {i} (page {p}) is inside the window of positions "
+                    f"[{first_pos}, {last_pos}] but has_swa={self.pool.has_swa(p)} pins={self.pool.swa_pins[p]}")
 
     def prefix_metrics_snapshot(self) -> dict:
         m = self.radix.snapshot() if self.radix else {}

@@ -80,9 +80,12 @@ class PrefillManager:
     def __init__(self, cache: CacheManager, table: TableManager, decode, page_size: int, max_seq_len: int):
         self.cache, self.table, self.decode = cache, table, decode
         self.ps, self.max_seq_len = page_size, max_seq_len
+        self.slot_budget = 0                   # prefill token budget the window-slot plan assumes (set per schedule)
         self.pending: Deque[PendingReq] = deque()
         self.resident: List[Req] = []          # admitted, prefill not finished (FIFO)
         self.generation = 0
+        self.deferred_chunks = 0
+        self.shrunk_chunks = 0
 
     def add_one_req(self, p: PendingReq) -> None:
         self.pending.append(p)
@@ -117,6 +120,10 @@ class PrefillManager:
         # for anybody's future pages
         if need + self._claimed_pages() > self.cache.available_pages - len(m.pages):
             return None
+        # window slots are a second, much smaller resource: every admitted request keeps a bounded number pinned
+        active = len(self.resident) + len(self.decode.running)
+        if active + 1 > self.cache.request_capacity(self.slot_budget):
+            return None
         slot = self.table.allocate()
         req = Req(input_ids=p.input_ids, table_idx=slot, cached_len=m.length, output_len=p.output_len, uid=p.uid,
                   sampling_params=p.sampling_params, reasoning_effort=p.reasoning_effort)
@@ -128,6 +135,7 @@ class PrefillManager:
 
     # ------------------------------------------------------------------ scheduling
     def schedule_next_batch(self, budget: int) -> Optional[Batch]:
+        self.slot_budget = budget
         # admit while the budget can still give every resident prompt a share
         while self.pending and len(self.resident) * min(self.ps, budget) < budget:
             req = self._try_admit(self.pending[0])
@@ -146,7 +154,15 @@ class PrefillManager:
         for r, g in zip(chosen, grants):
             if g <= 0:
                 continue
-            self.cache.allocate(r, r.cached_len + g)
+            q = min(self.ps, budget)
+            while g > 0 and not self.cache.try_allocate(r, r.cached_len + g):
+                # no storage for the whole share right now (other requests still pin it): take a smaller piece,
+                # whole quanta only, or wait for a later forward
+                g = (g // 2) // q * q
+                self.shrunk_chunks += 1
+            if g <= 0:
+                self.deferred_chunks += 1
+                continue
             r.prefill_granted += g
             reqs.append(r)
             chunks.append(g)

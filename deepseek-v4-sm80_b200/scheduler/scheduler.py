@@ -74,6 +74,9 @@ class Scheduler:
         self.step_log: List[Dict[str, Any]] = []
         self.record_steps = False
         self.bytes_h2d = self.bytes_d2h = 0
+        from ..env import ENV
+
+        self.check_window = bool(ENV.DEBUG_BOUNDS)   # assert window residency before every forward
         self.heartbeat = None
         if getattr(config, "heartbeat_name", ""):
             from ..utils.heartbeat import HeartbeatBoard
@@ -132,20 +135,42 @@ class Scheduler:
         if decision.phase == "prefill":
             batch = self.prefill.schedule_next_batch(decision.prefill_budget)
             if batch is None and dec:
-                batch = self.decode.schedule_next_batch()
+                batch = self._schedule_decode()
         elif decision.phase == "decode":
-            batch = self.decode.schedule_next_batch()
+            batch = self._schedule_decode()
         self.policy.record_scheduled(batch.phase if batch else None, prefill_runnable=pre, decode_runnable=dec)
         if batch is None:
             return None
         return batch, self._prepare_batch(batch)
 
+    def _schedule_decode(self) -> Optional[Batch]:
+        """The decode batch of the running requests that have storage for their next position.  Admission reserves
+        every page a request can need, so a failure here means the window-slot pool ran dry; the request that cannot
+        continue is ended (``abort``), the others carry on, and the scheduling loop survives."""
+        batch = self.decode.schedule_next_batch()
+        if batch is None:
+            return None
+        keep = []
+        for r in batch.reqs:
+            if self.cache.try_allocate(r, r.device_len):
+                keep.append(r)
+            else:
+                logger.warning_rank0("request %d ended: no KV storage for its next token (%s)", r.uid,
+                                     self.cache.prefix_metrics_snapshot())
+                self.decode.remove(r)
+                self._commit_terminal(r, "abort")
+        if not keep:
+            return None
+        batch.reqs = keep
+        return batch
+
     def _prepare_batch(self, batch: Batch) -> BatchSamplingArgs:
         e, ps = self.engine, self.ps
         reqs = batch.reqs
+        if self.check_window:
+            for r, n in zip(reqs, batch.chunk_lens if batch.is_prefill else [1] * len(reqs)):
+                self.cache.assert_window_resident(r, r.cached_len, r.cached_len + n - 1)
         if batch.is_decode:
-            for r in reqs:
-                self.cache.allocate(r, r.device_len)
             bs = len(reqs)
             padded = e.graph_runner.padded_size(bs) if e.graph_runner is not None else bs
             host = torch.empty(3, padded, dtype=torch.int32, pin_memory=e.is_cuda)

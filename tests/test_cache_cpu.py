@@ -108,7 +108,7 @@ def test_window_storage_is_released_behind_a_running_request():
     assert cm.release_swa_behind(r) == 0                     # nothing lies behind a 128-token window yet
     for n in (200, 300):
         cm.allocate(r, n)
-        r.device_len = n
+        r.cached_len, r.device_len = n, n + 1
         cm.release_swa_behind(r)
     # positions [0, 300-128) are out of reach: 172 // 16 = 10 whole pages are unpinned; their slots can be taken
     assert r.swa_pin_frontier == 10 and r.swa_evicted_seqlen == 160 and cm.counters["swa_unpinned"] == 10
@@ -139,7 +139,7 @@ def test_fewer_window_slots_than_pages_bound_what_a_request_can_hold():
     cm.allocate(r, 160)                                      # 10 pages, 10 window slots
     with pytest.raises(RuntimeError, match="out of KV pages"):
         cm.allocate(r, 176)
-    r.device_len = 160
+    r.cached_len, r.device_len = 160, 161
     assert cm.release_swa_behind(r) == 2                     # the window moved on: two slots come back
     cm.allocate(r, 176)
     assert len(r.pages) == 11
@@ -180,3 +180,77 @@ def test_row_wider_than_the_page_table_is_refused():
     cm.allocate(r, 64)
     with pytest.raises(RuntimeError, match="page table width"):
         cm.allocate(r, 65)
+
+
+def test_evictable_count_and_lru_are_kept_incrementally():
+    """The evictable-page figure admission reads is maintained on lock / unlock / insert / evict; it must equal a
+    full walk of the tree at every point, and eviction must take unlocked leaves oldest first without one."""
+    cm, pool, _ = _mgr(pages=64)
+    reqs = []
+    for i in range(4):
+        r = _req(list(range(1000 * (i + 1), 1000 * (i + 1) + 129)), slot=i % 4, uid=i)
+        cm.adopt_prefix(r, cm.match_req(r.input_ids))
+        _prefill_done(cm, r)
+        assert cm.radix.evictable_pages() == cm.radix._count_evictable()
+        reqs.append(r)
+    assert cm.radix.evictable_pages() == 0                      # all four paths are locked by their requests
+    for r in reqs[:3]:
+        cm.cache_req(r, finished=True)
+        assert cm.radix.evictable_pages() == cm.radix._count_evictable()
+    assert cm.radix.evictable_pages() == 24
+    cm.match_req(torch.tensor(list(range(1000, 1129)) + [1], dtype=torch.int32))   # touch the oldest path
+    assert cm.radix.evict(8) == 8
+    assert cm.match_req(torch.tensor(list(range(2000, 2130)), dtype=torch.int32)).length == 0   # 2nd oldest went
+    assert cm.match_req(torch.tensor(list(range(1000, 1130)), dtype=torch.int32)).length == 128  # touched one stayed
+    assert cm.radix.evictable_pages() == cm.radix._count_evictable() == 16
+    cm.cache_req(reqs[3], finished=True)
+    cm.radix.reset()
+    assert cm.radix.evictable_pages() == 0
+    pool.assert_no_leak()
+
+
+def test_duplicate_prefix_pages_are_swapped_for_the_cached_ones():
+    """Two requests prefill the same prompt at the same time; the second to finish finds its pages already in the
+    tree, switches to them (page-table row included) and returns its duplicates."""
+    cm, pool, table = _mgr(pages=64)
+    toks = list(range(300, 300 + 161))
+    a, b = _req(toks, slot=0, uid=0), _req(toks, slot=1, uid=1)
+    for r in (a, b):
+        cm.adopt_prefix(r, cm.match_req(r.input_ids))
+        cm.allocate(r, r.device_len)
+    assert not set(a.pages) & set(b.pages)
+    free_before = pool.num_free_pages
+    for r in (a, b):
+        r.complete_one()
+        cm.cache_req(r, finished=False)
+    assert b.pages[:10] == a.pages[:10] and b.pages[10] != a.pages[10]      # 160 shared tokens = 10 whole pages
+    assert cm.counters["dedup_pages"] == 10 and pool.num_free_pages == free_before + 10
+    want = torch.cat([torch.arange(p * PS, (p + 1) * PS) for p in b.pages]).to(torch.int32)
+    assert torch.equal(table[1, :len(want)], want)
+    assert all(pool.swa_pins[p] >= 2 for p in a.pages[2:10])                # both requests pin the shared window pages
+    for r in (a, b):
+        cm.cache_req(r, finished=True)
+    cm.radix.reset()
+    pool.assert_no_leak()
+
+
+def test_tree_gives_up_tail_pins_when_slots_run_short():
+    cm, pool, _ = _mgr(pages=64, swa=20)
+    a = _req(list(range(100, 100 + 161)), slot=0, uid=0, out=200)
+    cm.adopt_prefix(a, cm.match_req(a.input_ids))
+    _prefill_done(cm, a)                                       # 11 pages; the tree pins the tail of the locked path
+    assert pool.runtime_swa_counters()["pages_pinned_by_tree"] == 8
+    for n in (250, 331):                                       # decode on: the window leaves the prompt behind
+        cm.allocate(a, n)
+        a.cached_len, a.device_len = n - 1, n
+        cm.release_swa_behind(a)
+    held = pool.runtime_swa_counters()
+    assert held["pages_pinned"] >= 16                           # 9 by the request, the rest by the tree
+    b = _req(list(range(5000, 5000 + 150)), slot=1, uid=1)
+    cm.adopt_prefix(b, cm.match_req(b.input_ids))
+    assert cm.try_allocate(b, 150)                              # 10 slots: only there once the tree lets go
+    assert cm.counters["tree_pins_dropped"] > 0 and cm.counters["alloc_failures"] == 0
+    for r in (a, b):
+        cm.cache_req(r, finished=True)
+    cm.radix.reset()
+    pool.assert_no_leak()

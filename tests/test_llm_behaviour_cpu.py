@@ -13,7 +13,9 @@ def _llm(**kw):
     base = dict(model_config=ModelConfig.tiny(), device="cpu", page_size=16, max_running_req=4, num_page_override=64,
                 seed=0, use_dummy_weight=True, disable_log_stats=True)
     base.update(kw)
-    return LLM(**base)
+    llm = LLM(**base)
+    llm.check_window = True      # every forward asserts that the pages its sliding windows reach are resident and pinned
+    return llm
 
 
 def _prompts(n, length, seed=0):
@@ -90,10 +92,63 @@ def test_over_long_prompt_is_rejected_and_output_budget_is_clipped():
     _idle(llm)
 
 
-def test_random_load_under_page_pressure_is_token_exact_and_leak_free():
+def test_chunked_prefill_keeps_its_window_pages_while_others_decode():
+    """Three short requests decode while a 900-token prompt is prefilled in 64-token chunks over 16-token pages with
+    few window slots.  Before every forward (``check_window``) each page inside the window of the rows about to run
+    must own window storage and be pinned: while a prompt is still prefilling the release frontier follows the chunk
+    progress, not the prompt length.  The long prompt must also produce what it produces alone."""
+    from helpers import MiniRunner
+
+    cfg = ModelConfig.tiny()
+    short = _prompts(3, 20, seed=11)
+    long_prompt = _prompts(1, 900, seed=12)[0]
+    llm = _llm(num_page_override=96, max_extend_tokens=64)
+    sps = [SamplingParams(max_tokens=40, ignore_eos=True)] * 3 + [SamplingParams(max_tokens=4, ignore_eos=True)]
+    outs = llm.generate(short + [long_prompt], sps, arrival_gap_steps=1)
+    assert [len(o.token_ids) for o in outs] == [40, 40, 40, 4]
+    assert llm.stats.prefill_steps >= 900 // 64                    # the long prompt really ran in many chunks
+    assert llm.cache.counters["swa_unpinned"] >= 40                # and its window storage was released behind it
+    assert llm.cache.counters["alloc_failures"] == 0
+    r = MiniRunner(cfg, page_size=16, num_pages=96, seed=0, max_len=1024)
+    logits, o = None, 0
+    while o < 900:                                                 # same 64-token chunks, alone
+        logits = r.step([(0, long_prompt[o:o + 64])])
+        o += 64
+    top = logits[0].topk(2)
+    if float(top.values[0] - top.values[1]) > 0.05:                # skip the comparison on a near tie
+        assert outs[3].token_ids[0] == int(top.indices[0])
+    _idle(llm)
+    llm.cache.radix.reset()
+    llm.engine.pool.assert_no_leak()
+
+
+def test_window_slot_shortage_defers_and_shrinks_chunks_instead_of_raising():
+    """A pool with far fewer window slots than pages: admission limits the number of concurrent requests to what the
+    slots carry, chunks that cannot get slots shrink or wait, the prefix tree gives up its tail pins, and every
+    request still finishes with its full output.  Nothing raises out of the scheduling loop."""
+    llm = _llm(num_page_override=96, max_extend_tokens=128)
+    pool = llm.engine.pool
+    # keep 26 window slots: with 10 per request (8 window pages + 2) at most one or two requests fit beside a chunk
+    taken = [pool.free_swa.pop() for _ in range(len(pool.free_swa) - 26)]
+    pool.sizes.num_swa_slots = 26
+    assert llm.cache.request_capacity(128) == 1
+    prompts = _prompts(5, 200, seed=13)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=20, ignore_eos=True))
+    assert [o.finish_reason for o in outs] == ["length"] * 5 and all(len(o.token_ids) == 20 for o in outs)
+    _idle(llm)
+    llm.cache.radix.reset()
+    pool.free_swa.extend(taken)
+    pool.sizes.num_swa_slots = 26 + len(taken)
+    pool.assert_no_leak()
+
+
+def test_random_load_under_page_pressure_is_consistent_and_leak_free():
     """Twenty requests of random lengths (some sharing a prefix), more than the 4 request slots and more tokens than
-    the 40-page pool holds at once, released a few polls apart, two of them aborted in flight: every surviving
-    request must produce the tokens it produces alone, and afterwards nothing may be left allocated."""
+    the 40-page pool holds at once, released a few polls apart, two of them aborted in flight.  Structural checks:
+    window residency before every forward, exact output lengths, prefix hits and evictions happened, nothing stays
+    allocated.  Token check against a lone run of the same prompt: the wave runs other chunk and batch shapes and the
+    oracle's bf16 GEMMs are not bit-invariant to them, so a sequence may leave the lone run's -- but only at a step
+    where the lone run itself is nearly tied between the two tokens."""
     import random
 
     from helpers import MiniRunner
@@ -109,13 +164,14 @@ def test_random_load_under_page_pressure_is_token_exact_and_leak_free():
         budgets.append(rng.randint(1, 10))
     cfg = ModelConfig.tiny()
 
-    def alone(prompt, n_out):
+    def alone(prompt, forced):
+        """Logits of the lone run at every output step, teacher-forced with the wave's tokens."""
         r = MiniRunner(cfg, page_size=16, num_pages=40, seed=0)
-        out, logits = [], r.step([(0, prompt)])
-        for _ in range(n_out):
-            out.append(int(logits.argmax(-1)[0]))
-            logits = r.step([(0, [out[-1]])])
-        return out
+        rows, logits = [], r.step([(0, prompt)])
+        for t in forced:
+            rows.append(logits[0].float())
+            logits = r.step([(0, [t])])
+        return rows
 
     llm = _llm(num_page_override=40, max_extend_tokens=128)
     polls, aborted = {"n": 0}, {3: 9, 11: 30}                  # uid -> poll at which the abort arrives
@@ -132,19 +188,22 @@ def test_random_load_under_page_pressure_is_token_exact_and_leak_free():
     outs = llm.generate(prompts, sps, arrival_gap_steps=2)
     reasons = [o.finish_reason for o in outs]
     assert set(reasons) <= {"length", "abort"} and reasons.count("abort") <= 2
-    checked = same = same_first = 0
+    checked = exact = 0
     for i, o in enumerate(outs):
         if o.finish_reason == "length":
             assert len(o.token_ids) == budgets[i]
             if i % 3 == 0 or i % 4 == 0:                      # a sample of them, and every prefix sharer
-                ref = alone(prompts[i], budgets[i])
                 checked += 1
-                same += o.token_ids == ref
-                same_first += o.token_ids[0] == ref[0]
-    # The wave runs prefill chunks and decode batches of other shapes than the lone run.  The oracle's bf16 GEMMs are
-    # not bit-invariant to the batch shape, and with random weights router and argmax decisions are often near ties
-    # that such rounding tips (then the logits jump): a rare divergence is not an error, a frequent one would be.
-    assert checked >= 8 and same >= 0.75 * checked and same_first >= 0.9 * checked, (same, same_first, checked)
+                same = True
+                for step, (tok, row) in enumerate(zip(o.token_ids, alone(prompts[i], o.token_ids))):
+                    best = int(row.argmax())
+                    if tok != best:
+                        # teacher forcing keeps the lone run on the wave's sequence, so every step is comparable
+                        gap = float(row[best] - row[tok])
+                        assert gap < 0.25, f"request {i} step {step}: wave token {tok} is {gap:.3f} below {best}"
+                        same = False
+                exact += same
+    assert checked >= 8 and exact >= checked - 1, (exact, checked)   # measured: all exact; one near tie allowed
     assert llm.cache.radix.metrics["hit_tokens"] >= 128       # later sharers resumed on the cached prefix
     assert llm.cache.counters["evictions"] >= 1               # the pool was too small to keep everything cached
     _idle(llm)
