@@ -39,6 +39,7 @@ class ForwardOutput:
     next_tokens_cpu: torch.Tensor
     copy_done_event: Any
     forward_ms: Optional[float] = None
+    status: Any = None           # ops.native.StatusProbe whose snapshot was queued behind this forward (CUDA only)
 
 
 def swa_slot_plan(max_running_req: int, prefill_budget: int, page_size: int, window: int) -> int:
@@ -108,6 +109,15 @@ class Engine:
         self.sampler: Sampler = Sampler(self.device, cfg.vocab_size, config.seed)
         self.reasoning_token_ids = None
         self.graph_runner = None
+        self.status_probes = None
+        self._probe_i = 0
+        if self.is_cuda:
+            from ..env import ENV
+            from ..ops import native
+
+            native.set_peer_wait_ms(ENV.PEER_WAIT_MS.value)
+            if not ENV.DISABLE_STATUS_CHECK:
+                self.status_probes = [native.StatusProbe(), native.StatusProbe()]
         self._events: List[Any] = []
         self.timings: List[Dict[str, Any]] = []
         self.record_timings = False
@@ -251,9 +261,15 @@ class Engine:
         # the sampled token is the next step's input: keep it on the device, per request slot
         sample_slots = batch.slots[: batch.size] if batch.is_decode else batch.slots[batch.last_idx]
         self.last_token[sample_slots.long()] = next_tokens
+        probe = None
         if self.is_cuda:
             cpu = torch.empty(next_tokens.shape, dtype=next_tokens.dtype, pin_memory=True)
             cpu.copy_(next_tokens, non_blocking=True)
+            if self.status_probes is not None:
+                # two probes alternate: overlap scheduling keeps one forward in flight while the previous is read
+                probe = self.status_probes[self._probe_i]
+                self._probe_i ^= 1
+                probe.snapshot()
             ev = torch.cuda.Event()
             ev.record()
         else:
@@ -262,7 +278,7 @@ class Engine:
             t_ev[1].record()
             self.timings.append({"phase": batch.phase, "tokens": int(batch.num_token_non_padded),
                                  "reqs": batch.size, "events": t_ev})
-        return ForwardOutput(next_tokens, cpu, ev)
+        return ForwardOutput(next_tokens, cpu, ev, status=probe)
 
     # ------------------------------------------------------------------ misc
     def sync_all_ranks(self) -> None:

@@ -7,6 +7,7 @@
 #include <string.h>
 
 __device__ int g_dsv4_status[8];
+__device__ unsigned long long g_dsv4_peer_wait_ns = 2000000000ull;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -53,6 +54,23 @@ DSV4_API int dsv4_read_status(int* host_out, int clear) {
     e = cudaMemcpyToSymbol(g_dsv4_status, z, sizeof(z));
   }
   return (int)e;
+}
+
+// Queues a copy of the status word into `pinned_host` (8 ints of page-locked host memory) on `st`, without
+// synchronising: the caller reads it after whatever it already waits for on that stream.  A serving loop uses this
+// once per step, so that a wait that ran out on the device becomes a host error within one step.
+DSV4_API int dsv4_status_snapshot(int* pinned_host, cudaStream_t st) {
+  void* sym = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&sym, g_dsv4_status);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemcpyAsync(pinned_host, sym, sizeof(int) * 8, cudaMemcpyDeviceToHost, st);
+}
+
+// Sets the limit of waits on other GPUs (current device).  Values below 1 ms are refused.
+DSV4_API int dsv4_set_peer_wait_ms(long long ms) {
+  if (ms < 1) return 1;
+  const unsigned long long ns = (unsigned long long)ms * 1000000ull;
+  return (int)cudaMemcpyToSymbol(g_dsv4_peer_wait_ns, &ns, sizeof(ns));
 }
 
 bool dsv4_pdl_enabled() {

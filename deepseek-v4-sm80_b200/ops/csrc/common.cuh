@@ -37,7 +37,9 @@ __device__ __forceinline__ void dsv4_set_error(int code, int a, int b) {
   atomicAdd(&g_dsv4_status[3], 1);
 }
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s (waits on other GPUs)
+// Limit of a wait on another GPU's flag, in nanoseconds: 2 s unless dsv4_set_peer_wait_ms() changed it.
+extern __device__ unsigned long long g_dsv4_peer_wait_ns;
+#define kWaitLimitNs g_dsv4_peer_wait_ns
 constexpr long long kWaitLimitCycles = 4000000000ll;         // 2-3 s of SM clock (waits inside one CTA)
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {

@@ -426,7 +426,9 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
   CommCtx comm{};
   if (o.comm) {
     comm = *o.comm;
-    if ((long long)grid.x * grid.y > kCommSlots || o.splits != 1 || o.batches != 1) return 104;
+    // the fused epilogue uses the tile number as its flag slot; a deposit-only launch raises no flags
+    if (o.splits != 1 || o.batches != 1) return 104;
+    if (!o.deposit_only && (long long)grid.x * grid.y > kCommSlots) return 104;
   }
   GemmArgs g{M, N, K, ldo, sa, sb, o.sb_ld ? o.sb_ld : (K + 127) / 128, accumulate_out, o.a_col_pb, o.b_row_pb,
              o.out_col_pb, o.splits, o.ws, o.counters, o.deposit_only, g_weight_prefetch, o.cluster, o.partial_stride};
@@ -452,6 +454,10 @@ int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, in
       bn = 32;
   }
   if (FP8 && bn > 64) bn = 64;
+  // fused all-reduce epilogue: one flag slot per tile, so a tile count beyond the slots needs the wider tile
+  if (o.comm && !o.deposit_only && bn < 64 &&
+      (long long)((N + bn - 1) / bn) * ((M + kBM - 1) / kBM) > kCommSlots)
+    bn = 64;
   switch (bn) {
     case 128:
       if constexpr (!FP8) return launch_gemm<128, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, o);

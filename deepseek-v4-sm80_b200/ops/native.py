@@ -151,10 +151,48 @@ def read_status(clear: bool = True) -> list:
     return list(buf)
 
 
+STATUS_NAMES = {1: "wait timeout inside a kernel", 2: "index out of range", 3: "peer GPU did not answer in time"}
+
+
+class DeviceStatusError(NativeError):
+    """A kernel gave up a bounded wait or refused an index; results computed since are not trustworthy."""
+
+
+def _raise_status(st) -> None:
+    raise DeviceStatusError(f"a kernel reported status {st[0]} ({STATUS_NAMES.get(st[0], 'unknown')}; detail "
+                            f"{st[1]}, {st[2]}; {st[3]} occurrences)")
+
+
 def assert_device_ok() -> None:
     st = read_status()
     if st[0] != 0:
-        raise NativeError(f"a kernel reported status {st[0]} (detail {st[1]}, {st[2]}; {st[3]} occurrences)")
+        _raise_status(st)
+
+
+class StatusProbe:
+    """Per-step, non-blocking view of the device status word.  ``snapshot()`` queues an 8-int device-to-host copy
+    into page-locked memory on the current stream; ``check()`` -- called after the caller has synchronised with that
+    stream for its own reasons (the sampled tokens' copy event) -- raises :class:`DeviceStatusError` if a kernel
+    recorded a timeout or a bad index.  The serving loop calls both once per step, so a peer that stopped answering
+    ends the scheduler process (and with it the server's health) instead of producing garbage tokens."""
+
+    def __init__(self):
+        self.host = torch.zeros(8, dtype=torch.int32, pin_memory=True)
+        self.armed = False
+
+    def snapshot(self) -> None:
+        check(cuda_lib().dsv4_status_snapshot(ctypes.c_void_p(self.host.data_ptr()), stream()),
+              "dsv4_status_snapshot")
+        self.armed = True
+
+    def check(self) -> None:
+        if self.armed and int(self.host[0]) != 0:
+            _raise_status([int(v) for v in self.host])
+
+
+def set_peer_wait_ms(ms: int) -> None:
+    """Limit of the in-kernel waits on other GPUs' flags (default 2 000 ms)."""
+    check(cuda_lib().dsv4_set_peer_wait_ms(ctypes.c_longlong(int(ms))), "dsv4_set_peer_wait_ms")
 
 
 I = ctypes.c_int

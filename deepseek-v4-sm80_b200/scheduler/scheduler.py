@@ -235,6 +235,8 @@ class Scheduler:
             self.stats.on_decode(batch.size)
             self.decode.filter_reqs(batch.reqs)
         self.bytes_d2h += out.next_tokens_cpu.numel() * out.next_tokens_cpu.element_size()
+        if out.status is not None:
+            self.bytes_d2h += 32   # the status word snapshot
         return ForwardData(batch, out, epochs)
 
     # ------------------------------------------------------------------ results
@@ -243,6 +245,10 @@ class Scheduler:
             return
         if last.output.copy_done_event is not None:
             last.output.copy_done_event.synchronize()
+        if last.output.status is not None:
+            # a kernel that gave up a wait (a peer GPU that stopped answering) left garbage behind: stop here, loudly.
+            # The exception ends this scheduler process; the supervisor then turns the server to 503.
+            last.output.status.check()
         batch, toks = last.batch, last.output.next_tokens_cpu
         finals = batch.is_final if batch.is_prefill else [True] * batch.size
         replies: List[DetokenizeMsg] = []

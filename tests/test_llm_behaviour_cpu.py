@@ -280,3 +280,31 @@ def test_public_abort_reaches_a_request_in_every_stage():
     _idle(llm)
     llm.cache.radix.reset()
     llm.engine.pool.assert_no_leak()
+
+
+def test_a_device_timeout_status_stops_the_scheduler_loudly():
+    """The serving loop reads the device status word once per step.  Here the word is faked (no GPU): the forward's
+    output carries a probe whose snapshot says 'peer GPU did not answer in time'; the step that reads it must raise
+    instead of committing tokens computed after the timeout."""
+    import pytest
+
+    from minisgl.ops.native import DeviceStatusError, StatusProbe
+
+    llm = _llm()
+    real = llm.engine.forward_batch
+    calls = {"n": 0}
+
+    class FakeProbe(StatusProbe):
+        def __init__(self, code):
+            self.host, self.armed = torch.tensor([code, 5, 77, 1, 0, 0, 0, 0], dtype=torch.int32), True
+
+    def forward(batch, args):
+        out = real(batch, args)
+        calls["n"] += 1
+        out.status = FakeProbe(3 if calls["n"] == 3 else 0)
+        return out
+
+    llm.engine.forward_batch = forward
+    with pytest.raises(DeviceStatusError, match="peer GPU did not answer"):
+        llm.generate(_prompts(2, 30, seed=21), SamplingParams(max_tokens=8, ignore_eos=True))
+    assert calls["n"] in (3, 4)          # the loop stopped at the step that read the bad status (one may be in flight)
