@@ -98,7 +98,8 @@ def run_reference(args) -> None:
     out = {"impl": "reference"}
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "minisgl")):
-        out["unavailable"] = "baseline/_ref is not installed (pip install --no-deps --target baseline/_ref /root/reference)"
+        out["unavailable"] = ("baseline/_ref is not installed (pip install --no-index --no-build-isolation --no-deps "
+                              "--target baseline/_ref <reference checkout>)")
         print(json.dumps(out))
         return
     probe = ("import sys; sys.path.insert(0, %r); import torch; from minisgl.kernel import deepseek_v4 as k; "

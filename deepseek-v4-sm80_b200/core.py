@@ -1,13 +1,12 @@
 """Request, batch and context types shared by the scheduler, the engine and the model.
 
 Counterpart of the reference's python/minisgl/core.py:21-253: ``SamplingParams`` (greedy iff
-``(T<=0 or top_k==1) and top_p==1``), the per-request lifecycle ledger that defers resource release until
-every issued forward has completed, ``Req`` with its host token buffer, and ``Batch``.
+``(T<=0 or top_k==1) and top_p==1``), ``FlightLedger`` (launch / landing counters that hold a request's storage until
+no forward that includes it is running), ``Req`` with its host token buffer, and ``Batch``.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from enum import Enum, auto
 from typing import Any, List, Optional
 
 import torch
@@ -28,63 +27,75 @@ class SamplingParams:
         return (self.temperature <= 0.0 or self.top_k == 1) and self.top_p == 1.0
 
 
-class RequestLifecycleState(Enum):
-    ACTIVE = auto()
-    TERMINAL_PENDING_RETIRE = auto()
-    RETIRED = auto()
+class FlightLedger:
+    """Book-keeping of the forwards launched for one admitted request.
 
+    With overlap scheduling a request can end (EOS, length, abort) while a forward that contains it is still running
+    on the device; its pages, window slots and table row must stay untouched until that forward has landed.  The
+    ledger counts launches and landings -- forwards of one rank land in launch order, so two counters are enough --
+    and moves through three phases: ``open`` (may launch), ``closing`` (ended, waiting for landings) and ``closed``
+    (storage returned).  The reference keeps a set of issue epochs for the same purpose
+    (python/minisgl/core.py:33-97); ``admission`` plays the role of its generation id and guards against a landing
+    that belongs to an earlier occupant of the same request object.
+    """
 
-@dataclass
-class RequestLifecycle:
-    """Which forwards were issued for a request generation and whether its terminal status is committed."""
+    __slots__ = ("admission", "launched", "landed", "phase", "ended_because")
 
-    generation_id: int = -1
-    state: RequestLifecycleState = RequestLifecycleState.ACTIVE
-    next_issue_epoch: int = 0
-    outstanding_epochs: set = field(default_factory=set)
-    terminal_finish_reason: Optional[str] = None
-    resources_released: bool = False
+    def __init__(self, admission: int = -1):
+        self.admission = admission
+        self.launched = 0
+        self.landed = 0
+        self.phase = "open"
+        self.ended_because: Optional[str] = None
 
-    def issue(self) -> int:
-        if self.state is not RequestLifecycleState.ACTIVE:
-            raise RuntimeError(f"cannot issue forward for request in lifecycle state {self.state.name}")
-        e = self.next_issue_epoch
-        self.next_issue_epoch += 1
-        self.outstanding_epochs.add(e)
-        return e
+    # -- forwards
+    def launch(self) -> int:
+        """Registers one forward; returns its ticket (to be handed back to :meth:`land`)."""
+        if self.phase != "open":
+            raise RuntimeError(f"request already ended ({self.ended_because}); no further forward may include it")
+        self.launched += 1
+        return self.launched - 1
 
-    def complete(self, *, generation_id: int, issue_epoch: int) -> None:
-        if generation_id != self.generation_id:
-            raise RuntimeError(f"request generation mismatch: expected={self.generation_id}, got={generation_id}")
-        if issue_epoch not in self.outstanding_epochs:
-            raise RuntimeError(f"request issue epoch {issue_epoch} is not outstanding")
-        self.outstanding_epochs.remove(issue_epoch)
-
-    def commit_terminal(self, finish_reason: str) -> None:
-        if self.state is not RequestLifecycleState.ACTIVE:
-            raise RuntimeError(f"terminal status may be committed exactly once; state is {self.state.name}")
-        self.state = RequestLifecycleState.TERMINAL_PENDING_RETIRE
-        self.terminal_finish_reason = finish_reason
-
-    @property
-    def accepts_completion(self) -> bool:
-        return self.state is RequestLifecycleState.ACTIVE
+    def land(self, admission: int, ticket: int) -> None:
+        if admission != self.admission:
+            raise RuntimeError(f"landing for admission {admission} reached a request of admission {self.admission}")
+        if ticket != self.landed or ticket >= self.launched:
+            raise RuntimeError(f"forward ticket {ticket} landed out of order (next expected {self.landed}, "
+                               f"{self.launched} launched)")
+        self.landed += 1
 
     @property
-    def ready_to_release_resources(self) -> bool:
-        return (self.state is RequestLifecycleState.TERMINAL_PENDING_RETIRE and not self.outstanding_epochs
-                and not self.resources_released)
+    def in_flight(self) -> int:
+        return self.launched - self.landed
 
-    def mark_resources_released(self) -> None:
-        if not self.ready_to_release_resources:
-            raise RuntimeError("request resources may retire only once after all issued forwards complete")
-        self.resources_released = True
-        self.state = RequestLifecycleState.RETIRED
+    # -- end of life
+    @property
+    def is_open(self) -> bool:
+        return self.phase == "open"
+
+    def end(self, because: str) -> None:
+        if self.phase != "open":
+            raise RuntimeError(f"request ended twice: first {self.ended_because!r}, now {because!r}")
+        self.phase, self.ended_because = "closing", because
+
+    @property
+    def may_release(self) -> bool:
+        """True exactly once: ended, nothing in flight, storage not yet returned."""
+        return self.phase == "closing" and self.launched == self.landed
+
+    def released(self) -> None:
+        if not self.may_release:
+            raise RuntimeError(f"storage release in phase {self.phase!r} with {self.in_flight} forward(s) in flight")
+        self.phase = "closed"
 
 
 @dataclass(eq=False)
 class Req:
-    input_ids: torch.Tensor  # 1-D CPU int32 tensor: prompt + committed output tokens
+    """One admitted request.  ``input_ids`` is the host copy of prompt + committed output; ``cached_len`` counts the
+    positions whose KV is in the cache, ``device_len`` the positions the device knows after the forward in
+    preparation (cached + the rows that forward runs), ``max_device_len`` the prompt plus the output budget."""
+
+    input_ids: torch.Tensor  # 1-D CPU int32
     table_idx: int
     cached_len: int
     output_len: int
@@ -93,58 +104,65 @@ class Req:
     cache_handle: Any = None
     reasoning_effort: Optional[str] = None
     swa_evicted_seqlen: int = 0
-    lifecycle: RequestLifecycle = field(default_factory=RequestLifecycle)
+    lifecycle: FlightLedger = field(default_factory=FlightLedger)
     pages: List[int] = field(default_factory=list)  # page ids in sequence order (owned or shared via the radix tree)
 
     def __post_init__(self) -> None:
-        assert self.input_ids.device.type == "cpu"
-        self.device_len = len(self.input_ids)
-        self.max_device_len = len(self.input_ids) + self.output_len
-        assert 0 <= self.cached_len < self.device_len <= self.max_device_len
-        self.prompt_len = len(self.input_ids)
+        if self.input_ids.device.type != "cpu":
+            raise ValueError("a request keeps its token ids on the host")
+        n = len(self.input_ids)
+        self.prompt_len = n
+        self.device_len = n
+        self.max_device_len = n + self.output_len
+        if not (0 <= self.cached_len < n <= self.max_device_len):
+            raise ValueError(f"inconsistent lengths: cached {self.cached_len}, prompt {n}, "
+                             f"limit {self.max_device_len}")
+        self._grow: Optional[torch.Tensor] = None   # preallocated host buffer, created at the first decode token
         self.reasoning_state = initial_reasoning_state(self.reasoning_effort)
-        self._host_buf: Optional[torch.Tensor] = None
 
-    def observe_generated_token(self, token_id: int, *, think_end_token_id: int) -> None:
-        self.reasoning_state = advance_reasoning_state(self.reasoning_state, token_id,
-                                                       think_end_token_id=think_end_token_id)
+    # -- lengths
+    @property
+    def extend_len(self) -> int:
+        """Rows the next forward has to run to catch up with ``device_len``."""
+        return self.device_len - self.cached_len
 
     @property
     def remain_len(self) -> int:
         return self.max_device_len - self.device_len
 
     @property
-    def extend_len(self) -> int:
-        return self.device_len - self.cached_len
-
-    def complete_one(self) -> None:
-        self.cached_len = self.device_len
-        self.device_len += 1
-
-    def append_host(self, next_token: torch.Tensor) -> None:
-        """Commits one sampled token to the host copy; the buffer is allocated once, on the first decode."""
-        if next_token.device.type != "cpu" or next_token.dtype != self.input_ids.dtype or next_token.numel() != 1:
-            raise ValueError("append_host expects one CPU token of the request's dtype")
-        n = len(self.input_ids)
-        if n >= self.max_device_len:
-            raise RuntimeError("request has no remaining host token capacity")
-        if self._host_buf is None:
-            self._host_buf = torch.empty(self.max_device_len, dtype=self.input_ids.dtype)
-            self._host_buf[:n].copy_(self.input_ids)
-        self._host_buf[n] = next_token.reshape(())
-        self.input_ids = self._host_buf[: n + 1]
-
-    @property
     def can_decode(self) -> bool:
-        return self.remain_len > 0
+        return self.device_len < self.max_device_len
 
     @property
     def can_commit_token(self) -> bool:
         return len(self.input_ids) < self.max_device_len
 
+    def complete_one(self) -> None:
+        """A forward covered everything up to ``device_len`` and sampled one more token."""
+        self.cached_len, self.device_len = self.device_len, self.device_len + 1
+
+    # -- host token buffer
+    def append_host(self, next_token: torch.Tensor) -> None:
+        """Appends one sampled token (a one-element CPU tensor of the ids' dtype) to the host copy."""
+        if next_token.numel() != 1 or next_token.device.type != "cpu" or next_token.dtype != self.input_ids.dtype:
+            raise ValueError("append_host expects one CPU token of the request's dtype")
+        have = len(self.input_ids)
+        if have >= self.max_device_len:
+            raise RuntimeError("the request's output budget is used up")
+        if self._grow is None:
+            self._grow = torch.empty(self.max_device_len, dtype=self.input_ids.dtype)
+            self._grow[:have] = self.input_ids
+        self._grow[have] = next_token.view(())
+        self.input_ids = self._grow[: have + 1]
+
+    def observe_generated_token(self, token_id: int, *, think_end_token_id: int) -> None:
+        self.reasoning_state = advance_reasoning_state(self.reasoning_state, token_id,
+                                                       think_end_token_id=think_end_token_id)
+
     def __repr__(self) -> str:
-        return (f"Req(uid={self.uid}, table_idx={self.table_idx}, cached_len={self.cached_len}, "
-                f"device_len={self.device_len}, max_device_len={self.max_device_len})")
+        return (f"Req(uid={self.uid}, slot={self.table_idx}, cached={self.cached_len}, device={self.device_len}, "
+                f"limit={self.max_device_len}, {self.lifecycle.phase})")
 
 
 @dataclass

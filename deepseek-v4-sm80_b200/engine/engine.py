@@ -67,6 +67,9 @@ class Engine:
             self.device = torch.device(config.device)
         self.is_cuda = self.device.type == "cuda"
         if self.is_cuda:
+            from ..utils.arch import require_blackwell
+
+            require_blackwell(self.device.index)   # the kernels exist for sm_100a only: fail before touching weights
             torch.cuda.set_device(self.device)
             self.stream = torch.cuda.Stream(self.device)
         else:
@@ -172,8 +175,11 @@ class Engine:
         if self.config.use_dummy_weight or not self.config.model_path:
             from ..models import synth
 
+            from ..env import ENV
+
             return synth.random_weights(cfg, self.device, tp.rank, tp.size, self.config.moe_mode, self.config.seed,
-                                        fast_experts=self.is_cuda)
+                                        fast_experts=self.is_cuda,
+                                        draw_on_host=self.is_cuda and bool(ENV.DUMMY_WEIGHT_ON_HOST))
         from ..models.weight import load_checkpoint
         from ..utils.hf import download_hf_weight
 

@@ -45,6 +45,7 @@ class _Env:
     DISABLE_MULTIMEM = EnvVar("DISABLE_MULTIMEM", False, _bool)
     NVTX = EnvVar("NVTX", False, _bool)
     DEBUG_BOUNDS = EnvVar("DEBUG_BOUNDS", False, _bool)
+    DUMMY_WEIGHT_ON_HOST = EnvVar("DUMMY_WEIGHT_ON_HOST", False, _bool)   # draw random weights on the CPU, copy shards
     PEER_WAIT_MS = EnvVar("PEER_WAIT_MS", 2000, int)      # limit of in-kernel waits on other GPUs
     DISABLE_STATUS_CHECK = EnvVar("DISABLE_STATUS_CHECK", False, _bool)   # per-step device status read
 

@@ -129,21 +129,26 @@ def _hash_table(cfg: ModelConfig, g, device) -> torch.Tensor:
 
 
 def random_weights(cfg: ModelConfig, device, rank: int = 0, size: int = 1, moe_mode: str = "tp", seed: int = 0,
-                   fast_experts: bool = False) -> Dict[str, torch.Tensor]:
-    """Runtime tensors of a random-init model, sharded for (rank, size)."""
+                   fast_experts: bool = False, draw_on_host: bool = False) -> Dict[str, torch.Tensor]:
+    """Runtime tensors of a random-init model, sharded for (rank, size).  ``draw_on_host``: the raw tensors are drawn
+    and quantised on the CPU and only the shards are copied to ``device`` (slow for a full model, but it keeps the
+    device's kernel stream free of initialisation kernels -- a small smoke model uses it so that the first launches a
+    profiler sees are the model's own)."""
     out: Dict[str, torch.Tensor] = {}
-    top = {k: W.shard_tensor(k, v, rank, size, moe_mode) for k, v in make_raw_top(cfg, device, seed).items()}
+    src = "cpu" if draw_on_host else device
+    move = (lambda t: t.to(device)) if draw_on_host else (lambda t: t)
+    top = {k: move(W.shard_tensor(k, v, rank, size, moe_mode)) for k, v in make_raw_top(cfg, src, seed).items()}
     out.update(W.build_top(cfg, top))
     experts = set(W.local_experts(cfg, rank, size, moe_mode))
     for l in range(cfg.num_layers):
-        raw = make_raw_layer(cfg, l, device, seed, fast_experts)
+        raw = make_raw_layer(cfg, l, src, seed, fast_experts)
         sh = {}
         for k, v in raw.items():
             full = f"layers.{l}.{k}"
             m = W._EXPERT.match(full)
             if m is not None and int(m.group(2)) not in experts:
                 continue
-            sh[k] = W.shard_tensor(full, v, rank, size, moe_mode)
+            sh[k] = move(W.shard_tensor(full, v, rank, size, moe_mode))
         del raw
         out.update(W.build_layer(cfg, l, sh, rank, size, moe_mode))
         del sh

@@ -21,7 +21,7 @@ class DecodeManager:
     def filter_reqs(self, reqs) -> None:
         """Keeps the requests of the last forward that can still decode."""
         for r in reqs:
-            if r.can_decode and r.lifecycle.accepts_completion:
+            if r.can_decode and r.lifecycle.is_open:
                 self.running.add(r)
             else:
                 self.running.discard(r)

@@ -128,7 +128,7 @@ class PrefillManager:
         req = Req(input_ids=p.input_ids, table_idx=slot, cached_len=m.length, output_len=p.output_len, uid=p.uid,
                   sampling_params=p.sampling_params, reasoning_effort=p.reasoning_effort)
         self.generation += 1
-        req.lifecycle.generation_id = self.generation
+        req.lifecycle.admission = self.generation
         req.prefill_granted = 0
         self.cache.adopt_prefix(req, m)
         return req

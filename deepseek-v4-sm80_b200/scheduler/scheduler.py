@@ -115,7 +115,7 @@ class Scheduler:
         req = self.prefill.abort(uid)
         if req is None:
             req = next((r for r in self.decode.running if r.uid == uid), None)
-        if req is not None and req.lifecycle.accepts_completion:
+        if req is not None and req.lifecycle.is_open:
             self.decode.remove(req)
             self._commit_terminal(req, "abort")
 
@@ -216,7 +216,7 @@ class Scheduler:
         return e.sampler.prepare(batch)
 
     def _forward(self, batch: Batch, args: BatchSamplingArgs) -> ForwardData:
-        epochs = [(r, r.lifecycle.generation_id, r.lifecycle.issue()) for r in batch.reqs]
+        epochs = [(r, r.lifecycle.admission, r.lifecycle.launch()) for r in batch.reqs]
         if batch.is_prefill:
             finals = batch.is_final
             chunks = batch.chunk_lens
@@ -253,8 +253,8 @@ class Scheduler:
         finals = batch.is_final if batch.is_prefill else [True] * batch.size
         replies: List[DetokenizeMsg] = []
         for i, (req, gen, epoch) in enumerate(last.epochs):
-            req.lifecycle.complete(generation_id=gen, issue_epoch=epoch)
-            if not req.lifecycle.accepts_completion:
+            req.lifecycle.land(gen, epoch)
+            if not req.lifecycle.is_open:
                 continue  # aborted / finished while this forward was in flight
             if not finals[i]:
                 self.cache.release_swa_behind(req)
@@ -283,7 +283,7 @@ class Scheduler:
         self._retire_ready()
 
     def _commit_terminal(self, req: Req, reason: str, announce: bool = True) -> None:
-        req.lifecycle.commit_terminal(reason)
+        req.lifecycle.end(reason)
         self.pending_retire.append(req)
         self.finished_uids.add(req.uid)
         if announce:
@@ -298,10 +298,10 @@ class Scheduler:
         """Resources go back only once every forward issued for the request has completed."""
         keep = []
         for req in self.pending_retire:
-            if req.lifecycle.ready_to_release_resources:
+            if req.lifecycle.may_release:
                 self.cache.cache_req(req, finished=True)
                 self.table.free(req.table_idx)
-                req.lifecycle.mark_resources_released()
+                req.lifecycle.released()
             else:
                 keep.append(req)
         self.pending_retire = keep

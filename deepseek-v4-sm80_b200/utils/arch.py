@@ -30,10 +30,12 @@ def is_sm100_supported() -> bool:
     return is_arch_supported(10, 0)
 
 
-def is_dsv4_blackwell_capability() -> bool:
-    return device_capability() in B200_CAPABILITIES
+def is_dsv4_blackwell_capability(index: int = 0) -> bool:
+    return device_capability(index) in B200_CAPABILITIES
 
 
-def require_blackwell() -> None:
-    if not is_dsv4_blackwell_capability():
-        raise RuntimeError(f"the DSV4 kernels are compiled for sm_100a only; found capability {device_capability()}")
+def require_blackwell(index: int = 0) -> None:
+    """Called by the engine before it loads anything onto a CUDA device."""
+    if not is_dsv4_blackwell_capability(index or 0):
+        raise RuntimeError("the DSV4 kernels are compiled for sm_100a only; found capability "
+                           f"{device_capability(index or 0)}")

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from minisgl.core import Req, RequestLifecycle, SamplingParams
+from minisgl.core import FlightLedger, Req, SamplingParams
 from minisgl.engine import graph_memory
 from minisgl.engine.graph_policy import default_buckets, pick_bucket, resolve_graph_buckets
 from minisgl.kvcache.pool import DSV4KVPool, PoolSizes, bytes_per_page
@@ -80,23 +80,26 @@ def test_sequence_admission():
 
 # ---------------------------------------------------------------------------- lifecycle
 def test_lifecycle_defers_release_until_all_forwards_complete():
-    lc = RequestLifecycle(generation_id=7)
-    e0, e1 = lc.issue(), lc.issue()
-    lc.commit_terminal("stop")
-    assert not lc.ready_to_release_resources and not lc.accepts_completion
+    lc = FlightLedger(admission=7)
+    t0, t1 = lc.launch(), lc.launch()
+    lc.end("stop")
+    assert not lc.may_release and not lc.is_open and lc.in_flight == 2
     with pytest.raises(RuntimeError):
-        lc.issue()
-    lc.complete(generation_id=7, issue_epoch=e0)
-    assert not lc.ready_to_release_resources
+        lc.launch()
     with pytest.raises(RuntimeError):
-        lc.complete(generation_id=8, issue_epoch=e1)
-    lc.complete(generation_id=7, issue_epoch=e1)
-    assert lc.ready_to_release_resources
-    lc.mark_resources_released()
+        lc.land(7, t1)                      # forwards land in launch order
+    lc.land(7, t0)
+    assert not lc.may_release
     with pytest.raises(RuntimeError):
-        lc.mark_resources_released()
+        lc.land(8, t1)                      # a landing of another admission
+    lc.land(7, t1)
+    assert lc.may_release and lc.in_flight == 0
+    lc.released()
+    assert lc.phase == "closed"
     with pytest.raises(RuntimeError):
-        lc.commit_terminal("again")
+        lc.released()
+    with pytest.raises(RuntimeError):
+        lc.end("again")
 
 
 def test_req_host_buffer_and_counters():
