@@ -20,7 +20,7 @@ from ..core import Batch, Req
 from ..dsv4_release import DSV4_RELEASE, RECIPES
 from ..kvcache.pool import DSV4KVPool, PoolSizes, bytes_per_page, bytes_per_req_slot, bytes_per_swa_slot
 from ..models.config import ModelConfig
-from ..models.deepseek_v4 import DSV4Model, ForwardBatch
+from ..models.deepseek_v4 import DSV4Model, ForwardBatch, GreedyTail
 from ..parallel import comm as comm_mod
 from ..parallel.info import set_tp_info
 from ..utils.logger import init_logger, set_log_rank
@@ -247,26 +247,38 @@ class Engine:
     # ------------------------------------------------------------------ forward
     def make_forward_batch(self, batch: Batch) -> ForwardBatch:
         return ForwardBatch(batch.input_ids, batch.positions, batch.slots, batch.out_loc, batch.last_idx,
-                            self.page_table, batch.is_prefill, batch.max_context, None)
+                            self.page_table, batch.is_prefill, batch.max_context, None,
+                            token_feedback=self.last_token if batch.is_decode else None)
 
     def forward_batch(self, batch: Batch, args: BatchSamplingArgs) -> ForwardOutput:
         t_ev = None
         if self.record_timings and self.is_cuda:
             t_ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             t_ev[0].record()
-        if batch.is_decode:
-            batch.input_ids = self.last_token[batch.slots.long()]
+        # Greedy batches are sampled by the forward's last kernel (argmax over the vocabulary-parallel logits with
+        # the shards' candidates exchanged in-kernel), which also stores the token as the request's next input.
+        greedy = args.all_greedy and args.mask_ids is None
+        toks = None
+        if batch.is_decode and batch.input_ids is None:
+            # decode rows take their token from last_token[slot] inside the embedding kernel, which fills this buffer
+            batch.input_ids = torch.empty(batch.positions.shape[0], dtype=torch.int32, device=self.device)
         if self.graph_runner is not None and batch.is_decode and self.graph_runner.can_replay(batch):
-            logits = self.graph_runner.replay(batch)
+            logits, toks = self.graph_runner.replay(batch)
+            if not greedy:
+                logits = self.comm.all_gather_last(logits)
+        elif greedy:
+            logits, toks = self.model.forward(self.make_forward_batch(batch), GreedyTail(self.last_token))
         else:
             logits = self.model.forward(self.make_forward_batch(batch))
         for req in batch.reqs:
             req.complete_one()
-        logits = logits[: batch.size]
-        next_tokens = self.sampler.sample(logits, args).to(torch.int32)
-        # the sampled token is the next step's input: keep it on the device, per request slot
-        sample_slots = batch.slots[: batch.size] if batch.is_decode else batch.slots[batch.last_idx]
-        self.last_token[sample_slots.long()] = next_tokens
+        if greedy:
+            next_tokens = toks[: batch.size]
+        else:
+            next_tokens = self.sampler.sample(logits[: batch.size], args).to(torch.int32)
+            # the sampled token is the next step's input: keep it on the device, per request slot
+            sample_slots = batch.slots[: batch.size] if batch.is_decode else batch.slots[batch.last_idx]
+            self.last_token[sample_slots.long()] = next_tokens
         probe = None
         if self.is_cuda:
             cpu = torch.empty(next_tokens.shape, dtype=next_tokens.dtype, pin_memory=True)

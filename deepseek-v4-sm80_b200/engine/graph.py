@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..core import Batch
-from ..models.deepseek_v4 import ForwardBatch
+from ..models.deepseek_v4 import ForwardBatch, GreedyTail
 from ..ops import native
 from ..utils.logger import init_logger
 from .graph_policy import pick_bucket
@@ -25,16 +25,25 @@ logger = init_logger(__name__)
 
 
 class GraphCaptureBuffer:
+    """Static inputs and outputs of the captured decode graphs.  The per-step inputs sit in one int32 block
+    [4, max_bs] (positions, request slots, token locations, and the number of valid rows in [3, 0]) that one copy
+    fills from the block the scheduler uploaded.  Token ids are not an input: the graph's embedding kernel gathers
+    them from the engine's device-resident feedback buffer and leaves them in ``input_ids``; the graph's last
+    kernel writes the greedy tokens to ``next_tokens``."""
+
     def __init__(self, max_bs: int, device):
         z = dict(dtype=torch.int32, device=device)
+        self.block = torch.zeros(4, max_bs, **z)
+        self.positions, self.slots, self.out_loc = self.block[0], self.block[1], self.block[2]
+        self.num_valid = self.block[3, :1]
         self.input_ids = torch.zeros(max_bs, **z)
-        self.positions = torch.zeros(max_bs, **z)
-        self.slots = torch.zeros(max_bs, **z)
-        self.out_loc = torch.zeros(max_bs, **z)
-        self.num_valid = torch.zeros(1, **z)
+        self.next_tokens = torch.zeros(max_bs, **z)
 
     def copy_from(self, batch: Batch, bs: int) -> None:
-        self.input_ids[:bs].copy_(batch.input_ids[:bs], non_blocking=True)
+        blk = getattr(batch, "device_block", None)
+        if blk is not None and blk.shape == (4, bs):
+            self.block[:, :bs].copy_(blk, non_blocking=True)      # one strided copy for everything
+            return
         self.positions[:bs].copy_(batch.positions[:bs], non_blocking=True)
         self.slots[:bs].copy_(batch.slots[:bs], non_blocking=True)
         self.out_loc[:bs].copy_(batch.out_loc[:bs], non_blocking=True)
@@ -57,11 +66,12 @@ class GraphRunner:
         self._capture_all()
 
     # ------------------------------------------------------------------ capture
-    def _forward(self, bs: int, max_context: int) -> torch.Tensor:
+    def _forward(self, bs: int, max_context: int):
+        """One decode forward on the static buffers: (this rank's logits shard [bs, vocab / tp], greedy tokens)."""
         b, e = self.buffer, self.engine
         fb = ForwardBatch(b.input_ids[:bs], b.positions[:bs], b.slots[:bs], b.out_loc[:bs], None, e.page_table,
-                          False, max_context, b.num_valid)
-        return e.model.forward(fb)
+                          False, max_context, b.num_valid, token_feedback=e.last_token)
+        return e.model.forward(fb, GreedyTail(e.last_token, b.next_tokens[:bs]))
 
     def _capture_all(self) -> None:
         e = self.engine
@@ -84,7 +94,7 @@ class GraphRunner:
                 if self.pool is None:
                     self.pool = g.pool()
                 self.graphs[(bs, ci)] = g
-                self.logits[(bs, ci)] = out
+                self.logits[(bs, ci)] = out[0]
                 self.capture_status["captured"] += 1
         torch.cuda.synchronize()
         native.assert_device_ok()
@@ -111,7 +121,9 @@ class GraphRunner:
             return False
         return True
 
-    def replay(self, batch: Batch) -> torch.Tensor:
+    def replay(self, batch: Batch):
+        """Returns (this rank's logits shard of the padded batch, greedy tokens int32 [bucket]); the graph has
+        already stored the greedy tokens as next-step feedback."""
         bs = pick_bucket(self.buckets, batch.size)
         ci = self._class_of(batch.max_context)
         if bs is None or ci is None:
@@ -121,4 +133,4 @@ class GraphRunner:
         self.graphs[(bs, ci)].replay()
         native.add_launches(self.launches[(bs, ci)])
         self.capture_status["replays"] += 1
-        return self.logits[(bs, ci)]
+        return self.logits[(bs, ci)], self.buffer.next_tokens[:bs]

@@ -38,6 +38,20 @@ class ForwardBatch:
     is_prefill: bool
     max_context: int             # max position + 1 over the batch (host value; bounds workspace widths)
     num_valid: Optional[torch.Tensor] = None  # [1] int32: rows >= num_valid are padding (graph replay)
+    # [slots+1] int32 (decode only): the token of row t is token_feedback[slots[t]], the previous step's sample that
+    # never left the device; the embedding kernel gathers it and fills input_ids
+    token_feedback: Optional[torch.Tensor] = None
+
+
+@dataclass
+class GreedyTail:
+    """Asks ``forward`` to finish with greedy sampling on the device: the argmax over the (vocabulary-parallel) logits
+    is taken inside one kernel that also exchanges the shards' candidates between ranks, and the token goes to
+    ``out[row]`` and to ``token_feedback[slot of the row]``.  The reference captures its greedy argmax in the decode
+    graph for the same reason (python/minisgl/engine/graph.py:419-421)."""
+
+    token_feedback: torch.Tensor   # [slots+1] int32
+    out: Optional[torch.Tensor] = None  # [rows] int32 (allocated when None)
 
 
 class Comm:
@@ -50,6 +64,10 @@ class Comm:
 
     def all_gather_last(self, x: torch.Tensor) -> torch.Tensor:
         return x
+
+    def greedy_tokens(self, logits_local, slots, num_valid, tail: "GreedyTail") -> torch.Tensor:
+        """Greedy tokens of rows whose logits are sharded over the vocabulary; the default gathers, then picks."""
+        return O.greedy_tokens(self.all_gather_last(logits_local), 0, slots, num_valid, tail.token_feedback, tail.out)
 
 
 class DSV4Model:
@@ -252,12 +270,16 @@ class DSV4Model:
         O.check_index(fb.out_loc, -1, locs, "out_loc")
         O.check_index(fb.page_table, 0, locs, "page_table")
 
-    def forward(self, fb: ForwardBatch) -> torch.Tensor:
-        """Returns fp32 logits [B, vocab] for the rows ``fb.last_idx``."""
+    def forward(self, fb: ForwardBatch, greedy: Optional[GreedyTail] = None):
+        """Returns fp32 logits [B, vocab] for the rows ``fb.last_idx``; with ``greedy`` returns
+        (this rank's logits shard [B, vocab / tp], greedy tokens [B] int32) and skips the logits all-gather."""
         cfg, w = self.cfg, self.w
-        if self._debug_bounds:
+        if self._debug_bounds and fb.token_feedback is None:
             self.audit_inputs(fb)
-        x = O.embed(fb.input_ids, w["embed.weight"], cfg.hc_mult)
+        x = O.embed(fb.input_ids, w["embed.weight"], cfg.hc_mult, fb.token_feedback,
+                    fb.slots if fb.token_feedback is not None else None)
+        if self._debug_bounds and fb.token_feedback is not None:
+            self.audit_inputs(fb)
         for l in range(cfg.num_layers):
             x = self.layer(l, x, fb)
         if fb.last_idx is not None and (fb.is_prefill or fb.last_idx.shape[0] != x.shape[0]):
@@ -265,4 +287,8 @@ class DSV4Model:
         y = O.hc_head(x, w["hc_head.fn"], w["hc_head.scale"], w["hc_head.base"], cfg.hc_eps, cfg.rms_norm_eps,
                       w["norm.weight"])
         logits = O.gemm_bf16(y, w["head.weight"], out_dtype=torch.float32)
+        if greedy is not None:
+            gathered = fb.last_idx is not None and (fb.is_prefill or fb.last_idx.shape[0] != fb.slots.shape[0])
+            slots = fb.slots[fb.last_idx] if gathered else fb.slots
+            return logits, self.comm.greedy_tokens(logits, slots, None if gathered else fb.num_valid, greedy)
         return self.comm.all_gather_last(logits)

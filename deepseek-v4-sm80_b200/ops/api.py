@@ -66,10 +66,28 @@ def check_index(idx, lo: int, hi: int, what: str) -> None:
 
 
 # --------------------------------------------------------------------------- elementwise
-def embed(ids, weight, m: int):
+def embed(ids, weight, m: int, feedback=None, slots=None):
+    """feedback [slots+1] int32 / slots [T]: row t embeds the token ``feedback[slots[t]]`` (the previous step's sample,
+    kept on the device) and stores it into ``ids[t]``."""
     if ids.is_cuda:
-        return _cu().embed(ids, weight, m)
+        return _cu().embed(ids, weight, m, feedback, slots)
+    if feedback is not None:
+        ids.copy_(feedback[slots.long()])
     return weight[ids.long()].unsqueeze(1).repeat(1, m, 1)
+
+
+def greedy_tokens(logits, v_base: int, slots, num_valid, token_feedback, out=None, comm_ctx=None):
+    """Greedy sample of every row (lowest index wins ties) into ``out`` [rows] int32 and, for valid rows, into
+    ``token_feedback[slots[row]]``.  ``logits`` may be one rank's vocabulary shard (first column = token v_base)."""
+    if logits.is_cuda:
+        return _cu().greedy_tokens(logits, v_base, slots, num_valid, token_feedback, out, comm_ctx)
+    tok = (logits.float().argmax(-1) + v_base).to(torch.int32)
+    if out is None:
+        out = torch.empty_like(tok)
+    out.copy_(tok)
+    n = logits.shape[0] if num_valid is None else int(num_valid)
+    token_feedback[slots[:n].long()] = tok[:n]
+    return out
 
 
 def rms_norm(x, weight, eps: float, want_q: bool = False):

@@ -50,7 +50,10 @@ __global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __r
   } else {
     for (int r = blockIdx.x; r < rows; r += gridDim.x) deposit(r, r + 1);
     __syncthreads();
-    if (comm_use_two_shot(comm, rows, cols)) {
+    if (comm_use_multimem(comm, rows, cols)) {
+      const int r = blockIdx.x;
+      if (r < rows) comm_row_multimem(comm, epoch, r, cols, &ok, [&](int col, const uint4& v) { emit(r, col, v); });
+    } else if (comm_use_two_shot(comm, rows, cols)) {
       const int r = blockIdx.x;
       if (r < rows) comm_row_two_shot(comm, epoch, r, cols, &ok, [&](int col, const uint4& v) { emit(r, col, v); });
     } else {
@@ -78,6 +81,80 @@ __global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __r
   }
   __syncthreads();
   if (threadIdx.x == 0) comm_finish(comm, gridDim.x);
+}
+
+// Greedy sampling fused behind the vocabulary-parallel LM head.  Every rank holds the logits of its own vocabulary
+// shard; instead of all-gathering [rows, vocab] fp32 and taking the argmax of the whole row, each rank takes the
+// argmax of its shard (one CTA per row), pushes the (value, global index) pair -- 8 bytes -- into every peer's symmetric
+// buffer, and picks the best of the `world` candidates (largest value, lowest index on ties: the same rule as the
+// single-rank argmax, so all ranks agree).  The winning token is written to out[row] and to token_feedback[slots[row]],
+// from where the next step's embedding gathers it.  world == 1: no exchange.
+__global__ void __launch_bounds__(1024) greedy_tokens_kernel(const float* __restrict__ logits, int ld, int v_local,
+                                                             int v_base, const int* __restrict__ slots,
+                                                             const int* __restrict__ num_valid,
+                                                             int* __restrict__ token_feedback, int* __restrict__ out,
+                                                             int rows, const CommCtx comm) {
+  pdl_entry();
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int row = blockIdx.x;
+  const float* lr = logits + (size_t)row * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < v_local; i += blockDim.x) {
+    const float x = lr[i];
+    if (x > best || (x == best && i < bi)) best = x, bi = i;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+  }
+  if ((threadIdx.x & 31) == 0) sv[threadIdx.x >> 5] = best, si[threadIdx.x >> 5] = bi;
+  __syncthreads();
+  if (threadIdx.x >= 32) return;
+  best = threadIdx.x < (blockDim.x >> 5) ? sv[threadIdx.x] : -INFINITY;
+  bi = threadIdx.x < (blockDim.x >> 5) ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+  }
+  if (threadIdx.x != 0) return;
+  int tok = bi == 0x7fffffff ? 0 : bi + v_base;
+  if (comm.world > 1) {
+    const uint32_t epoch = comm_epoch(comm);
+    const int parity = epoch & 1;
+    // candidate table of this call on every rank: [writer rank][row] of (value bits, token)
+    const uint2 mine = make_uint2(__float_as_uint(best), (uint32_t)tok);
+    for (int p = 0; p < comm.world; ++p) {
+      uint2* tab = reinterpret_cast<uint2*>(comm_data(comm, p, parity));
+      asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(tab + (size_t)comm.rank * rows + row),
+                   "r"(mine.x), "r"(mine.y)
+                   : "memory");
+    }
+    comm_publish(comm, row, epoch);
+    if (comm_wait(comm, row, epoch)) {
+      const uint2* tab = reinterpret_cast<const uint2*>(comm_data(comm, comm.rank, parity));
+      float bv = -INFINITY;
+      int bt = 0x7fffffff;
+      for (int p = 0; p < comm.world; ++p) {
+        uint2 c;
+        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];"
+                     : "=r"(c.x), "=r"(c.y)
+                     : "l"(tab + (size_t)p * rows + row)
+                     : "memory");
+        const float v = __uint_as_float(c.x);
+        if (v > bv || (v == bv && (int)c.y < bt)) bv = v, bt = (int)c.y;
+      }
+      tok = bt == 0x7fffffff ? 0 : bt;
+    }
+    comm_finish(comm, gridDim.x);
+  }
+  out[row] = tok;
+  if (!num_valid || row < *num_valid) token_feedback[slots[row]] = tok;
 }
 
 // A wait that nothing satisfies: used by the failure-detection test to show that a missing peer ends in an error
@@ -108,6 +185,8 @@ DSV4_API int dsv4_comm_layout(long long* flags_bytes, int* channels, int* slots,
   return 0;
 }
 
+DSV4_API int dsv4_comm_ctx_size() { return (int)sizeof(CommCtx); }
+
 // x may be null when this rank's partial is already in the channel's symmetric buffer (a GEMM launched in deposit
 // mode on the same channel wrote it).  res / post / comb / xout (all null or all given): the hyper-connection post
 // mix is applied to the reduced rows and xout [rows, 4, cols] is written instead of out.
@@ -124,6 +203,21 @@ DSV4_API int dsv4_allreduce(const void* x, void* out, int rows, int cols, const 
   else
     dsv4_launch(allreduce_kernel<false>, rows < 1024 ? rows : 1024, 256, 0, st, (const __nv_bfloat16*)x,
                 (__nv_bfloat16*)out, rows, cols, hc, *comm);
+  return (int)cudaGetLastError();
+}
+
+// logits fp32 [rows, ld >= v_local]: this rank's vocabulary shard, whose first column is token v_base.
+// comm == null or world == 1: plain argmax.  Writes out[rows] (int32) and token_feedback[slots[row]] for valid rows.
+DSV4_API int dsv4_greedy_tokens(const float* logits, int ld, int v_local, int v_base, const int* slots,
+                                const int* num_valid, int* token_feedback, int* out, int rows, const CommCtx* comm,
+                                cudaStream_t st) {
+  if (rows <= 0) return 0;
+  CommCtx c{};
+  c.world = 1;
+  if (comm) c = *comm;
+  if (c.world > 1 && (rows > kCommSlots || (long long)rows * c.world * 8 > c.data_bytes)) return 503;
+  dsv4_launch(greedy_tokens_kernel, rows, 1024, 0, st, logits, ld, v_local, v_base, slots, num_valid, token_feedback, out,
+              rows, c);
   return (int)cudaGetLastError();
 }
 

@@ -17,6 +17,7 @@
 constexpr int kMaxRanks = 8;
 constexpr int kCommChannels = 3;
 constexpr int kCommSlots = 8192;
+constexpr int kTwoShotSlot = kCommSlots / 2;  // second-phase flags of the two-shot paths start here
 
 struct CommCtx {
   uint8_t* peer[kMaxRanks];   // symmetric base of every rank (peer[rank] is local)
@@ -27,7 +28,11 @@ struct CommCtx {
   long long small_bytes;      // bytes of one result buffer of the two-shot path (0: none)
   int* epoch;                 // local [kCommChannels] device ints
   int* done;                  // local [kCommChannels] device ints
+  uint8_t* mc;                // NVSwitch multicast mapping of the same allocation (null: none)
+  int mm;                     // 1: reductions go through the switch (multimem.ld_reduce / multimem.st)
+  int pad_;
 };
+static_assert(sizeof(CommCtx) == 128, "the Python side mirrors this struct field by field");
 
 __host__ __device__ inline size_t comm_flags_bytes() { return (size_t)kCommChannels * kMaxRanks * kCommSlots * 4; }
 __device__ __forceinline__ uint32_t* comm_flag(const CommCtx& c, int on_rank, int writer, int slot) {
@@ -166,13 +171,73 @@ __device__ __forceinline__ bool comm_wait_one(const CommCtx& c, int writer, int 
   return true;
 }
 
+// ---------------------------------------------------------------- in-switch reduction (NVLS)
+// The multicast mapping `c.mc` addresses the same offset of the symmetric allocation on EVERY rank at once:
+//   multimem.st        writes a value to all ranks' copies (one instruction instead of world-1 peer stores),
+//   multimem.ld_reduce makes the switch load all ranks' copies, add them and return the sum.
+// Flags keep the layout and the epoch protocol of the peer-to-peer paths, so both kinds of call can share a channel.
+__device__ __forceinline__ uint32_t* comm_mc_flag(const CommCtx& c, int writer, int slot) {
+  return reinterpret_cast<uint32_t*>(c.mc) + ((size_t)c.channel * kMaxRanks + writer) * kCommSlots + slot;
+}
+__device__ __forceinline__ __nv_bfloat16* comm_mc_data(const CommCtx& c, int parity) {
+  return reinterpret_cast<__nv_bfloat16*>(c.mc + comm_flags_bytes() +
+                                          ((size_t)c.channel * 2 + parity) * (size_t)c.data_bytes);
+}
+__device__ __forceinline__ void mm_st_u32(uint32_t* p, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void mm_st16(void* p, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+// Sum of the 8 bf16 values at this offset over all ranks, accumulated in fp32 inside the switch.
+__device__ __forceinline__ uint4 mm_ld_reduce16(const void* p) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ bool comm_use_multimem(const CommCtx& c, int rows, int cols) {
+  return c.mm && c.mc != nullptr && c.world > 1 && rows <= kTwoShotSlot && rows <= (int)gridDim.x && cols % 8 == 0;
+}
+// One-shot all-reduce of ONE row by ONE CTA through the switch (all threads call it; the CTA's partial row already
+// sits in comm_data(rank, parity) and the CTA has synchronised).  One multicast store raises this rank's flag on every
+// rank; once the world-1 other flags arrived, every rank asks the switch for the sum of the row.  One NVLink round
+// trip for the flags and one for the data, against two each on the two-shot path.  Every rank issues the same
+// ld_reduce, and the switch adds the ranks' copies in a fixed order, so all ranks receive the same bits (the
+// communicator checks this once at start-up and otherwise stays on the peer-to-peer paths).
+template <class Emit>
+__device__ __forceinline__ void comm_row_multimem(const CommCtx& c, uint32_t epoch, int row, int cols, int* sh_ok,
+                                                  Emit emit) {
+  const int parity = epoch & 1;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    mm_st_u32(comm_mc_flag(c, c.rank, row), epoch);
+    *sh_ok = comm_wait(c, row, epoch) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!*sh_ok) return;
+  const __nv_bfloat16* src = comm_mc_data(c, parity) + (size_t)row * cols;
+  for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 16) {
+    const int i1 = i + blockDim.x * 8;
+    const uint4 v0 = mm_ld_reduce16(src + i);
+    if (i1 < cols) {
+      const uint4 v1 = mm_ld_reduce16(src + i1);
+      emit(i1, v1);
+    }
+    emit(i, v0);
+  }
+}
+
 // Two-shot all-reduce of ONE row by ONE CTA (all threads call it; the CTA's partial row already sits in
 // comm_data(rank, parity) and the CTA has synchronised).  Row r is owned by rank r % world: the owner waits for the
 // 7 partials, sums them in rank order, writes the result row into every rank's result buffer and raises a second
 // flag; the other ranks only tell the owner that their partial is ready and wait for that second flag.  Per rank
 // this moves 2 * (world-1)/world of the tensor over NVLink instead of (world-1) times the tensor, and a non-owner
 // sends one flag instead of world-1.  emit(col, v) receives 8 reduced bf16 values of the row.
-constexpr int kTwoShotSlot = kCommSlots / 2;
 template <class Emit>
 __device__ __forceinline__ void comm_row_two_shot(const CommCtx& c, uint32_t epoch, int row, int cols, int* sh_ok,
                                                   Emit emit) {
@@ -246,9 +311,13 @@ __device__ __forceinline__ int comm_big_block_rows(int rows) {
   return r;
 }
 inline bool comm_host_use_big(const CommCtx& c, int rows) { return c.world > 1 && c.big && rows > 256; }
+// With c.mm set, the owner's reduction is one multimem.ld_reduce per 16 bytes (the switch adds the ranks' partials)
+// and its result goes to all ranks with one multimem.st; the second flag is one multicast store as well.  Per rank
+// that is (world-1)/world of the tensor in each NVLink direction, half of what the peer-to-peer form moves.
 template <class Deposit, class Emit>
 __device__ __forceinline__ void comm_big_two_shot(const CommCtx& c, uint32_t epoch, int rows, int cols, int* sh_ok,
                                                   Deposit deposit, Emit emit) {
+  const bool use_mm = c.mm && c.mc != nullptr;
   const int parity = epoch & 1, G = gridDim.x, R = comm_big_block_rows(rows), nblk = (rows + R - 1) / R;
   __nv_bfloat16* mine = comm_data(c, c.rank, parity);
   for (int b = blockIdx.x, k = 0; b < nblk; b += G, ++k) {
@@ -267,7 +336,32 @@ __device__ __forceinline__ void comm_big_two_shot(const CommCtx& c, uint32_t epo
     }
     __syncthreads();
     const int ok = *sh_ok;
-    if (owner == c.rank && ok) {
+    if (owner == c.rank && ok && use_mm) {
+      // the block's rows are contiguous: four independent switch reductions per thread and trip
+      const int c8 = cols / 8, n8 = (r1 - r0) * c8;
+      __nv_bfloat16* mcb = comm_mc_data(c, parity) + (size_t)r0 * cols;
+      for (int i = threadIdx.x; i < n8; i += blockDim.x * 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = i + u * (int)blockDim.x;
+          if (j < n8) v[u] = mm_ld_reduce16(mcb + (size_t)j * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = i + u * (int)blockDim.x;
+          if (j < n8) {
+            mm_st16(mcb + (size_t)j * 8, v[u]);
+            emit(r0 + j / c8, (j % c8) * 8, v[u]);
+          }
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        mm_st_u32(comm_mc_flag(c, c.rank, kTwoShotSlot + b), epoch);
+      }
+    } else if (owner == c.rank && ok) {
       for (int r = r0; r < r1; ++r) {
         const size_t off = (size_t)r * cols;
         for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 16) {

@@ -18,11 +18,20 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 }
 
 // ------------------------------------------------------------------ embedding
-__global__ void embed_kernel(const int* __restrict__ ids, const uint4* __restrict__ w, uint4* __restrict__ out, int m,
-                             int h8) {
+// feedback != null: the token of row t is feedback[slots[t]] (the token sampled for that request by the previous
+// step, which never left the device) and is also written to ids[t] for the kernels that need the id later.
+__global__ void embed_kernel(int* __restrict__ ids, const int* __restrict__ feedback, const int* __restrict__ slots,
+                             const uint4* __restrict__ w, uint4* __restrict__ out, int m, int h8) {
   pdl_entry();
   const int t = blockIdx.x;
-  const uint4* src = w + (size_t)ids[t] * h8;
+  int id;
+  if (feedback) {
+    id = feedback[slots[t]];
+    if (threadIdx.x == 0) ids[t] = id;
+  } else {
+    id = ids[t];
+  }
+  const uint4* src = w + (size_t)id * h8;
   for (int i = threadIdx.x; i < h8; i += blockDim.x) {
     const uint4 v = src[i];
     for (int s = 0; s < m; ++s) out[((size_t)t * m + s) * h8 + i] = v;
@@ -345,10 +354,11 @@ __global__ void index_check_kernel(const int* __restrict__ idx, long long n, int
 
 }  // namespace
 
-DSV4_API int dsv4_embed(const int* ids, const void* w, void* out, int t, int m, int h, cudaStream_t st) {
+DSV4_API int dsv4_embed(int* ids, const int* feedback, const int* slots, const void* w, void* out, int t, int m, int h,
+                        cudaStream_t st) {
   if (t <= 0) return 0;
-  if (h % 8) return 120;
-  dsv4_launch(embed_kernel, t, 256, 0, st, ids, (const uint4*)w, (uint4*)out, m, h / 8);
+  if (h % 8 || (feedback && !slots)) return 120;
+  dsv4_launch(embed_kernel, t, 256, 0, st, ids, feedback, slots, (const uint4*)w, (uint4*)out, m, h / 8);
   return (int)cudaGetLastError();
 }
 // q_out / s_out (may be null): additionally writes the e4m3 quantisation of the result, dense [rows, d] with one

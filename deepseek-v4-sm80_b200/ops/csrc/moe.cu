@@ -695,7 +695,10 @@ __global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat1
   } else {
     for (int t = blockIdx.x; t < t_rows; t += gridDim.x) combine(t, t + 1);
     __syncthreads();
-    if (comm_use_two_shot(comm, t_rows, h)) {
+    if (comm_use_multimem(comm, t_rows, h)) {
+      const int t = blockIdx.x;
+      if (t < t_rows) comm_row_multimem(comm, epoch, t, h, &ok, [&](int col, const uint4& v) { emit(t, col, v); });
+    } else if (comm_use_two_shot(comm, t_rows, h)) {
       const int t = blockIdx.x;
       if (t < t_rows) comm_row_two_shot(comm, epoch, t, h, &ok, [&](int col, const uint4& v) { emit(t, col, v); });
     } else {

@@ -55,10 +55,23 @@ def check_index(idx, lo: int, hi: int, tag: int) -> None:
     nv.call("check_index", nv.ptr(idx), ctypes.c_longlong(idx.numel()), I(lo), I(hi), I(tag))
 
 
-def embed(ids, weight, m: int):
+def embed(ids, weight, m: int, feedback=None, slots=None):
+    """feedback / slots: row t embeds token feedback[slots[t]] and writes it to ids[t]."""
     t, h = ids.shape[0], weight.shape[1]
     out = torch.empty(t, m, h, dtype=weight.dtype, device=weight.device)
-    nv.call("embed", _i32(ids), nv.ptr(weight), nv.ptr(out), I(t), I(m), I(h))
+    nv.call("embed", _i32(ids), nv.ptr(feedback), nv.ptr(slots), nv.ptr(weight), nv.ptr(out), I(t), I(m), I(h))
+    return out
+
+
+def greedy_tokens(logits, v_base: int, slots, num_valid, token_feedback, out=None, comm_ctx=None):
+    """Argmax of fp32 logits rows (this rank's vocabulary shard starting at token v_base; with comm_ctx the shards'
+    candidates are exchanged inside the kernel), written to out [rows] int32 and to token_feedback[slots[row]]."""
+    rows, v = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    nv.call("greedy_tokens", nv.ptr(logits), I(logits.stride(0)), I(v), I(v_base), _i32(slots), nv.ptr(num_valid),
+            _i32(token_feedback), _i32(out), I(rows), ctypes.byref(comm_ctx) if comm_ctx is not None else None)
     return out
 
 

@@ -39,7 +39,8 @@ class CommCtx(ctypes.Structure):
     _fields_ = [("peer", ctypes.c_void_p * MAX_RANKS), ("rank", ctypes.c_int), ("world", ctypes.c_int),
                 ("channel", ctypes.c_int), ("big", ctypes.c_int), ("data_bytes", ctypes.c_longlong),
                 ("small_bytes", ctypes.c_longlong),
-                ("epoch", ctypes.c_void_p), ("done", ctypes.c_void_p)]
+                ("epoch", ctypes.c_void_p), ("done", ctypes.c_void_p),
+                ("mc", ctypes.c_void_p), ("mm", ctypes.c_int), ("pad_", ctypes.c_int)]
 
 
 class SymmComm(Comm):
@@ -60,6 +61,7 @@ class SymmComm(Comm):
         nv.check(lib.dsv4_comm_layout(ctypes.byref(fb), ctypes.byref(ch), ctypes.byref(sl), ctypes.byref(mr)),
                  "dsv4_comm_layout")
         assert mr.value == MAX_RANKS
+        assert lib.dsv4_comm_ctx_size() == ctypes.sizeof(CommCtx), "CommCtx layout differs from the native library's"
         self.flags_bytes, self.channels, self.slots = fb.value, ch.value, sl.value
         self.data_bytes = (max_rows * hidden * 2 + 255) // 256 * 256
         # result buffers of the two-shot path (row counts of a decode batch): the owner of a row writes its sum here
@@ -72,7 +74,8 @@ class SymmComm(Comm):
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         ptrs = list(self.handle.buffer_ptrs)
-        self.has_multicast = bool(getattr(self.handle, "multicast_ptr", 0))
+        self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.has_multicast = bool(self.mc_ptr)
         self.ctx = []
         for c in range(self.channels):
             x = CommCtx()
@@ -82,9 +85,15 @@ class SymmComm(Comm):
             x.small_bytes = self.small_bytes
             x.epoch = self.state.data_ptr()
             x.done = self.state.data_ptr() + 4 * self.channels
+            x.mc, x.mm = self.mc_ptr or None, 0
             self.ctx.append(x)
         self.counters = {"all_reduce": 0, "gemm_allreduce": 0, "moe_allreduce": 0, "all_gather": 0}
         self.big = False
+        self.multimem = False
+        from ..env import ENV
+
+        if self.has_multicast and self.size > 1 and not _SKIP_EXCHANGE and not ENV.DISABLE_MULTIMEM:
+            self._enable_multimem(hidden, min(max_rows, 256))
         if _BIG and self.size > 1 and not _SKIP_EXCHANGE and max_rows >= 512:
             self._enable_big(hidden, max_rows)
 
@@ -92,6 +101,46 @@ class SymmComm(Comm):
         self.big = on
         for x in self.ctx:
             x.big = 1 if on else 0
+
+    def _set_multimem(self, on: bool) -> None:
+        self.multimem = on
+        for x in self.ctx:
+            x.mm = 1 if on else 0
+
+    def _enable_multimem(self, hidden: int, rows: int) -> None:
+        """Switch the in-switch (NVLS) reductions on and keep them only if, on a few random tensors, (a) the sums
+        agree with NCCL, (b) no wait ran out and (c) every rank received exactly the same bits -- the one-shot form
+        lets each rank ask the switch for the sum itself, and replicated activations must stay identical across
+        ranks.  All ranks decide together."""
+        from ..utils.logger import init_logger
+
+        self._set_multimem(True)
+        good = True
+        status = [0]
+        for it in range(3):
+            g = torch.Generator(device="cpu").manual_seed(4321 + 17 * it + self.rank)
+            x = (torch.randn(rows, hidden, generator=g) * (1 + it)).to(self.device, torch.bfloat16)
+            want = x.float()
+            dist.all_reduce(want, group=self.group)
+            got = self.all_reduce(x)
+            torch.cuda.synchronize(self.device)
+            status = nv.read_status(clear=True)
+            tol = 0.03 * self.size ** 0.5 * 4 * (1 + it)
+            bits = got.view(torch.int16).to(torch.int64)
+            h = torch.stack([bits.sum(), (bits * torch.arange(1, bits.numel() + 1, device=self.device).view_as(bits)
+                                          % 1000003).sum()])
+            lo, hi = h.clone(), h.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.group)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.group)
+            good = good and status[0] == 0 and bool(torch.isfinite(got).all()) and \
+                float((got.float() - want).abs().max()) < tol and bool((lo == hi).all())
+        flag = torch.tensor([1 if good else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self._set_multimem(False)
+            init_logger(__name__).warning("in-switch (multimem) all-reduce failed its start-up check "
+                                          f"(status {status[:4]}); using the peer-to-peer exchange")
+        self.counters["all_reduce"] = 0
 
     def _enable_big(self, hidden: int, max_rows: int) -> None:
         """Switch the block-wise two-shot path on, reduce tensors with it and with NCCL, and keep it only if every
@@ -199,6 +248,16 @@ class SymmComm(Comm):
                 nv.ptr(out), nv.ptr(num_valid), I(t), I(topk), I(h), nv.ptr(None), nv.ptr(None), nv.ptr(None),
                 nv.ptr(None), ctypes.byref(self.ctx[self.CH_MOE]))
         return out
+
+    def greedy_tokens(self, logits_local, slots, num_valid, tail) -> torch.Tensor:
+        """Per-shard argmax + candidate exchange + pick, in one kernel (csrc/comm.cu: greedy_tokens_kernel); no
+        logits all-gather."""
+        from ..ops import api as O
+
+        self.counters["greedy_exchange"] = self.counters.get("greedy_exchange", 0) + 1
+        per = -(-self.vocab_size // self.size) if self.vocab_size else logits_local.shape[1]
+        return O.greedy_tokens(logits_local, self.rank * per, slots, num_valid, tail.token_feedback, tail.out,
+                               comm_ctx=self.ctx[self.CH_GENERIC])
 
     def all_gather_last(self, x: torch.Tensor) -> torch.Tensor:
         self.counters["all_gather"] += 1

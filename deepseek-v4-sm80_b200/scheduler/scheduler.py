@@ -173,7 +173,8 @@ class Scheduler:
         if batch.is_decode:
             bs = len(reqs)
             padded = e.graph_runner.padded_size(bs) if e.graph_runner is not None else bs
-            host = torch.empty(3, padded, dtype=torch.int32, pin_memory=e.is_cuda)
+            host = torch.zeros(4, padded, dtype=torch.int32, pin_memory=e.is_cuda)
+            host[3, 0] = bs                       # number of valid rows, read by the captured graph
             pos = [r.device_len - 1 for r in reqs]
             host[0, :bs] = torch.tensor(pos, dtype=torch.int32)
             host[1, :bs] = torch.tensor([r.table_idx for r in reqs], dtype=torch.int32)
@@ -185,6 +186,8 @@ class Scheduler:
             dev = host.to(self.device, non_blocking=True)
             self.bytes_h2d += host.numel() * 4
             batch.positions, batch.slots, batch.out_loc = dev[0], dev[1], dev[2]
+            batch.device_block = dev
+            batch.input_ids = None                # gathered on the device from the previous step's samples
             batch.last_idx = None
             batch.num_token_non_padded = bs
             batch.padded_reqs = list(reqs) + [None] * (padded - bs)

@@ -278,7 +278,7 @@ def test_graph_runner_selects_bucket_and_context_class_without_a_gpu():
     r.logits = {k: f"logits{k}" for k in r.graphs}
     r.launches = {k: 100 + k[0] for k in r.graphs}
     copies = []
-    r.buffer = SimpleNamespace(copy_from=lambda batch, bs: copies.append(bs))
+    r.buffer = SimpleNamespace(copy_from=lambda batch, bs: copies.append(bs), next_tokens=torch.arange(8))
 
     def batch(size, ctx, phase="decode", padded=None):
         n = padded if padded is not None else size
@@ -295,7 +295,8 @@ def test_graph_runner_selects_bucket_and_context_class_without_a_gpu():
     from minisgl.ops import native
 
     n0 = native.launch_count()
-    assert r.replay(b) == "logits(4, 1)" and r.graphs[(4, 1)].n == 1 and copies == [4]
+    logits, toks = r.replay(b)
+    assert logits == "logits(4, 1)" and toks.tolist() == [0, 1, 2, 3] and r.graphs[(4, 1)].n == 1 and copies == [4]
     assert native.launch_count() - n0 == 104 and r.capture_status["replays"] == 1
     with pytest.raises(AssertionError, match="padded"):
         r.replay(batch(3, 5000))                      # not padded to its bucket

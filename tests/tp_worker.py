@@ -27,6 +27,29 @@ def rel(a, b):
 
 
 def main():
+    """Runs the checks; a failing rank does not just exit: every rank first reaches the final barrier and tears its
+    process group (and with it the symmetric / multicast mappings) down, then the failing one exits non-zero."""
+    failure = None
+    try:
+        _checks()
+    except BaseException as e:  # noqa: BLE001 - reported below, after the orderly teardown
+        import traceback
+
+        failure = e
+        traceback.print_exc()
+    try:
+        if torch.cuda.is_available() and torch.cuda.is_initialized():
+            torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        pass
+    if failure is not None:
+        sys.exit(1)
+
+
+def _checks():
     ap = argparse.ArgumentParser()
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--moe-mode", default="ep")
@@ -58,6 +81,9 @@ def main():
 
         assert isinstance(comm, SymmComm), type(comm)
         assert comm.big, "the block-wise two-shot path failed its start-up check"
+        if comm.has_multicast and os.environ.get("MINISGL_DISABLE_MULTIMEM", "0") != "1":
+            assert comm.multimem, "the in-switch all-reduce failed its start-up check"
+        print(f"rank {rank}: multicast {comm.has_multicast} multimem {comm.multimem} big {comm.big}", flush=True)
         # 1) stand-alone all-reduce vs NCCL, several sizes, repeated (epochs / parity buffers)
         # (2000 rows: more blocks than CTAs, i.e. several passes of the block-wise path)
         for rows in (1, 8, 128, 257, 1000, 2000):
@@ -68,6 +94,22 @@ def main():
                 out = comm.all_reduce(x)
                 torch.cuda.synchronize()
                 assert rel(out, ref) < 1e-2, (rows, it, rel(out, ref))
+        # 1b) a rank that arrives half a second late (a host-side pause before its launch, as a GC pause or a slow
+        # message would cause): the others wait inside their kernels, well within the limit, and the sums still agree
+        for late in range(min(world, 2)):
+            x = (torch.randn(128, 4096, device=dev) * (rank + 1)).to(torch.bfloat16)
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            torch.cuda.synchronize()
+            dist.barrier()
+            if rank == late:
+                import time
+
+                time.sleep(0.5)
+            out = comm.all_reduce(x)
+            torch.cuda.synchronize()
+            assert rel(out, ref) < 1e-2, ("late rank", late, rel(out, ref))
+            assert native.read_status(clear=False)[0] == 0
         # 2) fused FP8 GEMM + all-reduce vs separate GEMM + NCCL
         from minisgl.ops import api as O
 
@@ -104,8 +146,6 @@ def main():
         native.assert_device_ok()
         assert rel(l_tp, l_1) < 0.2, rel(l_tp, l_1)  # e4m3 rounding and router top-k flips amplify over layers
         print(f"OK cuda rank {rank} rel {rel(l_tp, l_1):.4f} counters {comm.counters}", flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
 
 
 if __name__ == "__main__":
