@@ -256,6 +256,7 @@ def main():
             "config": {"model": f"DeepSeek-V4-Flash architecture, {layers}/43 layers, {args.experts} experts",
                        "global_batch": args.batch, "seq_len": args.prompt_len, "output_len": n_out,
                        "parallelism": f"tp{world}" + (f"+{args.moe_mode}{world}" if world > 1 else ""),
+                       "collectives": getattr(llm.engine.comm, "mode", "none"),
                        "page_size": eng.page_size, "cuda_graph": eng.graph_runner is not None,
                        "kv_pages": eng.num_pages, "swa_slots": eng.kv_plan["swa_slots"],
                        "l2": "inputs larger than L2 (weights read per step: %.1f GiB per GPU)" % (eng.weight_bytes / 2**30)},

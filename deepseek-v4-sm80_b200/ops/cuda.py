@@ -234,6 +234,34 @@ def indexer_kv_store(pooled, fb, norm_w, eps, spec, vals, scales, ps: int):
             rope_params(spec), nv.ptr(vals), nv.ptr(scales), I(t), I(d), I(ps))
 
 
+LOGITS_WORKSPACE_BYTES = 512 << 20   # bound of the fp32 logits workspace of one indexer call (rows are chunked)
+
+
+def _mma_indexer_ok(h: int, d: int, ps: int) -> bool:
+    rpp = ps // 4
+    return h == 64 and d == 128 and ps % 4 == 0 and rpp >= 8 and (64 % rpp == 0 or rpp % 64 == 0)
+
+
+def indexer_logits(qc, wf, vals, scales, slots, positions, pt, ps: int, width: int, prefill: bool, out=None,
+                   force_scalar: bool = False):
+    """fp32 logits [t, width] of the rows' compressed history (-inf past each row's length).  64 x 128 indexers run
+    on the tensor cores (csrc/indexer_mma.cu); other shapes on the CUDA-core kernel."""
+    t, h, d = qc.shape
+    logits = out if out is not None else torch.empty(t, width, dtype=torch.float32, device=qc.device)
+    if _mma_indexer_ok(h, d, ps) and not force_scalar:
+        tg = 4 if (prefill and t >= 4) else 1
+        groups = (t + tg - 1) // tg
+        nblocks = (width + 127) // 128
+        nsplit = max(1, min(nblocks, -(-2 * num_sms(qc.device) // groups)))
+        nv.call("indexer_logits_mma", nv.ptr(qc), nv.ptr(wf), nv.ptr(vals), nv.ptr(scales), L(vals.shape[0]),
+                _i32(slots), _i32(positions), _i32(pt), I(pt.stride(0)), I(ps), nv.ptr(logits), I(width), I(t), I(h),
+                I(d), I(tg), I(nsplit))
+    else:
+        nv.call("indexer_logits", nv.ptr(qc), nv.ptr(wf), nv.ptr(vals), nv.ptr(scales), _i32(slots), _i32(positions),
+                _i32(pt), I(pt.stride(0)), I(ps), nv.ptr(logits), I(width), I(t), I(h), I(d))
+    return logits
+
+
 def indexer_select(qc, wf, vals, scales, fb, ps: int, k: int):
     t, h, d = qc.shape
     idx = torch.empty(t, k, dtype=torch.int32, device=qc.device)
@@ -244,11 +272,21 @@ def indexer_select(qc, wf, vals, scales, fb, ps: int, k: int):
         nv.call("topk", nv.ptr(None), I(k), _i32(fb.positions), nv.ptr(idx), nv.ptr(out_len), I(t), I(k))
         return idx, out_len
     width = (n_max + 63) // 64 * 64
-    logits = torch.empty(t, width, dtype=torch.float32, device=qc.device)
+    # The workspace is t x width floats; at a million tokens of context a row is 1 MiB, so the rows are processed in
+    # chunks that keep it within LOGITS_WORKSPACE_BYTES (the reference bounds its workspace the same way,
+    # python/minisgl/kernel/deepseek_v4.py:883-927).
+    rows = max(1, min(t, LOGITS_WORKSPACE_BYTES // (width * 4)))
+    if rows >= 4:
+        rows -= rows % 4
     pt = fb.page_table
-    nv.call("indexer_logits", nv.ptr(qc), nv.ptr(wf), nv.ptr(vals), nv.ptr(scales), _i32(fb.slots),
-            _i32(fb.positions), _i32(pt), I(pt.stride(0)), I(ps), nv.ptr(logits), I(width), I(t), I(h), I(d))
-    nv.call("topk", nv.ptr(logits), I(width), _i32(fb.positions), nv.ptr(idx), nv.ptr(out_len), I(t), I(k))
+    logits = torch.empty(rows, width, dtype=torch.float32, device=qc.device)
+    for a in range(0, t, rows):
+        b = min(a + rows, t)
+        n = b - a
+        indexer_logits(qc[a:b], wf[a:b], vals, scales, fb.slots[a:b], fb.positions[a:b], pt, ps, width,
+                       fb.is_prefill, out=logits[:n])
+        nv.call("topk", nv.ptr(logits), I(width), _i32(fb.positions[a:b]), nv.ptr(idx[a:b]), nv.ptr(out_len[a:b]),
+                I(n), I(k))
     return idx, out_len
 
 

@@ -73,8 +73,12 @@ class SymmComm(Comm):
         self.state = torch.zeros(2 * self.channels, dtype=torch.int32, device=self.device)  # epochs, done counters
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
-        ptrs = list(self.handle.buffer_ptrs)
-        self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        off = int(getattr(self.handle, "offset", 0) or 0)     # of this tensor inside the rank's allocation block
+        ptrs = [int(p) + off for p in self.handle.buffer_ptrs]
+        if ptrs[self.rank] != self.buf.data_ptr():
+            raise RuntimeError("symmetric-memory handle does not describe the buffer it was made for")
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.mc_ptr = mc + off if mc else 0
         self.has_multicast = bool(self.mc_ptr)
         self.ctx = []
         for c in range(self.channels):
@@ -96,6 +100,16 @@ class SymmComm(Comm):
             self._enable_multimem(hidden, min(max_rows, 256))
         if _BIG and self.size > 1 and not _SKIP_EXCHANGE and max_rows >= 512:
             self._enable_big(hidden, max_rows)
+        from ..utils.logger import init_logger
+
+        init_logger(__name__).info_rank0(
+            "NVLink communicator: %d ranks, multicast mapping %s, in-switch reductions %s, block-wise prefill path %s",
+            self.size, "yes" if self.has_multicast else "no", "on" if self.multimem else "off",
+            "on" if self.big else "off")
+
+    @property
+    def mode(self) -> str:
+        return ("multimem" if self.multimem else "p2p") + ("+blockwise" if self.big else "")
 
     def _set_big(self, on: bool) -> None:
         self.big = on

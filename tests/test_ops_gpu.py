@@ -44,6 +44,33 @@ def test_embed_rmsnorm_silu_addcast():
     assert torch.equal(o, exp)
 
 
+def test_embed_token_feedback_and_greedy_tail():
+    """Decode rows take their token from the device-resident feedback buffer (embedding kernel gathers it and fills
+    the id buffer); the greedy tail is an argmax with lowest-index ties that also scatters the token back."""
+    w = bf(500, 4096, seed=40)
+    feedback = torch.randint(0, 500, (9,), dtype=torch.int32)
+    slots = torch.tensor([3, 0, 8, 8, 5], dtype=torch.int32)
+    ids = torch.full((5,), -1, dtype=torch.int32, device=DEV)
+    out = O.embed(ids, w.to(DEV), 4, feedback.to(DEV), slots.to(DEV))
+    want = feedback[slots.long()]
+    assert torch.equal(ids.cpu(), want) and torch.equal(out.cpu(), w[want.long()].unsqueeze(1).repeat(1, 4, 1))
+    g = torch.Generator().manual_seed(41)
+    logits = torch.randn(6, 129280 // 8, generator=g)
+    logits[2, 77] = logits[2, 4000] = 50.0                        # a tie: the lower index wins
+    logits[4] = float("-inf")
+    fb_dev = torch.full((9,), -7, dtype=torch.int32, device=DEV)
+    sl = torch.tensor([1, 2, 3, 4, 5, 6], dtype=torch.int32, device=DEV)
+    nvalid = torch.tensor([5], dtype=torch.int32, device=DEV)
+    toks = O.greedy_tokens(logits.to(DEV), 1000, sl, nvalid, fb_dev)
+    exp = logits.argmax(-1) + 1000
+    exp[2], exp[4] = 1077, 1000                                     # all -inf: the first column of the shard
+    assert toks.cpu().tolist() == exp.tolist()
+    assert fb_dev.cpu().tolist() == [-7] + exp[:5].tolist() + [-7, -7, -7]   # row 5 is padding: not fed back
+    cpu_fb = torch.full((9,), -7, dtype=torch.int32)
+    cpu = O.greedy_tokens(logits[:4], 1000, sl.cpu()[:4], None, cpu_fb)
+    assert cpu.tolist() == exp[:4].tolist() and cpu_fb.tolist()[1:5] == exp[:4].tolist()
+
+
 @pytest.mark.parametrize("block", [128, 64])
 def test_fp8_quant_matches_oracle(block):
     x = bf(33, 1024, std=2.0, seed=6)
@@ -97,7 +124,7 @@ def test_hc_pre_post_head():
 
 def _fb(pos, slots, page_table, out_loc=None, max_context=None):
     return types.SimpleNamespace(positions=pos, slots=slots, page_table=page_table, out_loc=out_loc,
-                                 max_context=max_context or int(pos.max()) + 1, num_valid=None)
+                                 max_context=max_context or int(pos.max()) + 1, num_valid=None, is_prefill=False)
 
 
 def _mk_batch(ps=256, seed=0):
@@ -202,6 +229,65 @@ def test_indexer_logits_and_topk():
                  cuda.nv.ptr(l1), cuda.I(2), cuda.I(512))
     assert o1[0].cpu().tolist() == list(range(100, 612))
     assert o1[1].cpu().tolist() == list(range(1536, 2048))
+
+
+@pytest.mark.parametrize("prefill", [False, True])
+def test_indexer_logits_tensor_core_kernel(prefill):
+    """The tcgen05 logits kernel against the fp32 oracle and against the CUDA-core kernel: a prefill chunk whose
+    rows run through two requests (groups of four rows share key tiles; one group straddles the request boundary)
+    and a decode batch (every row its own request), ragged lengths, -inf past every row's length, and the row
+    chunking that bounds the workspace."""
+    from minisgl.ops import cuda
+
+    ps = 256
+    g = torch.Generator().manual_seed(11)
+    pt = torch.zeros(4, 8192, dtype=torch.int32)
+    pages = torch.randperm(64, generator=g).tolist()
+    for s_ in range(2):
+        for k in range(32):
+            pg = pages[s_ * 32 + k]
+            pt[s_ + 1, k * ps:(k + 1) * ps] = torch.arange(pg * ps, (pg + 1) * ps, dtype=torch.int32)
+    if prefill:
+        pos = torch.cat([torch.arange(5000, 5041), torch.arange(0, 30), torch.arange(8100, 8105)]).to(torch.int32)
+        slots = torch.cat([torch.full((41,), 1), torch.full((30,), 2), torch.full((5,), 1)]).to(torch.int32)
+    else:
+        pos = torch.tensor([8191, 2, 3, 4095, 511, 512, 6000, 1023], dtype=torch.int32)
+        slots = torch.tensor([1, 2, 1, 2, 1, 2, 1, 2], dtype=torch.int32)
+    t = pos.shape[0]
+    qc = (torch.randn(t, 64, 128, generator=g) * 2).to(quant.FP8).view(torch.uint8)
+    wf = torch.randn(t, 64, generator=g)
+    vals = (torch.randn(64 * 64, 128, generator=g) * 2).to(quant.FP8).view(torch.uint8)
+    scales = torch.pow(2.0, torch.randint(-6, 3, (64 * 64,), generator=g).float())
+    width = 2048
+    a = [x.to(DEV) for x in (qc, wf, vals, scales, slots, pos, pt)]
+    mma = cuda.indexer_logits(*a, ps, width, prefill).cpu()
+    scalar = cuda.indexer_logits(*a, ps, width, prefill, force_scalar=True).cpu()
+    j = torch.arange(width)
+    n = ((pos.long() + 1) // 4).clamp(max=width)
+    rows = (pt[slots.long()][:, (4 * j + 3).clamp(max=8191)].long() // ps) * 64 + ((4 * j + 3) % ps)[None, :] // 4
+    want = ref.indexer_logits(qc, wf, vals, scales, rows, n)
+    valid = j[None, :] < n[:, None]
+    assert bool(torch.isinf(mma[~valid]).all()) and bool((mma[~valid] < 0).all())
+    # e4m3 products are exact; only the order of the fp32 additions differs between the three
+    scale = want[valid].abs().max()
+    assert float((mma[valid] - want[valid]).abs().max()) <= 2e-4 * float(scale)
+    assert float((mma[valid] - scalar[valid]).abs().max()) <= 2e-4 * float(scale)
+    # selection through the public op, with the workspace bound forcing three row chunks
+    fbd = _fb(a[5], a[4], a[6], None, 8192)
+    fbd.is_prefill = prefill
+    idx0, len0 = O.indexer_select(a[0], a[1], a[2], a[3], fbd, ps, 512)
+    old = cuda.LOGITS_WORKSPACE_BYTES
+    cuda.LOGITS_WORKSPACE_BYTES = width * 4 * max(t // 3, 1)
+    try:
+        idx1, len1 = O.indexer_select(a[0], a[1], a[2], a[3], fbd, ps, 512)
+    finally:
+        cuda.LOGITS_WORKSPACE_BYTES = old
+    assert torch.equal(idx0, idx1) and torch.equal(len0, len1)
+    fbc = _fb(pos, slots, pt, None, 8192)
+    idx_r, len_r = O.indexer_select(qc, wf, vals, scales, fbc, ps, 512)
+    assert torch.equal(len0.cpu(), len_r)
+    for r in range(t):
+        assert len(set(idx0[r].cpu().tolist()) ^ set(idx_r[r].tolist())) <= 4, r
 
 
 @pytest.mark.parametrize("heads", [8, 64])

@@ -130,6 +130,24 @@ def _checks():
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         assert float(lo) == float(hi)
+        # 2b) greedy sampling over vocabulary-parallel logits: per-shard argmax + in-kernel candidate exchange must
+        # give the argmax of the gathered row on every rank, ties to the lowest token id
+        vl = 4096 // world
+        gen = torch.Generator().manual_seed(99)
+        full = torch.randn(128, 4096, generator=gen)
+        full[5, 100] = full[5, 4000] = 60.0
+        shard = full[:, rank * vl:(rank + 1) * vl].contiguous().to(dev)
+        from minisgl.models.deepseek_v4 import GreedyTail
+
+        fbuf = torch.zeros(200, dtype=torch.int32, device=dev)
+        sl = torch.arange(128, dtype=torch.int32, device=dev)
+        for it in range(3):
+            toks = comm.greedy_tokens(shard, sl, None, GreedyTail(fbuf))
+            torch.cuda.synchronize()
+            want = full.argmax(-1)
+            want[5] = 100
+            assert toks.cpu().tolist() == want.tolist(), (it, (toks.cpu() != want).nonzero().flatten()[:5])
+            assert fbuf[:128].cpu().tolist() == want.tolist()
         # 3) whole model: tensor/expert parallel vs single rank
         # (600 prompt tokens: the prefill's collectives take the block-wise path, the decode steps the row-wise one)
         toks = torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist()
