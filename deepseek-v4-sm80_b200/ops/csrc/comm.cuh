@@ -433,6 +433,57 @@ inline int comm_big_grid(int rows) {
   return nblk < sms ? nblk : sms;
 }
 
+// ---------------------------------------------------------------- row-sharded (sequence-parallel) exchange
+// Between the two collectives of a block the layer can keep its activations sharded by rows: rank r owns the rows
+// [r * rows_per_rank, (r + 1) * rows_per_rank) (a multiple of 128, so that a 128-row GEMM tile has one owner).
+//   reduce-scatter: a producer (projection GEMM epilogue, MoE combine) stores each partial row straight into the
+//     OWNER's buffer rs[src rank][local row][col] over NVLink and, once a 128-row block is complete, raises
+//     flag[RS][src][local block] at the owner; the owner adds the `world` partials in rank order (sp.cu).
+//   all-gather: the owner pushes its finished rows (bf16, e4m3 and scales) into every rank's gathered buffer and
+//     raises flag[AG][owner][global block] everywhere; the consuming GEMM's TMA producer waits for the flag of its
+//     row block before it loads the block's A tiles (gemm_tcgen05.cu), weights streaming in the meantime.
+// These calls are issued eagerly (prefill), so the host numbers them: `seq` is a counter that all ranks advance
+// alike, flags carry it, and a waiter accepts any value >= its own.  All waits are bounded.
+constexpr int kSpSlots = 256;
+enum { kSpAG = 0, kSpRS = 1 };
+struct SpCtx {
+  uint8_t* peer[kMaxRanks];
+  uint8_t* mc;            // multicast mapping (null: plain peer stores)
+  int rank, world;
+  int rows_per_rank;      // multiple of 128
+  int hidden;
+  long long flags_off;    // uint32 [2 kinds][kMaxRanks writers][kSpSlots]
+  long long ag_off;       // gathered rows of this channel: bf16 [tpad, hidden] | u8 [tpad, hidden] | f32 [tpad, hidden/128]
+  long long rs_off;       // partial rows of this channel: bf16 [world][rows_per_rank][hidden]
+  unsigned int seq;
+  int use_mc;             // 1: pushes and flags go through multimem.st
+};
+static_assert(sizeof(SpCtx) == 120, "the Python side mirrors this struct field by field");
+__device__ __forceinline__ uint32_t* sp_flag(const SpCtx& c, int on_rank, int kind, int writer, int slot) {
+  return reinterpret_cast<uint32_t*>(c.peer[on_rank] + c.flags_off) + ((size_t)kind * kMaxRanks + writer) * kSpSlots +
+         slot;
+}
+__device__ __forceinline__ uint32_t* sp_mc_flag(const SpCtx& c, int kind, int writer, int slot) {
+  return reinterpret_cast<uint32_t*>(c.mc + c.flags_off) + ((size_t)kind * kMaxRanks + writer) * kSpSlots + slot;
+}
+// Bounded wait on ONE local flag word (any value >= seq passes).  Called by one thread.
+__device__ __forceinline__ bool sp_wait_flag(const uint32_t* f, uint32_t seq, int who, int slot) {
+  unsigned long long t0 = 0;
+  for (int spin = 0;; ++spin) {
+    if ((int)(ld_relaxed_sys(f) - seq) >= 0) break;
+    if ((spin & 63) == 63) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        dsv4_set_error(DSV4_ERR_PEER_TIMEOUT, who, slot);
+        return false;
+      }
+    }
+  }
+  __threadfence_system();
+  return true;
+}
+
 // Last CTA of the grid advances the channel epoch (call once per CTA, by one thread, at the very end).
 __device__ __forceinline__ void comm_finish(const CommCtx& c, int total_ctas) {
   __threadfence();

@@ -52,6 +52,13 @@ struct GemmArgs {
                        //      shared memory (no workspace, no atomics)
   long long partial_stride;  // > 0: split s writes its own partial product to out + s * partial_stride (no reduction;
                              //      the consumer kernel sums the splits in order)
+  // Row-sharded exchange (comm.cuh, "row-sharded"): sp_mode 1 = the A operand is the gathered buffer: the TMA
+  // producer waits for the flag of its 128-row block (raised by the block's owner) before loading A tiles;
+  // sp_mode 2 = reduce-scatter epilogue: every partial row goes to its owner's buffer over NVLink and the last
+  // column tile of a row block raises the block's flag at the owner.
+  int sp_mode;
+  int* sp_counters;          // [row blocks], zero between launches (sp_mode 2)
+  SpCtx sp;
 };
 
 __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const float* v, int ncols_valid) {
@@ -164,7 +171,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0) {
     if (lane == 0) {
       const int ax = batch * g.a_col_pb, by = batch * g.b_row_pb + n0;
-      for (int i = 0; i < nkt; ++i) {
+      bool gate_ok = true;
+      if (g.sp_mode == 1) {
+        // all-gather fused into the load: the rows of this tile were pushed into the local gathered buffer by their
+        // owner; wait for the owner's flag, then make its (generic-proxy) writes visible to the TMA reads
+        const int owner = m0 / g.sp.rows_per_rank;
+        if (owner != g.sp.rank)
+          gate_ok = sp_wait_flag(sp_flag(g.sp, g.sp.rank, kSpAG, owner, m0 >> 7), g.sp.seq, owner, m0 >> 7);
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        if (!gate_ok) *abort_flag = 1;
+      }
+      for (int i = 0; i < nkt && gate_ok; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
         uint8_t* a = tiles + s * Cfg::kStageBytes;
@@ -304,6 +321,31 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (warp == 2 && lane == 0) g.counters[tile] = 0;
       }
     }
+    if (g.sp_mode == 2) {
+      if constexpr (sizeof(OutT) == 2) {
+        const int rpr = g.sp.rows_per_rank;
+        const int owner = m0 / rpr;                 // a 128-row tile has one owner (rpr is a multiple of 128)
+        if (write_out && grow < M) {
+          OutT* dst0 = reinterpret_cast<OutT*>(g.sp.peer[owner] + g.sp.rs_off) +
+                       ((size_t)g.sp.rank * rpr + (grow - owner * rpr)) * N;
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = n0 + c * 32;
+            if (col < N) store_row_chunk(dst0 + col, &acc[c * 32], N - col);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          __threadfence_system();
+          if (atomicAdd(&g.sp_counters[blockIdx.y], 1) == (int)gridDim.x - 1) {
+            g.sp_counters[blockIdx.y] = 0;
+            __threadfence_system();
+            st_relaxed_sys(sp_flag(g.sp, owner, kSpRS, g.sp.rank, (m0 - owner * rpr) >> 7), g.sp.seq);
+          }
+        }
+      }
+      write_out = false;
+    }
     if (write_out && grow < M) {
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
@@ -401,6 +443,9 @@ struct LaunchOpts {
   int a_cols = 0, b_rows = 0;  // full extents of the operands (0 = K / N)
   int sb_ld = 0;
   const CommCtx* comm = nullptr;
+  int sp_mode = 0;
+  const SpCtx* sp = nullptr;
+  int* sp_counters = nullptr;
 };
 
 int g_weight_prefetch = 0;  // set by dsv4_gemm_set_weight_prefetch
@@ -431,7 +476,10 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
     if (!o.deposit_only && (long long)grid.x * grid.y > kCommSlots) return 104;
   }
   GemmArgs g{M, N, K, ldo, sa, sb, o.sb_ld ? o.sb_ld : (K + 127) / 128, accumulate_out, o.a_col_pb, o.b_row_pb,
-             o.out_col_pb, o.splits, o.ws, o.counters, o.deposit_only, g_weight_prefetch, o.cluster, o.partial_stride};
+             o.out_col_pb, o.splits, o.ws, o.counters, o.deposit_only, g_weight_prefetch, o.cluster, o.partial_stride,
+             o.sp_mode, o.sp_counters, o.sp ? *o.sp : SpCtx{}};
+  if (o.sp_mode && (!o.sp || o.sp->rows_per_rank % kBM || o.batches != 1)) return 106;
+  if (o.sp_mode == 2 && (o.splits != 1 || !o.sp_counters)) return 107;
   if (o.cluster) {
     if (o.splits != 2 && o.splits != 4 && o.splits != 8) return 105;
     dsv4_launch_cluster(kern, grid, 192, Cfg::kSmemBytes, stream, o.splits, tmA, tmB, out, g, comm);
@@ -534,6 +582,43 @@ DSV4_API int dsv4_gemm_fp8(const void* x, const void* w, void* out, const float*
     return dispatch_bn<true, float>(x, w, (float*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn, stream, o);
   return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, sa, sb, accumulate_out, bn,
                                           stream, o);
+}
+
+// Row-sharded exchange, consumer side ("all-gather -> projection"): x / sa are this rank's gathered buffer; the
+// producer warp of every CTA waits for the owner's flag of its 128-row block before it loads the block's A tiles.
+// partials != 0: split-K partial products like dsv4_gemm_bf16_partials (bf16 operands only).
+DSV4_API int dsv4_gemm_fp8_gated(const void* x, const void* w, void* out, const float* sa, const float* sb, int M, int N,
+                                 int K, int ldx, int ldw, int ldo, int bn, const SpCtx* sp, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 128) || (ldx % 16) || (ldw % 16)) return 111;
+  LaunchOpts o;
+  o.sp_mode = 1;
+  o.sp = sp;
+  return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, sa, sb, 0, bn, stream, o);
+}
+DSV4_API int dsv4_gemm_bf16_partials_gated(const void* x, const void* w, float* out, int M, int N, int K, int ldx,
+                                           int ldw, int ldo, int bn, int splits, long long split_stride,
+                                           const SpCtx* sp, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 8) || (ldx % 8) || (ldw % 8) || splits < 1 || split_stride < (long long)M * ldo) return 118;
+  LaunchOpts o;
+  o.splits = splits;
+  o.partial_stride = split_stride;
+  o.sp_mode = 1;
+  o.sp = sp;
+  return dispatch_bn<false, float>(x, w, out, M, N, K, ldx, ldw, ldo, nullptr, nullptr, 0, bn ? bn : 32, stream, o);
+}
+// Row-sharded exchange, producer side ("projection -> reduce-scatter"): the epilogue stores every partial row into its
+// owner's buffer over NVLink; dsv4_sp_rs_reduce on the owner adds the partials.  counters: >= ceil(M / 128) zero ints.
+DSV4_API int dsv4_gemm_fp8_rs(const void* x, const void* w, const float* sa, const float* sb, int M, int N, int K,
+                              int ldx, int ldw, int bn, const SpCtx* sp, int* counters, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K % 128) || (ldx % 16) || (ldw % 16) || (N % 8) || N != sp->hidden) return 112;
+  LaunchOpts o;
+  o.sp_mode = 2;
+  o.sp = sp;
+  o.sp_counters = counters;
+  return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, M, N, K, ldx, ldw, N, sa, sb, 0, bn, stream, o);
 }
 
 // Fused projection + all-reduce: every rank multiplies its K-shard, the epilogue publishes the partial tile to the

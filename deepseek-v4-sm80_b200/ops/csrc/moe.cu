@@ -728,6 +728,55 @@ __global__ void __launch_bounds__(256) moe_finalize_ar_kernel(const __nv_bfloat1
   if (threadIdx.x == 0) comm_finish(comm, gridDim.x);
 }
 
+// Combine with a reduce-scatter instead of an all-reduce (row-sharded layer, comm.cuh): CTA t sums the local routes of
+// token t (+ the shared expert) like moe_finalize_kernel and stores the partial row straight into the buffer of the
+// rank that owns row t; the last row of a 128-row block raises the block's flag at the owner, whose
+// sp_rs_reduce_kernel adds the ranks' partials (and applies the hyper-connection post mix).
+__global__ void __launch_bounds__(256) moe_finalize_rs_kernel(const __nv_bfloat16* __restrict__ yr,
+                                                              const int* __restrict__ route_pos,
+                                                              const __nv_bfloat16* __restrict__ shared, int topk, int h,
+                                                              int t_rows, const SpCtx sp, int* __restrict__ counters) {
+  pdl_entry();
+  const int t = blockIdx.x;
+  const int rpr = sp.rows_per_rank, owner = t / rpr, blk = t >> 7;
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(sp.peer[owner] + sp.rs_off) +
+                       ((size_t)sp.rank * rpr + (t - owner * rpr)) * h;
+  for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < topk; ++k) {
+      if (route_pos[t * topk + k] < 0) continue;
+      const uint4 u = *reinterpret_cast<const uint4*>(yr + ((size_t)t * topk + k) * h + i);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p[j]);
+        acc[2 * j] += f.x, acc[2 * j + 1] += f.y;
+      }
+    }
+    const uint4 su = *reinterpret_cast<const uint4*>(shared + (size_t)t * h + i);
+    const __nv_bfloat162* spv = reinterpret_cast<const __nv_bfloat162*>(&su);
+    uint4 o;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 r2 = __bfloat1622float2(__floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]));
+      const float2 s2 = __bfloat1622float2(spv[j]);
+      po[j] = __floats2bfloat162_rn(r2.x + s2.x, r2.y + s2.y);
+    }
+    st_peer16(dst + i, o);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const int rows_in_blk = min(128, t_rows - blk * 128);
+    if (atomicAdd(&counters[blk], 1) == rows_in_blk - 1) {
+      counters[blk] = 0;
+      __threadfence_system();
+      st_relaxed_sys(sp_flag(sp, owner, kSpRS, sp.rank, (blk * 128 - owner * rpr) >> 7), sp.seq);
+    }
+  }
+}
+
 template <int MODE, int NT>
 int launch_moe_gemm(const void* w, const uint8_t* scales, const void* x, int x_rows, const PlanHeader* hdr,
                     const int* tiles, const int* sorted_route, const float* sorted_w, void* out, int e_local, int K,
@@ -817,6 +866,18 @@ DSV4_API int dsv4_moe_finalize(const void* yr, const int* plan, int routes, int 
   dsv4_launch(moe_finalize_kernel, t, 256, 0, st, (const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
               (__nv_bfloat16*)out, num_valid, topk, h,
               HcPostArgs{xout ? (const __nv_bfloat16*)res : nullptr, post, comb, (__nv_bfloat16*)xout});
+  return (int)cudaGetLastError();
+}
+
+// Combine + reduce-scatter (see moe_finalize_rs_kernel).  counters: >= ceil(t / 128) zero ints.  dsv4_sp_rs_reduce on
+// every rank must follow.
+DSV4_API int dsv4_moe_finalize_rs(const void* yr, const int* plan, int routes, int max_tiles, const void* shared, int t,
+                                  int topk, int h, const SpCtx* sp, int* counters, cudaStream_t st) {
+  if (t <= 0) return 0;
+  if (h % 8 || h != sp->hidden || sp->rows_per_rank % 128 || !shared) return 232;
+  const int* route_pos = plan + 4 + 3 * max_tiles + routes;
+  dsv4_launch(moe_finalize_rs_kernel, t, 256, 0, st, (const __nv_bfloat16*)yr, route_pos, (const __nv_bfloat16*)shared,
+              topk, h, t, *sp, counters);
   return (int)cudaGetLastError();
 }
 

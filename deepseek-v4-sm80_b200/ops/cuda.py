@@ -276,15 +276,15 @@ def indexer_select(qc, wf, vals, scales, fb, ps: int, k: int):
     # chunks that keep it within LOGITS_WORKSPACE_BYTES (the reference bounds its workspace the same way,
     # python/minisgl/kernel/deepseek_v4.py:883-927).
     rows = max(1, min(t, LOGITS_WORKSPACE_BYTES // (width * 4)))
-    if rows >= 4:
-        rows -= rows % 4
+    if 4 <= rows < t:
+        rows -= rows % 4        # whole groups of four rows per chunk
     pt = fb.page_table
     logits = torch.empty(rows, width, dtype=torch.float32, device=qc.device)
     for a in range(0, t, rows):
         b = min(a + rows, t)
         n = b - a
         indexer_logits(qc[a:b], wf[a:b], vals, scales, fb.slots[a:b], fb.positions[a:b], pt, ps, width,
-                       fb.is_prefill, out=logits[:n])
+                       bool(getattr(fb, "is_prefill", False)), out=logits[:n])
         nv.call("topk", nv.ptr(logits), I(width), _i32(fb.positions[a:b]), nv.ptr(idx[a:b]), nv.ptr(out_len[a:b]),
                 I(n), I(k))
     return idx, out_len
