@@ -125,9 +125,12 @@ class DSV4Model:
             xq = O.fp8_quant(x)
         return O.gemm_fp8(xq[0], xq[1], self.w[name + ".weight"], self.w[name + ".scale"])
 
-    def attention(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None, hc=None) -> torch.Tensor:
+    def attention(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None, hc=None, sp=None) -> torch.Tensor:
         """hc = (residual, post, comb): when the communicator can fuse the hyper-connection post mix behind its
-        reduction, the new residual streams are returned instead of the block output (flagged by ``self._mixed``)."""
+        reduction, the new residual streams are returned instead of the block output (flagged by ``self._mixed``).
+        sp = (plan, gate): row-sharded layer.  y / yq are this rank's gathered buffer, whose rows arrive from their
+        owners while the first projection runs (its loads wait per row block, ``gate``); the output projection is
+        reduce-scattered and hc holds the own rows only."""
         cfg, w, p = self.cfg, self.w, f"L{l}.attn."
         t = y.shape[0]
         rope = self.ropes[l]
@@ -137,6 +140,12 @@ class DSV4Model:
         if yq is None:
             yq = O.fp8_quant(y)
         iw = None
+        qkv = None
+        if sp is not None:
+            # the all-gather is fused into this GEMM's loads; everything else that reads y is issued behind it
+            from ..ops.gemm import gemm_fp8_gated
+
+            qkv = gemm_fp8_gated(yq[0], yq[1], w[p + "wqkv_a.weight"], w[p + "wqkv_a.scale"], sp[1])
         if ratio:
             # compressor (and indexer cache) branch: depends only on y, meets the query chain at the selection
             with self._fork(y):
@@ -154,7 +163,8 @@ class DSV4Model:
                 pooled = O.compress(proj, fb, ratio, cfg.head_dim, w[p + "comp.ape"], kvv["ring"], kvv.get("ckpt"),
                                     ps)
                 O.compress_store(pooled, fb, w[p + "comp.norm"], cfg.rms_norm_eps, rope, kvv["comp"], ps, ratio)
-        qkv = O.gemm_fp8(yq[0], yq[1], w[p + "wqkv_a.weight"], w[p + "wqkv_a.scale"])
+        if qkv is None:
+            qkv = O.gemm_fp8(yq[0], yq[1], w[p + "wqkv_a.weight"], w[p + "wqkv_a.scale"])
         q_lora, qlq = O.rms_norm(qkv[:, : cfg.q_lora_rank], w[p + "q_norm.weight"], cfg.rms_norm_eps, want_q=True)
         kv = qkv[:, cfg.q_lora_rank:]
         q = O.gemm_fp8(qlq[0], qlq[1], w[p + "wq_b.weight"], w[p + "wq_b.scale"]).view(t, self.h_local, cfg.head_dim)
@@ -175,6 +185,11 @@ class DSV4Model:
         o = O.attention(q, fb, kvv["swa"], self.pool.swa_map, kvv.get("comp"), ratio, topk_idx, topk_len,
                         w[p + "sink"], cfg.head_dim ** -0.5, ps, cfg.window_size, out_rope=rope)
         o2 = O.gemm_bf16_grouped(o.reshape(t, self.h_local * cfg.head_dim), w[p + "wo_a.weight_bf16"], self.g_local)
+        if sp is not None:
+            oq = O.fp8_quant(o2)
+            self._mixed = True
+            return self.comm.sp_gemm_fp8_reduce_scatter(sp[0], self.comm.CH_ATTN, oq[0], oq[1], w[p + "wo_b.weight"],
+                                                        w[p + "wo_b.scale"], hc=hc)
         if getattr(self.comm, "fused", False):
             oq = O.fp8_quant(o2)
             self._mixed = hc is not None
@@ -182,18 +197,30 @@ class DSV4Model:
         out = self._fp8_linear(o2, p + "wo_b")
         return self.comm.all_reduce(out, "attn")
 
-    def moe(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None, hc=None) -> torch.Tensor:
+    def moe(self, l: int, y: torch.Tensor, fb: ForwardBatch, yq=None, hc=None, sp=None) -> torch.Tensor:
         cfg, w, p = self.cfg, self.w, f"L{l}.moe."
         if yq is None:
             yq = O.fp8_quant(y)
-        with self._fork(y):  # shared expert beside the router / planning chain
-            gu = O.gemm_fp8(yq[0], yq[1], w[p + "sh_gate_up.weight"], w[p + "sh_gate_up.scale"])
-            aq = O.silu_mul_clamp_quant(gu, cfg.swiglu_limit)
-            shared = O.gemm_fp8(aq[0], aq[1], w[p + "sh_down.weight"], w[p + "sh_down.scale"])
         gate_w = w[p + "gate.weight_bf16"] if y.is_cuda and (p + "gate.weight_bf16") in w else w[p + "gate.weight"]
-        idx, wt = O.moe_gate(y, gate_w, w.get(p + "gate.bias"), cfg.num_experts_per_tok,
-                             cfg.routed_scaling_factor, cfg.scoring_func, w.get(p + "gate.tid2eid"), fb.input_ids,
-                             fb.num_valid)
+
+        def shared_expert():
+            with self._fork(y):  # beside the router / planning chain
+                gu = O.gemm_fp8(yq[0], yq[1], w[p + "sh_gate_up.weight"], w[p + "sh_gate_up.scale"])
+                aq = O.silu_mul_clamp_quant(gu, cfg.swiglu_limit)
+                return O.gemm_fp8(aq[0], aq[1], w[p + "sh_down.weight"], w[p + "sh_down.scale"])
+
+        def router(gate=None):
+            return O.moe_gate(y, gate_w, w.get(p + "gate.bias"), cfg.num_experts_per_tok,
+                              cfg.routed_scaling_factor, cfg.scoring_func, w.get(p + "gate.tid2eid"), fb.input_ids,
+                              fb.num_valid, **({"gate": gate} if gate is not None else {}))
+
+        if sp is not None:
+            # row-sharded layer: the router GEMM's loads wait for the gathered rows; the shared expert follows it
+            idx, wt = router(sp[1])
+            shared = shared_expert()
+        else:
+            shared = shared_expert()
+            idx, wt = router()
         if self._debug_bounds:
             O.check_index(idx, -1, cfg.n_routed_experts, "expert_ids")
         if y.is_cuda:
@@ -205,6 +232,9 @@ class DSV4Model:
                                           cfg.swiglu_limit, self.expert_base)
             t, k, h = y.shape[0], idx.shape[1], y.shape[1]
             self._join(y)
+            if sp is not None:
+                self._mixed = True
+                return self.comm.sp_moe_finalize_reduce_scatter(sp[0], rows, plan, mt, shared, t, k, h, hc=hc)
             if getattr(self.comm, "fused", False):
                 self._mixed = hc is not None
                 return self.comm.moe_finalize_allreduce(rows, plan, mt, shared, fb.num_valid, t, k, h, hc=hc)
@@ -228,6 +258,45 @@ class DSV4Model:
             y = fn(l, y, fb, yq, (x, post, comb))
             x = y if self._mixed else O.hc_post(y, x, post, comb)
         return x
+
+    def layer_sp(self, l: int, x_own: torch.Tensor, fb: ForwardBatch, plan) -> torch.Tensor:
+        """One layer with the residual streams sharded by rows (x_own = this rank's rows [n_own, 4, H]).  Per block:
+        hyper-connection pre mix, norm and FP8 quantisation on the own rows only, written into the rank's rows of the
+        gathered buffer; all-gather push; the block on all rows (heads / experts sharded as always), whose first GEMM
+        consumes the gathered rows as they arrive and whose last kernel reduce-scatters; hyper-connection post mix
+        on the own rows, fused behind the reduction."""
+        cfg, w, p, c = self.cfg, self.w, f"L{l}.", self.comm
+        t, r0, n = plan.t, plan.row0, plan.n_own
+        for blk, fn, norm, ch in (("hc_attn", self.attention, "attn_norm", c.CH_ATTN),
+                                  ("hc_ffn", self.moe, "ffn_norm", c.CH_MOE)):
+            ag_y, ag_q, ag_s = c.sp_buffers(plan, ch)
+            _, post, comb, _ = O.hc_pre(x_own, w[p + blk + ".fn"], w[p + blk + ".scale"], w[p + blk + ".base"],
+                                        cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps, w[p + norm + ".weight"],
+                                        want_q=True, out=(ag_y[r0:r0 + n], ag_q[r0:r0 + n], ag_s[r0:r0 + n]))
+            gate = c.sp_all_gather(plan, ch)
+            x_own = fn(l, ag_y[:t], fb, (ag_q[:t], ag_s[:t]), (x_own, post, comb), sp=(plan, gate))
+        return x_own
+
+    def _forward_sp(self, fb: ForwardBatch, plan, greedy):
+        cfg, w, c = self.cfg, self.w, self.comm
+        r0, n = plan.row0, plan.n_own
+        x_own = O.embed(fb.input_ids[r0:r0 + n], w["embed.weight"], cfg.hc_mult)
+        for l in range(cfg.num_layers):
+            x_own = self.layer_sp(l, x_own, fb, plan)
+        # the rows whose logits are wanted live on their owners: every rank contributes its own ones, zeros elsewhere
+        last = fb.last_idx if fb.last_idx is not None else torch.arange(plan.t, device=x_own.device)
+        b, h = last.shape[0], cfg.hidden_size
+        mine = (last >= r0) & (last < r0 + n)
+        sel = torch.zeros(b, cfg.hc_mult, h, dtype=x_own.dtype, device=x_own.device)
+        if n > 0:
+            sel[mine] = x_own[(last[mine] - r0)]
+        x = c.all_reduce(sel.view(b * cfg.hc_mult, h)).view(b, cfg.hc_mult, h)
+        y = O.hc_head(x, w["hc_head.fn"], w["hc_head.scale"], w["hc_head.base"], cfg.hc_eps, cfg.rms_norm_eps,
+                      w["norm.weight"])
+        logits = O.gemm_bf16(y, w["head.weight"], out_dtype=torch.float32)
+        if greedy is not None:
+            return logits, c.greedy_tokens(logits, fb.slots[last], None, greedy)
+        return c.all_gather_last(logits)
 
     # ------------------------------------------------------------------ forward
     def prepare_report(self) -> dict:
@@ -276,6 +345,10 @@ class DSV4Model:
         cfg, w = self.cfg, self.w
         if self._debug_bounds and fb.token_feedback is None:
             self.audit_inputs(fb)
+        if fb.is_prefill and fb.input_ids.is_cuda and hasattr(self.comm, "sp_plan") and self.moe_mode == "ep":
+            plan = self.comm.sp_plan(fb.input_ids.shape[0])
+            if plan is not None:
+                return self._forward_sp(fb, plan, greedy)
         x = O.embed(fb.input_ids, w["embed.weight"], cfg.hc_mult, fb.token_feedback,
                     fb.slots if fb.token_feedback is not None else None)
         if self._debug_bounds and fb.token_feedback is not None:

@@ -146,11 +146,12 @@ def q_kv_norm_rope_store(q, kv, positions, kv_w, eps, spec, swa_cache, out_loc, 
 
 
 # --------------------------------------------------------------------------- hyper-connections
-def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None, want_q: bool = False):
+def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None, want_q: bool = False, out=None):
     """Returns (y, post, comb); with ``norm_w`` y is additionally RMS-normalised (fused on CUDA); with ``want_q``
-    a fourth item, the (e4m3, scales) quantisation of y (also fused on CUDA)."""
+    a fourth item, the (e4m3, scales) quantisation of y (also fused on CUDA).  ``out`` (CUDA only): result rows
+    (y, q, s) to write into."""
     if x.is_cuda:
-        return _cu().hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w, want_q)
+        return _cu().hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w, want_q, out)
     y, post, comb = ref.hc_pre(x, fn, scale, base, iters, eps, norm_eps)
     if norm_w is not None:
         y = ref.rms_norm(y, norm_w, norm_eps)
@@ -237,9 +238,9 @@ def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_
 
 
 # --------------------------------------------------------------------------- MoE
-def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid=None):
+def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid=None, gate=None):
     if y.is_cuda:
-        return _cu().moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid)
+        return _cu().moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid, gate)
     idx, w = ref.moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids)
     if num_valid is not None:
         idx[int(num_valid):] = -1

@@ -163,11 +163,16 @@ def _hc_mixes(x, fn):
     return gemm_bf16_partials(x.reshape(t, -1), fn)
 
 
-def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None, want_q: bool = False):
+def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None, want_q: bool = False, out=None):
+    """out = (y, q, s): preallocated result rows (the row-sharded layer passes its rows of the gathered buffer)."""
     t, m, h = x.shape
     assert m == 4 and x.is_contiguous()
-    y = torch.empty(t, h, dtype=x.dtype, device=x.device)
-    q, s = _quant_out(t, h, x.device, want_q)
+    if out is not None:
+        y, q, s = out
+        assert y.shape == (t, h) and y.is_contiguous() and q.is_contiguous() and s.is_contiguous() and h % 256 == 0
+    else:
+        y = torch.empty(t, h, dtype=x.dtype, device=x.device)
+        q, s = _quant_out(t, h, x.device, want_q)
     post = torch.empty(t, m, dtype=torch.float32, device=x.device)
     comb = torch.empty(t, m, m, dtype=torch.float32, device=x.device)
     mixes = _hc_mixes(x, fn)
@@ -314,14 +319,15 @@ _NO_ROPE = RopeSpec.make(64, 10000.0, 0, 1.0, 32, 1)
 _SCORING = {"sqrtsoftplus": 0, "sigmoid": 1, "softmax": 2}
 
 
-def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid=None):
+def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_valid=None, gate=None):
+    """gate: row-sharded exchange context; the router GEMM then waits for each row block's all-gather flag."""
     from .gemm import gemm_bf16_partials
 
     # the router weight is bf16 in the checkpoint (its fp32 copy converts back losslessly); the model passes the bf16
     # tensor it keeps next to the fp32 one.  No cache keyed by address here: a later model may reuse the address.
     wb = gate_w if gate_w.dtype == torch.bfloat16 else gate_w.to(torch.bfloat16)
     t, e = y.shape[0], gate_w.shape[0]
-    scores = gemm_bf16_partials(y, wb)  # [S, T, E]; the selection kernel adds the splits
+    scores = gemm_bf16_partials(y, wb, gate=gate)  # [S, T, E]; the selection kernel adds the splits
     idx = torch.empty(t, topk, dtype=torch.int32, device=y.device)
     wts = torch.empty(t, topk, dtype=torch.float32, device=y.device)
     nv.call("moe_topk", nv.ptr(scores), nv.ptr(bias if tid2eid is None else None), nv.ptr(tid2eid),

@@ -114,9 +114,10 @@ def gemm_bf16(x, w, out=None, out_dtype=torch.bfloat16, accumulate=False, bn=0, 
     return out
 
 
-def gemm_bf16_partials(x, w, splits: int = 0):
+def gemm_bf16_partials(x, w, splits: int = 0, gate=None):
     """Split-K bf16 GEMM that leaves the reduction to its consumer: returns fp32 [splits, M, N] with
-    sum(0) == x @ w^T.  A split whose K range is empty writes zeros."""
+    sum(0) == x @ w^T.  A split whose K range is empty writes zeros.  gate (a row-sharded exchange context): x is
+    the gathered buffer and every CTA waits for its row block's all-gather flag before loading it."""
     x2 = _as2d(x)
     m, k = x2.shape
     n = w.shape[0]
@@ -130,8 +131,24 @@ def gemm_bf16_partials(x, w, splits: int = 0):
         return torch.stack([xf[:, s * per:(s + 1) * per] @ wf[:, s * per:(s + 1) * per].t() for s in range(splits)])
     assert x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x2.stride(-1) == 1 and w.stride(-1) == 1
     out = torch.empty(splits, m, n, dtype=torch.float32, device=x.device)
+    if gate is not None:
+        nv.call("gemm_bf16_partials_gated", nv.ptr(x2), nv.ptr(w), nv.ptr(out), I(m), I(n), I(k), I(x2.stride(0)),
+                I(w.stride(0)), I(n), I(32), I(splits), L(m * n), ctypes.byref(gate))
+        return out
     nv.call("gemm_bf16_partials", nv.ptr(x2), nv.ptr(w), nv.ptr(out), I(m), I(n), I(k), I(x2.stride(0)),
             I(w.stride(0)), I(n), I(32), I(splits), L(m * n))
+    return out
+
+
+def gemm_fp8_gated(xq, sx, wq, sw, gate):
+    """``gemm_fp8`` whose activation operand is the gathered buffer of a row-sharded exchange: the all-gather is
+    fused into the A-tile loads (each CTA waits for its row block's flag, weights stream meanwhile)."""
+    m, k = xq.shape
+    n = wq.shape[0]
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=xq.device)
+    bn, _ = pick_tiling(m, n, k // 128, 1, True, 0, 1)
+    nv.call("gemm_fp8_gated", nv.ptr(xq), nv.ptr(wq), nv.ptr(out), nv.ptr(sx), nv.ptr(sw), I(m), I(n), I(k),
+            I(xq.stride(0)), I(wq.stride(0)), I(n), I(bn), ctypes.byref(gate))
     return out
 
 

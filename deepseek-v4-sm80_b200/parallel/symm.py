@@ -43,6 +43,27 @@ class CommCtx(ctypes.Structure):
                 ("mc", ctypes.c_void_p), ("mm", ctypes.c_int), ("pad_", ctypes.c_int)]
 
 
+class SpCtx(ctypes.Structure):
+    """Mirror of the native SpCtx (csrc/comm.cuh): one row-sharded exchange on one channel."""
+
+    _fields_ = [("peer", ctypes.c_void_p * MAX_RANKS), ("mc", ctypes.c_void_p), ("rank", ctypes.c_int),
+                ("world", ctypes.c_int), ("rows_per_rank", ctypes.c_int), ("hidden", ctypes.c_int),
+                ("flags_off", ctypes.c_longlong), ("ag_off", ctypes.c_longlong), ("rs_off", ctypes.c_longlong),
+                ("seq", ctypes.c_uint), ("use_mc", ctypes.c_int)]
+
+
+class SpPlan:
+    """Row ownership of one forward of ``t`` rows: rank r owns rows [r * rpr, (r + 1) * rpr) with rpr a multiple of
+    128 (the GEMM row tile), ``tpad = world * rpr``; ``row0`` / ``n_own`` describe this rank's valid rows."""
+
+    def __init__(self, t: int, rank: int, world: int):
+        self.t = t
+        self.rpr = -(-(-(-t // world)) // 128) * 128
+        self.tpad = self.rpr * world
+        self.row0 = min(rank * self.rpr, t)
+        self.n_own = max(min(t - rank * self.rpr, self.rpr), 0)
+
+
 class SymmComm(Comm):
     fused = True
     CH_ATTN, CH_MOE, CH_GENERIC = 0, 1, 2
@@ -63,10 +84,22 @@ class SymmComm(Comm):
         assert mr.value == MAX_RANKS
         assert lib.dsv4_comm_ctx_size() == ctypes.sizeof(CommCtx), "CommCtx layout differs from the native library's"
         self.flags_bytes, self.channels, self.slots = fb.value, ch.value, sl.value
-        self.data_bytes = (max_rows * hidden * 2 + 255) // 256 * 256
+        # row-sharded exchange: rows are padded to world x (a multiple of 128)
+        self.hidden = hidden
+        self.sp_tpad_max = SpPlan(max_rows, 0, self.size).tpad
+        assert lib.dsv4_sp_ctx_size() == ctypes.sizeof(SpCtx), "SpCtx layout differs from the native library's"
+        self.sp_slots = lib.dsv4_sp_slots()
+        self.data_bytes = (self.sp_tpad_max * hidden * 2 + 255) // 256 * 256
         # result buffers of the two-shot path (row counts of a decode batch): the owner of a row writes its sum here
         self.small_bytes = (min(max_rows, 256) * hidden * 2 + 255) // 256 * 256
         total = self.flags_bytes + self.channels * 2 * self.data_bytes + self.channels * 2 * self.small_bytes
+        # appended for the row-sharded exchange: flag words, then one gathered buffer (bf16 rows | e4m3 rows | scales)
+        # per layer block kind
+        self.sp_flags_off = total
+        total += (2 * MAX_RANKS * self.sp_slots * 4 + 255) // 256 * 256
+        self.sp_ag_bytes = (self.sp_tpad_max * (3 * hidden + hidden // 128 * 4) + 255) // 256 * 256
+        self.sp_ag_off = [total, total + self.sp_ag_bytes]
+        total += 2 * self.sp_ag_bytes
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self.handle = symm_mem.rendezvous(self.buf, self.group)
         self.buf.zero_()
@@ -91,7 +124,15 @@ class SymmComm(Comm):
             x.done = self.state.data_ptr() + 4 * self.channels
             x.mc, x.mm = self.mc_ptr or None, 0
             self.ctx.append(x)
-        self.counters = {"all_reduce": 0, "gemm_allreduce": 0, "moe_allreduce": 0, "all_gather": 0}
+        self.counters = {"all_reduce": 0, "gemm_allreduce": 0, "moe_allreduce": 0, "all_gather": 0,
+                         "sp_all_gather": 0, "sp_reduce_scatter": 0}
+        self._ptrs = ptrs
+        self.sp_seq = 0
+        self.sp_counters = torch.zeros(2 * self.sp_slots, dtype=torch.int32, device=self.device)
+        # rows at or above this count run the layer row-sharded (prefill); 0 switches it off
+        self.sp_min_rows = int(_os.environ.get("MINISGL_SP_MIN_ROWS", "1024")) if self.size > 1 else 0
+        if self.sp_tpad_max // 128 > self.sp_slots or hidden % 256:
+            self.sp_min_rows = 0
         self.big = False
         self.multimem = False
         from ..env import ENV
@@ -185,6 +226,81 @@ class SymmComm(Comm):
             init_logger(__name__).warning("block-wise two-shot all-reduce failed its start-up check "
                                           f"(status {status[:4]}); prefill uses the one-shot exchange")
         self.counters["all_reduce"] = 0
+
+    # ------------------------------------------------------------------ row-sharded (sequence-parallel) exchange
+    def sp_plan(self, t: int) -> Optional[SpPlan]:
+        """Ownership plan if a forward of t rows should run row-sharded, else None."""
+        if self.sp_min_rows <= 0 or t < self.sp_min_rows or _SKIP_EXCHANGE:
+            return None
+        p = SpPlan(t, self.rank, self.size)
+        return p if p.tpad <= self.sp_tpad_max else None
+
+    def _sp_ctx(self, plan: SpPlan, channel: int, seq: int) -> SpCtx:
+        c = SpCtx()
+        for r in range(self.size):
+            c.peer[r] = self._ptrs[r]
+        c.mc = self.mc_ptr or None
+        c.rank, c.world, c.rows_per_rank, c.hidden = self.rank, self.size, plan.rpr, self.hidden
+        c.flags_off, c.ag_off = self.sp_flags_off, self.sp_ag_off[channel]
+        c.rs_off = self.flags_bytes + (channel * 2) * self.data_bytes       # parity-0 area of the channel
+        c.seq, c.use_mc = seq, 1 if (self.multimem and self.mc_ptr) else 0
+        return c
+
+    def sp_buffers(self, plan: SpPlan, channel: int):
+        """This rank's copy of the channel's gathered buffer: (y bf16 [tpad, h], q e4m3 [tpad, h], s fp32 [tpad, h/128])."""
+        h, tp = self.hidden, plan.tpad
+        o = self.sp_ag_off[channel]
+        y = self.buf[o:o + tp * h * 2].view(torch.bfloat16).view(tp, h)
+        o += tp * h * 2
+        q = self.buf[o:o + tp * h].view(torch.float8_e4m3fn).view(tp, h)
+        o += tp * h
+        s = self.buf[o:o + tp * (h // 128) * 4].view(torch.float32).view(tp, h // 128)
+        return y, q, s
+
+    def sp_all_gather(self, plan: SpPlan, channel: int) -> SpCtx:
+        """Pushes this rank's rows of the gathered buffer (written by the kernels before this call) to all peers and
+        returns the context with which the consuming GEMMs gate their loads."""
+        self.sp_seq += 1
+        self.counters["sp_all_gather"] += 1
+        ctx = self._sp_ctx(plan, channel, self.sp_seq)
+        nv.call("sp_ag_push", ctypes.byref(ctx), I(plan.tpad), nv.ptr(self.sp_counters))
+        return ctx
+
+    def sp_gemm_fp8_reduce_scatter(self, plan: SpPlan, channel: int, xq, sx, w, ws, hc=None) -> torch.Tensor:
+        """Projection of all rows by this rank's K shard, reduce-scattered: the GEMM epilogue stores every partial row
+        into its owner's buffer over NVLink, the owner adds the ranks' partials.  Returns this rank's rows
+        [n_own, n], or with hc = (residual, post, comb) of the own rows the new residual streams [n_own, 4, n]."""
+        m, k = xq.shape
+        n = w.shape[0]
+        self.sp_seq += 1
+        self.counters["sp_reduce_scatter"] += 1
+        ctx = self._sp_ctx(plan, channel, self.sp_seq)
+        cnt = self.sp_counters[self.sp_slots:]
+        nv.call("gemm_fp8_rs", nv.ptr(xq), nv.ptr(w), nv.ptr(sx), nv.ptr(ws), I(m), I(n), I(k), I(xq.stride(0)),
+                I(w.stride(0)), I(0), ctypes.byref(ctx), nv.ptr(cnt))
+        return self._sp_reduce(ctx, plan, n, hc)
+
+    def sp_moe_finalize_reduce_scatter(self, plan: SpPlan, rows, moe_plan, max_tiles, shared, t, topk, h, hc=None):
+        """Expert combine of all rows on this rank's experts (+ shared expert shard), reduce-scattered like above."""
+        self.sp_seq += 1
+        self.counters["sp_reduce_scatter"] += 1
+        ctx = self._sp_ctx(plan, self.CH_MOE, self.sp_seq)
+        cnt = self.sp_counters[self.sp_slots:]
+        nv.call("moe_finalize_rs", nv.ptr(rows), nv.ptr(moe_plan), I(t * topk), I(max_tiles), nv.ptr(shared), I(t),
+                I(topk), I(h), ctypes.byref(ctx), nv.ptr(cnt))
+        return self._sp_reduce(ctx, plan, h, hc)
+
+    def _sp_reduce(self, ctx: SpCtx, plan: SpPlan, n: int, hc):
+        if hc is not None:
+            res, post, comb = hc
+            xout = torch.empty_like(res)
+            nv.call("sp_rs_reduce", ctypes.byref(ctx), I(plan.n_own), I(n), nv.ptr(None), nv.ptr(res), nv.ptr(post),
+                    nv.ptr(comb), nv.ptr(xout))
+            return xout
+        out = torch.empty(plan.n_own, n, dtype=torch.bfloat16, device=self.device)
+        nv.call("sp_rs_reduce", ctypes.byref(ctx), I(plan.n_own), I(n), nv.ptr(out), nv.ptr(None), nv.ptr(None),
+                nv.ptr(None), nv.ptr(None))
+        return out
 
     # ------------------------------------------------------------------ collectives
     def all_reduce(self, x: torch.Tensor, tag: str = "") -> torch.Tensor:

@@ -148,6 +148,48 @@ def _checks():
             want[5] = 100
             assert toks.cpu().tolist() == want.tolist(), (it, (toks.cpu() != want).nonzero().flatten()[:5])
             assert fbuf[:128].cpu().tolist() == want.tolist()
+        # 2c) row-sharded exchange, kernel by kernel.  All-gather fused into a GEMM's loads: every rank writes only its
+        # own rows of a common tensor into the gathered buffer, pushes them, and the gated GEMM over ALL rows must
+        # equal the plain GEMM over the full tensor.  Reduce-scatter fused into a GEMM epilogue: against NCCL.
+        from minisgl.ops.gemm import gemm_fp8_gated
+        from minisgl.parallel.symm import SpPlan
+
+        for trows in (600, 1500):
+            plan = SpPlan(trows, rank, world)
+            gen = torch.Generator().manual_seed(7 + trows)
+            xf = torch.randn(trows, 4096, generator=gen).to(torch.bfloat16).to(dev)
+            xq_full, sx_full = O.fp8_quant(xf)
+            ag_y, ag_q, ag_s = comm.sp_buffers(plan, comm.CH_ATTN)
+            ag_y.zero_(); ag_q.view(torch.uint8).zero_(); ag_s.zero_()
+            r0, n = plan.row0, plan.n_own
+            ag_y[r0:r0 + n] = xf[r0:r0 + n]
+            ag_q[r0:r0 + n] = xq_full[r0:r0 + n]
+            ag_s[r0:r0 + n] = sx_full[r0:r0 + n]
+            torch.cuda.synchronize()
+            dist.barrier()
+            ww = torch.randn(2048, 4096, device=dev) * 0.02
+            wq, wsc = quant.fp8_weight_quant(ww)
+            ws = quant.e8m0_decode(wsc)
+            gate = comm.sp_all_gather(plan, comm.CH_ATTN)
+            got = gemm_fp8_gated(ag_q[:trows], ag_s[:trows], wq, ws, gate)
+            want = O.gemm_fp8(xq_full, sx_full, wq, ws)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), ("gated gemm", trows, rel(got, want))
+            assert torch.equal(ag_y[:trows], xf), "gathered bf16 rows differ"
+            # reduce-scatter epilogue
+            xr = (torch.randn(trows, 1024, device=dev) * (rank + 1)).to(torch.bfloat16)
+            xq, sx = O.fp8_quant(xr)
+            w2 = torch.randn(4096, 1024, device=dev) * 0.02
+            w2q, w2c = quant.fp8_weight_quant(w2)
+            w2s = quant.e8m0_decode(w2c)
+            full = O.gemm_fp8(xq, sx, w2q, w2s, out_dtype=torch.float32)
+            dist.all_reduce(full)
+            own = comm.sp_gemm_fp8_reduce_scatter(plan, comm.CH_ATTN, xq, sx, w2q, w2s)
+            torch.cuda.synchronize()
+            assert own.shape[0] == n
+            if n:
+                assert rel(own, full[r0:r0 + n]) < 1e-2, ("reduce-scatter", trows, rel(own, full[r0:r0 + n]))
+            assert native.read_status(clear=False)[0] == 0
         # 3) whole model: tensor/expert parallel vs single rank
         # (600 prompt tokens: the prefill's collectives take the block-wise path, the decode steps the row-wise one)
         toks = torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist()
@@ -163,6 +205,20 @@ def _checks():
         torch.cuda.synchronize()
         native.assert_device_ok()
         assert rel(l_tp, l_1) < 0.2, rel(l_tp, l_1)  # e4m3 rounding and router top-k flips amplify over layers
+        # 3b) the same prompt with the layer row-sharded during prefill (reduce-scatter / all-gather instead of the
+        # all-reduces): same logits as the replicated run up to bf16 summation order
+        assert comm.counters["sp_all_gather"] == 2, comm.counters      # only the kernel checks above used it so far
+        comm.sp_min_rows = 256
+        sp = MiniRunner(cfg, dev, comm=comm, moe_mode=args.moe_mode, rank=rank, size=world, seed=2, **kw)
+        l_sp = sp.step([(0, toks)])
+        for t in toks[:3]:
+            l_sp = sp.step([(0, [t])])
+        torch.cuda.synchronize()
+        native.assert_device_ok()
+        assert comm.counters["sp_all_gather"] == 2 + 2 * cfg.num_layers, comm.counters
+        assert rel(l_sp, l_tp) < 0.1, ("row-sharded vs replicated", rel(l_sp, l_tp))
+        assert rel(l_sp, l_1) < 0.2, rel(l_sp, l_1)
+        comm.sp_min_rows = 1024
         print(f"OK cuda rank {rank} rel {rel(l_tp, l_1):.4f} counters {comm.counters}", flush=True)
 
 
