@@ -9,11 +9,19 @@ full model's shapes:
                         epilogue vs the same GEMM followed by NCCL
   * moe_combine       : expert-parallel routed experts (256/N experts per rank, uniform-random top-6 routing), with the
                         per-token route sum + shared expert + all-reduce in one kernel vs unfused finalize + NCCL
-Times are per call inside a CUDA graph of `--iters` calls (no host launch gaps), with an L2 flush before every call
-whose own cost is subtracted, reduced with MAX over ranks.  The roofline of a
-fused call is the slower of FLOPs / measured GEMM peak and NVLink bytes / 770 GB/s, the bytes being those of the
-one-shot exchange ((N-1) * M * 4096 * 2 pulled by each GPU); above 256 rows the block-wise two-shot path moves
-2 * (N-1)/N * M * 4096 * 2 instead and can therefore read above 1.
+  * wo_b_rs           : the same projection with the reduce-scatter fused into the GEMM epilogue (partial rows stored
+                        straight into their owner's buffer, owner adds them) vs GEMM + ``dist.reduce_scatter_tensor``
+  * ag_wqkv_a         : all-gather fused into the first projection [M, 4096] x [2048, 4096]^T (owners push their rows,
+                        the GEMM's loads wait per 128-row block) vs ``dist.all_gather_into_tensor`` + GEMM
+  * moe_rs            : the expert combine with the reduce-scatter form
+Times of the first three are per call inside a CUDA graph of `--iters` calls (no host launch gaps), with an L2 flush
+before every call whose own cost is subtracted, reduced with MAX over ranks.  The row-sharded forms (``*_rs``,
+``ag_*``) number their exchanges on the host, so they and their NCCL baselines are timed eagerly, back to back on
+one stream (marked ``eager`` in the output; below a few hundred rows such a number is bound by the host's launch
+rate).  The roofline of a fused call is the slower of FLOPs / measured GEMM peak and NVLink bytes / 770 GB/s.  Bytes
+per GPU: one-shot all-reduce (N-1) * M * 4096 * 2 pulled; two-shot and in-switch forms 2 * (N-1)/N * M * 4096 * 2 (so
+a number measured with them can read above 1 against the one-shot roofline); reduce-scatter (N-1)/N * M * 4096 * 2;
+all-gather (N-1)/N * M * (4096 * 3 + 128) (bf16 rows, e4m3 rows and scales).
 """
 from __future__ import annotations
 
@@ -78,6 +86,23 @@ def _time(fn, iters, flush):
     return float(t)
 
 
+def _time_eager(fn, iters):
+    """Microseconds per call, max over ranks: `iters` calls issued back to back on the current stream."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) * 1e3 / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, nargs="+", default=[1, 8, 32, 128, 256, 8192])
@@ -93,7 +118,7 @@ def main(argv=None):
     from minisgl.parallel.comm import init_distributed
     from minisgl.parallel.info import DistributedInfo
 
-    _, comm = init_distributed(DistributedInfo(rank, world), dev, max_rows=max(a.rows), hidden=4096)
+    _, comm = init_distributed(DistributedInfo(rank, world), dev, max_rows=max(max(a.rows), 512), hidden=4096)
     tflops, hbm, src = _peaks()
     H, KO = 4096, 8192 // world
     e_local, inter, topk = 256 // world, 2048, 6
@@ -149,6 +174,62 @@ def main(argv=None):
         moe_bytes = touched * (3 * inter * H // 2 + 3 * inter * H // 32)
         res["moe_roofline_us"] = max(moe_flops / (tflops * 1e6), moe_bytes / (hbm * 1e3), t_link)
         res["moe_roofline_frac"] = res["moe_roofline_us"] / res["moe_fused_us"]
+        res["collectives"] = getattr(comm, "mode", "none")
+        # ---- row-sharded forms (eager timing, see the module docstring)
+        from minisgl.ops.gemm import gemm_fp8_gated
+        from minisgl.parallel.symm import SpPlan
+
+        plan = SpPlan(m, rank, world)
+        if plan.tpad <= comm.sp_tpad_max:
+            it = a.iters
+            mp = plan.tpad
+            pad_x = torch.zeros(mp, KO, device=dev, dtype=torch.bfloat16)
+            pad_x[:m] = xo
+            pq, ps_ = O.fp8_quant(pad_x)
+            rs_out = torch.empty(plan.rpr, H, device=dev, dtype=torch.bfloat16)
+
+            def rs_nccl():
+                y = O.gemm_fp8(pq, ps_, wq, ws)
+                dist.reduce_scatter_tensor(rs_out, y)
+
+            res["wo_b_rs_gemm_plus_nccl_us"] = _time_eager(rs_nccl, it)
+            res["wo_b_rs_fused_us"] = _time_eager(
+                lambda: comm.sp_gemm_fp8_reduce_scatter(plan, comm.CH_ATTN, xq, sx, wq, ws), it)
+            rs_link = (world - 1) / world * m * H * 2 / (NVLINK_GBS * 1e3)
+            res["wo_b_rs_roofline_us"] = max(flops / (tflops * 1e6), rs_link)
+            res["wo_b_rs_roofline_frac"] = res["wo_b_rs_roofline_us"] / res["wo_b_rs_fused_us"]
+            # all-gather -> first projection (2048 output columns of the full model's wqkv_a)
+            wa = torch.randn(2048, H, device=dev, generator=g) * 0.02
+            waq, wac = quant.fp8_weight_quant(wa)
+            was = quant.e8m0_decode(wac)
+            ag_y, ag_q, ag_s = comm.sp_buffers(plan, comm.CH_ATTN)
+            yq_own, ys_own = O.fp8_quant(torch.randn(plan.rpr, H, device=dev, generator=g).to(torch.bfloat16))
+            ag_q[rank * plan.rpr:(rank + 1) * plan.rpr] = yq_own
+            ag_s[rank * plan.rpr:(rank + 1) * plan.rpr] = ys_own
+            full_q = torch.empty(mp, H, device=dev, dtype=torch.uint8)
+            full_s = torch.empty(mp, H // 128, device=dev, dtype=torch.float32)
+
+            def ag_nccl():
+                dist.all_gather_into_tensor(full_q, yq_own.view(torch.uint8))
+                dist.all_gather_into_tensor(full_s, ys_own)
+                O.gemm_fp8(full_q.view(torch.float8_e4m3fn)[:m], full_s[:m], waq, was)
+
+            def ag_fused():
+                gate = comm.sp_all_gather(plan, comm.CH_ATTN)
+                gemm_fp8_gated(ag_q[:m], ag_s[:m], waq, was, gate)
+
+            res["ag_wqkv_a_nccl_plus_gemm_us"] = _time_eager(ag_nccl, it)
+            res["ag_wqkv_a_fused_us"] = _time_eager(ag_fused, it)
+            ag_link = (world - 1) / world * m * (3 * H + H // 128 * 4) / (NVLINK_GBS * 1e3)
+            res["ag_wqkv_a_roofline_us"] = max(2.0 * m * H * 2048 / (tflops * 1e6), ag_link)
+            res["ag_wqkv_a_roofline_frac"] = res["ag_wqkv_a_roofline_us"] / res["ag_wqkv_a_fused_us"]
+
+            def moe_rs():
+                rows, mplan, mt = C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, base)
+                return comm.sp_moe_finalize_reduce_scatter(plan, rows, mplan, mt, shared, m, topk, H)
+
+            res["moe_rs_fused_us"] = _time_eager(moe_rs, max(it // 2, 3))
+            res["eager"] = ["wo_b_rs_*", "ag_wqkv_a_*", "moe_rs_*"]
         rows_out.append(res)
         if rank == 0:
             print(json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in res.items()}), flush=True)

@@ -110,7 +110,7 @@ DSV4_API int dsv4_sp_slots() { return kSpSlots; }
 // counters: >= rows_per_rank / 128 zeroed ints.
 DSV4_API int dsv4_sp_ag_push(const SpCtx* c, int tpad, int* counters, cudaStream_t st) {
   if (c->world <= 1) return 0;
-  if (c->rows_per_rank % 128 || c->hidden % 128 || tpad != c->rows_per_rank * c->world) return 520;
+  if (c->rows_per_rank % 128 || c->hidden % 512 || tpad != c->rows_per_rank * c->world) return 520;
   if (tpad / 128 > kSpSlots) return 521;
   dsv4_launch(sp_ag_push_kernel, dim3(c->rows_per_rank / 128, kParts), 256, 0, st, *c, tpad, counters);
   return (int)cudaGetLastError();
