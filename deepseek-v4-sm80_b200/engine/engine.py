@@ -215,7 +215,7 @@ class Engine:
         swa_slots = swa_slot_plan(c.max_running_req, c.max_prefill_length, ps, cfg.window_size)
         per_page = bytes_per_page(cfg, ps)
         fixed = swa_slots * bytes_per_swa_slot(cfg, ps) + (c.max_running_req + 1) * bytes_per_req_slot(cfg)
-        want_pages = min(c.max_running_req * div_ceil(limit, ps) + div_ceil(c.max_prefill_length, ps), 1 << 16)
+        want_pages = min(c.max_running_req * div_ceil(limit, ps) + div_ceil(c.max_prefill_length, ps), 1 << 18)
         if self.is_cuda:
             free = self._sync_free_memory()
             total = torch.cuda.get_device_properties(self.device).total_memory

@@ -14,6 +14,13 @@
 // swa_map[loc / ps] * ps + loc % ps.  (m, l) start at (sink, 1), which adds exp(sink - m) to the denominator only --
 // the reference's two-source kernel semantics
 // (python/minisgl/kernel/csrc/jit/dsv4_sparse_attention_two_source_bf16.cu:77-168).
+//
+// Split-KV (decode with few tokens and long histories): grid.y CTAs share one token, each takes a contiguous range of
+// the token's key tiles and leaves its unnormalised accumulator with its running (max, sum) in a scratch buffer; the
+// last CTA of the token to finish (a per-token counter) merges the partials in split order --
+//   M = max_s m_s,  L = sum_s l_s e^(m_s - M),  o = sum_s acc_s e^(m_s - M) / L
+// -- and runs the usual epilogue.  The sink belongs to split 0.  The reference's decode kernel splits the same way
+// (python/minisgl/kernel/triton/deepseek_v4.py:1645, :2002-2050, up to 16 splits).
 #include "common.cuh"
 #include "rope.cuh"
 
@@ -69,6 +76,10 @@ struct AttnArgs {
   const int* num_valid;
   int out_rope;   // != 0: rotate the last rp.rotary_dim dims of every output head row by -position (the inverse
   RopeParams rp;  //       RoPE the output projection expects), on the bf16-rounded values, in the epilogue
+  int nsplit;        // CTAs per token (grid.y); > 1 needs the three buffers below
+  float* part_acc;   // [t][nsplit][HL][512] unnormalised accumulators
+  float* part_ml;    // [t][nsplit][HL][2]   running max and sum
+  int* counters;     // [t] zero between launches
 };
 
 // row of 512 bf16 = 64 chunks of 16 B; chunk c of row r is stored at chunk (c ^ (r & 7))
@@ -110,9 +121,11 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
   constexpr int kSwaBit = 1 << 30;                                   // set: row of the window cache, else compressed
 
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.y, nsplit = a.nsplit;
   if (a.num_valid && t >= *a.num_valid) {
-    for (int i = tid; i < HL * D / 8; i += NTHR)
-      reinterpret_cast<uint4*>(a.o + (size_t)t * HL * D)[i] = make_uint4(0, 0, 0, 0);
+    if (split == 0)
+      for (int i = tid; i < HL * D / 8; i += NTHR)
+        reinterpret_cast<uint4*>(a.o + (size_t)t * HL * D)[i] = make_uint4(0, 0, 0, 0);
     return;
   }
   const int p = a.pos[t], slot = a.slots[t];
@@ -132,7 +145,17 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
     if (r < HL) v = reinterpret_cast<const uint4*>(a.q + ((size_t)t * HL + r) * D)[c];
     reinterpret_cast<uint4*>(qs + r * D)[swz_row(r, c)] = v;
   }
-  if (tid < HP) ms[tid] = tid < HL ? a.sink[tid] : 0.f, ls[tid] = 1.f;
+  // the sink starts split 0's running (max, sum); the other splits start empty (a finite floor instead of -inf keeps
+  // exp(m_old - m_new) well defined for a split that meets no valid key)
+  if (tid < HP) {
+    if (split == 0)
+      ms[tid] = tid < HL ? a.sink[tid] : 0.f, ls[tid] = 1.f;
+    else
+      ms[tid] = -1e30f, ls[tid] = 0.f;
+  }
+  // this CTA's keys: a contiguous range of whole tiles
+  const int tiles_per = (ntiles + nsplit - 1) / nsplit;
+  const int k_lo = min(split * tiles_per * KT, ntot), k_hi = min((split + 1) * tiles_per * KT, ntot);
 
   // Rows of keys [base, base + RB) -> rowsrc.  A key's row hangs on a chain of two or three dependent loads
   // (selected index -> page-table entry -> window slot); resolving a tile's keys right before its gather would put
@@ -170,11 +193,12 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
     }
   };
 
+  int rbase = 0;                       // first key whose row sits in rowsrc[0]
   constexpr int TPK = NTHR / KT;       // threads cooperating on one key row
   constexpr int CPT = 64 / TPK;        // 16-byte chunks per thread
   auto issue_tile = [&](int tile, int buf) {
     const int kk = tid / TPK, part = tid % TPK;
-    const int e = rowsrc[(tile * KT + kk) % RB];
+    const int e = rowsrc[tile * KT + kk - rbase];
     const __nv_bfloat16* src = nullptr;
     if (e >= 0) src = (e & kSwaBit) ? a.swa + (size_t)(e & (kSwaBit - 1)) * D : a.comp + (size_t)e * D;
     __nv_bfloat16* dst = kvs + ((size_t)buf * KT + kk) * D;
@@ -193,8 +217,9 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
 #pragma unroll
   for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-  for (int base = 0; base < ntot; base += RB) {
-  const int tile_lo = base / KT, tile_hi = min(ntiles, (base + RB) / KT);
+  for (int base = k_lo; base < k_hi; base += RB) {
+  const int tile_lo = base / KT, tile_hi = min((k_hi + KT - 1) / KT, (base + RB) / KT);
+  rbase = base;
   resolve(base);
   __syncthreads();
   issue_tile(tile_lo, tile_lo & 1);
@@ -296,6 +321,68 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
   }
   }
   __syncthreads();
+  if (nsplit > 1) {
+    // leave this split's partial, then the last CTA of the token merges all of them
+    __shared__ int is_last;
+    const int r0 = mt * 16 + (lane >> 2);
+    float* pa = a.part_acc + ((size_t)t * nsplit + split) * HL * D;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int d0 = g * C::DW + nt * 8 + (lane & 3) * 2;
+      if (r0 < HL) *reinterpret_cast<float2*>(pa + (size_t)r0 * D + d0) = make_float2(acc[nt][0], acc[nt][1]);
+      if (r0 + 8 < HL) *reinterpret_cast<float2*>(pa + (size_t)(r0 + 8) * D + d0) = make_float2(acc[nt][2], acc[nt][3]);
+    }
+    if (tid < HL) {
+      float* pm = a.part_ml + (((size_t)t * nsplit + split) * HL + tid) * 2;
+      pm[0] = ms[tid], pm[1] = ls[tid];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const int prev = atomicAdd(&a.counters[t], 1);
+      is_last = prev == nsplit - 1;
+      if (is_last) a.counters[t] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // per head row: global max, rescale factors per split (kept in shared memory: alpha reused as scratch is too
+    // small, so recompute per thread -- nsplit <= 32)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+    for (int s2 = 0; s2 < nsplit; ++s2) {
+      const float* pm = a.part_ml + ((size_t)t * nsplit + s2) * HL * 2;
+      if (r0 < HL) mx0 = fmaxf(mx0, __ldcg(pm + r0 * 2));
+      if (r0 + 8 < HL) mx1 = fmaxf(mx1, __ldcg(pm + (r0 + 8) * 2));
+    }
+    float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    for (int s2 = 0; s2 < nsplit; ++s2) {
+      const float* pm = a.part_ml + ((size_t)t * nsplit + s2) * HL * 2;
+      const float* ps2 = a.part_acc + ((size_t)t * nsplit + s2) * HL * D;
+      float w0 = 0.f, w1 = 0.f;
+      if (r0 < HL) w0 = __expf(__ldcg(pm + r0 * 2) - mx0), l0 += __ldcg(pm + r0 * 2 + 1) * w0;
+      if (r0 + 8 < HL) w1 = __expf(__ldcg(pm + (r0 + 8) * 2) - mx1), l1 += __ldcg(pm + (r0 + 8) * 2 + 1) * w1;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int d0 = g * C::DW + nt * 8 + (lane & 3) * 2;
+        if (r0 < HL) {
+          const float2 v = __ldcg(reinterpret_cast<const float2*>(ps2 + (size_t)r0 * D + d0));
+          acc[nt][0] = fmaf(v.x, w0, acc[nt][0]), acc[nt][1] = fmaf(v.y, w0, acc[nt][1]);
+        }
+        if (r0 + 8 < HL) {
+          const float2 v = __ldcg(reinterpret_cast<const float2*>(ps2 + (size_t)(r0 + 8) * D + d0));
+          acc[nt][2] = fmaf(v.x, w1, acc[nt][2]), acc[nt][3] = fmaf(v.y, w1, acc[nt][3]);
+        }
+      }
+    }
+    __syncthreads();
+    if ((lane & 3) == 0 && g == 0) {   // one writer per head row
+      if (r0 < HL) ls[r0] = l0;
+      if (r0 + 8 < HL) ls[r0 + 8] = l1;
+    }
+    __syncthreads();
+  }
   {
     const int r0 = mt * 16 + (lane >> 2);
     const float i0 = 1.f / ls[r0], i1 = 1.f / ls[r0 + 8];
@@ -320,6 +407,7 @@ __global__ void __launch_bounds__(AttnCfg<HL>::NW * 32) sparse_attn_kernel(AttnA
 
 template <int HL>
 int launch_attn(const AttnArgs& a, int t, cudaStream_t st) {
+  if (a.nsplit > 32) return 304;
   using C = AttnCfg<HL>;
   static bool set = false;
   if (!set) {
@@ -328,7 +416,7 @@ int launch_attn(const AttnArgs& a, int t, cudaStream_t st) {
       return 301;
     set = true;
   }
-  dsv4_launch(sparse_attn_kernel<HL>, t, C::NW * 32, C::SMEM, st, a);
+  dsv4_launch(sparse_attn_kernel<HL>, dim3(t, a.nsplit), C::NW * 32, C::SMEM, st, a);
   return (int)cudaGetLastError();
 }
 
@@ -338,13 +426,16 @@ DSV4_API int dsv4_sparse_attention(const void* q, void* o, const int* slots, con
                                    int ld_pt, const void* swa, const int* swa_map, const void* comp,
                                    const int* topk_idx, const int* topk_len, int topk_width, int mode, int ratio,
                                    const float* sink, float scale, int ps, int window, const int* num_valid, int t,
-                                   int heads, int d, int out_rope, RopeParams rp, cudaStream_t st) {
+                                   int heads, int d, int out_rope, RopeParams rp, int nsplit, float* part_acc,
+                                   float* part_ml, int* counters, cudaStream_t st) {
   if (t <= 0) return 0;
   if (d != D) return 300;
+  if (nsplit < 1) nsplit = 1;
+  if (nsplit > 1 && (!part_acc || !part_ml || !counters)) return 305;
   if (out_rope && (rp.rotary_dim <= 0 || rp.rotary_dim > 128 || rp.rotary_dim % 8)) return 303;
   AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)o, slots, pos, page_table, ld_pt, (const __nv_bfloat16*)swa,
              swa_map, (const __nv_bfloat16*)comp, topk_idx, topk_len, topk_width, mode, ratio, sink, scale, ps,
-             window, num_valid, out_rope, rp};
+             window, num_valid, out_rope, rp, nsplit, part_acc, part_ml, counters};
   switch (heads) {
     case 8: return launch_attn<8>(a, t, st);
     case 16: return launch_attn<16>(a, t, st);

@@ -296,19 +296,48 @@ def indexer_select(qc, wf, vals, scales, fb, ps: int, k: int):
 
 
 # --------------------------------------------------------------------------- attention
+_ATTN_COUNTERS = {}
+
+
+def attention_splits(t: int, heads: int, mode: int, ratio: int, topk_width: int, window: int, max_context: int,
+                     prefill: bool, sms: int) -> int:
+    """CTAs per token.  Splitting pays when the tokens alone leave SMs idle and a token has many key tiles (decode of
+    a few long sequences); a batch that fills the GPU, and every prefill chunk, runs one CTA per token."""
+    if prefill or t <= 0:
+        return 1
+    keys = window + (topk_width if mode == 1 else (max_context // ratio if mode == 2 else 0))
+    kt = 64 if heads <= 16 else 32          # keys per tile of the kernel's configuration
+    ntiles = -(-keys // kt)
+    return int(max(1, min(sms // t, -(-ntiles // 2), 32)))
+
+
 def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_len, sink, scale, ps: int,
-              window: int, out_rope=None):
-    """out_rope: RopeSpec whose inverse rotation the kernel applies to the tail of every output row."""
+              window: int, out_rope=None, nsplit: int = 0):
+    """out_rope: RopeSpec whose inverse rotation the kernel applies to the tail of every output row.
+    nsplit: CTAs per token (0: chosen by :func:`attention_splits`)."""
     t, h, d = q.shape
     o = torch.empty_like(q)
     mode = 1 if ratio == 4 else (2 if ratio else 0)
     pt = fb.page_table
+    if nsplit <= 0:
+        nsplit = attention_splits(t, h, mode, ratio, topk_idx.shape[1] if mode == 1 else 0, window,
+                                  int(fb.max_context), bool(getattr(fb, "is_prefill", False)), num_sms(q.device))
+    acc = ml = cnt = None
+    if nsplit > 1:
+        acc = torch.empty(t, nsplit, h, d, dtype=torch.float32, device=q.device)
+        ml = torch.empty(t, nsplit, h, 2, dtype=torch.float32, device=q.device)
+        key = q.device.index or 0
+        cnt = _ATTN_COUNTERS.get(key)
+        if cnt is None or cnt.shape[0] < t:
+            cnt = torch.zeros(max(t, 4096), dtype=torch.int32, device=q.device)
+            _ATTN_COUNTERS[key] = cnt
     nv.call("sparse_attention", nv.ptr(q), nv.ptr(o), _i32(fb.slots), _i32(fb.positions), _i32(pt), I(pt.stride(0)),
             nv.ptr(swa_cache), _i32(swa_map), nv.ptr(comp_cache if mode else None),
             nv.ptr(topk_idx if mode == 1 else None), nv.ptr(topk_len if mode == 1 else None),
             I(topk_idx.shape[1] if mode == 1 else 0), I(mode), I(ratio), nv.ptr(sink), F(scale), I(ps), I(window),
             nv.ptr(fb.num_valid), I(t), I(h), I(d), I(1 if out_rope is not None else 0),
-            rope_params(out_rope if out_rope is not None else _NO_ROPE))
+            rope_params(out_rope if out_rope is not None else _NO_ROPE), I(nsplit), nv.ptr(acc), nv.ptr(ml),
+            nv.ptr(cnt))
     return o
 
 

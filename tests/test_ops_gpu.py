@@ -330,6 +330,20 @@ def test_sparse_attention(heads, ratio):
     o2_r = O.rope_tail(o.clone(), fbd.positions, spec, inverse=True)
     assert torch.equal(o2[..., :448], o[..., :448])
     close(o2, o2_r, atol=1e-2)
+    # split-KV: the token's key tiles spread over several CTAs and merged must give the one-CTA result (same
+    # arithmetic up to the order of the fp32 additions), for split counts that leave some CTAs without any key too
+    from minisgl.ops import cuda
+
+    one = cuda.attention(q.to(DEV), fbd, swa.to(DEV), swa_map.to(DEV), dv(comp), ratio, dv(tk_idx), dv(tk_len),
+                         sink.to(DEV), 512 ** -0.5, ps, 128, out_rope=spec, nsplit=1)
+    close(one, O.rope_tail(o_r.to(DEV), fbd.positions, spec, inverse=True), atol=2e-2)
+    for ns in (2, 5, 32):
+        many = cuda.attention(q.to(DEV), fbd, swa.to(DEV), swa_map.to(DEV), dv(comp), ratio, dv(tk_idx), dv(tk_len),
+                              sink.to(DEV), 512 ** -0.5, ps, 128, out_rope=spec, nsplit=ns)
+        close(many, one, atol=4e-3, rtol=1e-2)
+        again = cuda.attention(q.to(DEV), fbd, swa.to(DEV), swa_map.to(DEV), dv(comp), ratio, dv(tk_idx),
+                               dv(tk_len), sink.to(DEV), 512 ** -0.5, ps, 128, out_rope=spec, nsplit=ns)
+        assert torch.equal(many, again)          # the merge runs in split order whichever CTA finishes last
 
 
 def test_moe_gate_and_experts():
