@@ -122,7 +122,8 @@ def test_chat_formatter_from_the_model_folder(tmp_path):
 
 
 @pytest.mark.parametrize("mod", ["offline.bench", "offline.bench_wildchat", "online.bench_simple", "online.bench_qwen",
-                                 "perf_matrix", "scheduler_sim", "decode_step", "moe_gemm", "ops", "collectives"])
+                                 "perf_matrix", "scheduler_sim", "decode_step", "moe_gemm", "ops", "collectives",
+                                 "online_trace", "coverage_run"])
 def test_public_benchmark_scripts_import_and_describe_their_arguments(mod, capsys):
     m = importlib.import_module("minisgl.benchmark." + mod)
     assert callable(m.main) and (m.__doc__ or "").strip()
@@ -149,3 +150,24 @@ def test_generate_prompt_never_exceeds_the_count_with_an_unstable_tokenizer():
     tok = Growing()
     for n in (17, 64):
         assert len(tok.encode(C.generate_prompt(tok, n, seed=n))) <= n
+
+
+def test_online_trace_runs_timed_arrivals_through_the_engine():
+    """Poisson arrivals in wall-clock time on the tiny CPU model: every request finishes with its full output, the
+    shared prefix gives radix hits, latencies come out ordered (p50 <= p99), and the perf-matrix harness reports its
+    per-scenario figures and the memory ledger."""
+    from minisgl.benchmark import online_trace, perf_matrix
+
+    res = online_trace.main(["--tiny", "--device", "cpu", "--page-size", "16", "--num-pages", "512", "--max-running",
+                             "8", "--requests", "10", "--rates", "40", "--prompt-median", "60", "--output-median", "6",
+                             "--max-prompt", "300", "--max-output", "12"])
+    r = res[0]
+    assert r["requests"] == r["finished"] == 10 and r["output_tokens"] > 10
+    assert r["ttft_s"]["p50"] <= r["ttft_s"]["p99"] and r["tpot_ms"]["p50"] <= r["tpot_ms"]["p99"]
+    trace = online_trace.token_trace(200, 8.0, 1000, seed=3)
+    gaps = [b[0] - a[0] for a, b in zip(trace, trace[1:])]
+    assert all(g >= 0 for g in gaps) and 0.08 < sum(gaps) / len(gaps) < 0.2          # mean gap ~ 1 / rate
+    assert all(16 <= len(t[1]) <= 16384 and 1 <= t[2] <= 4096 for t in trace)
+    out = perf_matrix.main(["--tiny", "--device", "cpu", "--page-size", "16", "--num-pages", "256", "--max-running", "8",
+                            "--scale", "0.05", "--scenarios", "P1K_M8", "--ledger"])
+    assert out[0]["requests"] == 8 and out[0]["ledger"]["kv_plan"]["num_pages"] == 256
