@@ -206,7 +206,9 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   }
 }
 
-// xs[pos] = fp16(x[route / topk]): the grouped GEMMs run fp16 x fp16 (FP4 weights convert to fp16 in one instruction)
+// xs[pos] = fp16(x[route / topk]): the grouped GEMMs run fp16 x fp16 (FP4 weights convert to fp16 in one instruction).
+// bf16 reaches far beyond fp16's range; an activation above 65 504 in magnitude saturates to the largest finite fp16
+// instead of becoming infinity (normalised activations stay orders of magnitude below that).
 __global__ void moe_permute_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs,
                                    const int* __restrict__ sorted_route, const PlanHeader* __restrict__ hdr, int topk,
                                    int h8) {
@@ -220,7 +222,12 @@ __global__ void moe_permute_kernel(const uint4* __restrict__ x, uint4* __restric
     uint4 o;
     __half2* hp = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) hp[j] = __float22half2_rn(__bfloat1622float2(b[j]));
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(b[j]);
+      f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
+      f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
+      hp[j] = __float22half2_rn(f);
+    }
     xs[(size_t)pos * h8 + i] = o;
   }
 }
