@@ -206,6 +206,8 @@ def main(argv=None):
     ap.add_argument("--context", type=int, default=0, help="> 0: also the attention / indexer / compressor kernels")
     ap.add_argument("--prefill", type=int, default=0, help="1: the rows are one request's prefill chunk")
     ap.add_argument("--cache-ops-only", action="store_true")
+    ap.add_argument("--eager", type=int, default=0,
+                    help="> 0: run every operator this many times eagerly and report nothing (profiler captures)")
     a = ap.parse_args(argv)
     from minisgl.benchmark.perf import time_in_graph
     from minisgl.ops import native
@@ -220,6 +222,11 @@ def main(argv=None):
         if a.only and name not in a.only:
             continue
         fn, nbytes = spec[0], spec[1]
+        if a.eager > 0:
+            for _ in range(a.eager):
+                fn()
+            torch.cuda.synchronize()
+            continue
         ms = time_in_graph(fn, calls=a.calls)
         us = ms * 1e3
         gbs = nbytes / us / 1e3

@@ -141,6 +141,7 @@ def main(argv=None) -> List[dict]:
     ap.add_argument("--trace-kernels", action="store_true", help="per-launcher call counts and device time")
     ap.add_argument("--experts", type=int, default=0, help="routed experts of the random-init model (0: the full 256)")
     ap.add_argument("--graph-bs", type=int, nargs="*", default=None, help="CUDA-graph batch sizes (default: recipe)")
+    ap.add_argument("--recipe", default="", help="serving recipe (sets max running requests and graph buckets)")
     a = ap.parse_args(argv)
     cat = catalogue(a.scale)
     if a.list:
@@ -164,8 +165,18 @@ def main(argv=None) -> List[dict]:
     longest = max(max(cat[s].prompt_lens) + cat[s].output_len for s in a.scenarios)
     if a.num_pages:
         kw["num_page_override"] = a.num_pages
-    llm = LLM(a.model, max_running_req=a.max_running, context_length=max(longest + 64, 4096), device=a.device,
-              page_size=a.page_size, **kw)
+    if a.recipe:
+        kw["recipe"] = a.recipe
+    else:
+        kw["max_running_req"] = a.max_running
+    t_start = time.perf_counter()
+    llm = LLM(a.model, context_length=max(longest + 64, 4096), device=a.device, page_size=a.page_size, **kw)
+    if llm.tp.is_primary():
+        gr = llm.engine.graph_runner
+        print(json.dumps({"startup_s": round(time.perf_counter() - t_start, 2),
+                          "graphs_captured": gr.capture_status["captured"] if gr is not None else 0,
+                          "graph_buckets": gr.buckets if gr is not None else [],
+                          "context_classes": gr.classes if gr is not None else []}), flush=True)
     llm.engine.record_timings = bool(a.timings) and llm.engine.is_cuda
     if a.trace_kernels and llm.engine.is_cuda:
         from minisgl.ops import native
