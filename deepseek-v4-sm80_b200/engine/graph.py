@@ -38,6 +38,7 @@ class GraphCaptureBuffer:
         self.num_valid = self.block[3, :1]
         self.input_ids = torch.zeros(max_bs, **z)
         self.next_tokens = torch.zeros(max_bs, **z)
+        self.logits = None    # [max_bs, vocab / tp] fp32, shared by all graphs (set by the runner)
 
     def copy_from(self, batch: Batch, bs: int) -> None:
         blk = getattr(batch, "device_block", None)
@@ -57,6 +58,10 @@ class GraphRunner:
         self.classes: List[int] = list(engine.context_classes)
         self.max_bs = max(self.buckets)
         self.buffer = GraphCaptureBuffer(self.max_bs, engine.device)
+        # every graph writes its logits shard into the same static buffer: a per-graph output would pin
+        # bucket x vocab floats for each of the dozens of (bucket, context class) graphs of a serving recipe
+        self.buffer.logits = torch.empty(self.max_bs, engine.weights["head.weight"].shape[0], dtype=torch.float32,
+                                         device=engine.device)
         self.graphs: Dict[Tuple[int, int], torch.cuda.CUDAGraph] = {}
         self.logits: Dict[Tuple[int, int], torch.Tensor] = {}
         self.launches: Dict[Tuple[int, int], int] = {}
@@ -71,7 +76,7 @@ class GraphRunner:
         b, e = self.buffer, self.engine
         fb = ForwardBatch(b.input_ids[:bs], b.positions[:bs], b.slots[:bs], b.out_loc[:bs], None, e.page_table,
                           False, max_context, b.num_valid, token_feedback=e.last_token)
-        return e.model.forward(fb, GreedyTail(e.last_token, b.next_tokens[:bs]))
+        return e.model.forward(fb, GreedyTail(e.last_token, b.next_tokens[:bs], b.logits[:bs]))
 
     def _capture_all(self) -> None:
         e = self.engine

@@ -52,6 +52,7 @@ class GreedyTail:
 
     token_feedback: torch.Tensor   # [slots+1] int32
     out: Optional[torch.Tensor] = None  # [rows] int32 (allocated when None)
+    logits_out: Optional[torch.Tensor] = None  # [rows, vocab / tp] fp32: where the head GEMM writes (else allocated)
 
 
 class Comm:
@@ -359,7 +360,10 @@ class DSV4Model:
             x = x[fb.last_idx].contiguous()
         y = O.hc_head(x, w["hc_head.fn"], w["hc_head.scale"], w["hc_head.base"], cfg.hc_eps, cfg.rms_norm_eps,
                       w["norm.weight"])
-        logits = O.gemm_bf16(y, w["head.weight"], out_dtype=torch.float32)
+        if greedy is not None and greedy.logits_out is not None:
+            logits = O.gemm_bf16(y, w["head.weight"], out=greedy.logits_out[: y.shape[0]])
+        else:
+            logits = O.gemm_bf16(y, w["head.weight"], out_dtype=torch.float32)
         if greedy is not None:
             gathered = fb.last_idx is not None and (fb.is_prefill or fb.last_idx.shape[0] != fb.slots.shape[0])
             slots = fb.slots[fb.last_idx] if gathered else fb.slots
