@@ -23,10 +23,9 @@ constexpr int DI = 128;          // indexer head dim = bytes per e4m3 row = one 
 constexpr int HEADS = 64;
 constexpr int KB = 128;          // keys per tile (TMEM lanes)
 constexpr int TGMAX = 4;         // tokens per group (N = 256 at most)
-constexpr int SA = 6;            // key-tile ring
+constexpr int SA = 6;            // key-tile ring (four-token groups); one-token groups use 4 stages
 constexpr int kATile = KB * DI;  // 16 KiB
 constexpr int kQTile = HEADS * DI;  // 8 KiB per token
-constexpr uint32_t kTmemCols = 512;  // two accumulators of up to 256 columns
 
 struct IdxArgs {
   const float* wf;        // [T, 64] folded head weights
@@ -41,7 +40,12 @@ struct IdxArgs {
   int T;
   int tg;                 // tokens per group (1, 2 or 4)
   int box_rows;           // key rows per TMA box = min(ps / 4, 64)
+  int stages;             // key-tile ring depth
+  int tmem_cols;          // tensor-memory columns: two accumulators of tg * 64 columns, rounded to a power of two
 };
+// Shared memory and tensor memory are sized by the group width: a decode launch (one token per group, N = 64) then
+// fits three CTAs on an SM instead of one, which is what hides the page-table -> TMA -> MMA latency chain there.
+inline int idx_smem_bytes(int tg, int stages) { return stages * kATile + tg * kQTile + tg * HEADS * 4 + 256 + 1024; }
 
 constexpr int kSmemBytes = SA * kATile + TGMAX * kQTile + TGMAX * HEADS * 4 + 256 + 1024;
 
@@ -52,9 +56,10 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
   extern __shared__ uint8_t ix_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ix_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* atiles = smem;                                   // [SA][128 keys][128 B], 128B-swizzled by TMA
-  uint8_t* qtile = smem + SA * kATile;                      // [tg * 64 rows][128 B]
-  float* wfs = reinterpret_cast<float*>(qtile + TGMAX * kQTile);   // [tg][64]
-  uint64_t* full = reinterpret_cast<uint64_t*>(wfs + TGMAX * HEADS);
+  const int NS = a.stages;
+  uint8_t* qtile = smem + NS * kATile;                      // [tg * 64 rows][128 B]
+  float* wfs = reinterpret_cast<float*>(qtile + a.tg * kQTile);   // [tg][64]
+  uint64_t* full = reinterpret_cast<uint64_t*>(wfs + a.tg * HEADS);
   uint64_t* empty = full + SA;
   uint64_t* tfull = empty + SA;    // [2]
   uint64_t* tempty = tfull + 2;    // [2]
@@ -69,7 +74,7 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
   const int rpp = a.ps >> 2;                   // compressed rows per page
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < SA; ++i) mbar_init(&full[i], 1), mbar_init(&empty[i], 1);
+    for (int i = 0; i < NS; ++i) mbar_init(&full[i], 1), mbar_init(&empty[i], 1);
     for (int i = 0; i < 2; ++i) mbar_init(&tfull[i], 1), mbar_init(&tempty[i], 128);
     mbar_init(qfull, 1);
     *abort_flag = 0;
@@ -78,7 +83,7 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
     tma_prefetch_desc(&tmQ);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_alloc(tmem_holder, (uint32_t)a.tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -130,7 +135,7 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
       int nmax = 0;
       for (int g = p_first[p]; g < p_first[p] + p_cnt[p]; ++g) nmax = max(nmax, n_tok[g]);
       for (int kb = split; kb < p_blocks[p]; kb += nsplit, ++it) {
-        const int s = it % SA;
+        const int s = it % NS;
         // each lane resolves the rows of its boxes before the stage wait, so the lookups overlap the wait
         int rowsrc[4];
         int mine = 0;
@@ -148,7 +153,7 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
         for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         int ok = 1;
         if (lane == 0) {
-          ok = mbar_wait<32>(&empty[s], ((it / SA) & 1) ^ 1, abort_flag, 11) ? 1 : 0;
+          ok = mbar_wait<32>(&empty[s], ((it / NS) & 1) ^ 1, abort_flag, 11) ? 1 : 0;
           if (ok) mbar_expect_tx(&full[s], (uint32_t)total * a.box_rows * DI);
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -170,17 +175,17 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
         const uint32_t idesc = umma_idesc(KB, HEADS * p_cnt[p], 0, 0);
         const uint8_t* qb = qtile + p_first[p] * kQTile;
         for (int kb = split; kb < p_blocks[p]; kb += nsplit, ++it) {
-          const int s = it % SA, b = it & 1;
+          const int s = it % NS, b = it & 1;
           if (!mbar_wait(&tempty[b], ((it >> 1) & 1) ^ 1, abort_flag, 13)) {
             ok = false;
             break;
           }
-          if (!mbar_wait(&full[s], (it / SA) & 1, abort_flag, 14)) {
+          if (!mbar_wait(&full[s], (it / NS) & 1, abort_flag, 14)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t d = tmem_base + b * 256;
+          const uint32_t d = tmem_base + b * (a.tg * HEADS);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_f8(d, umma_desc_k128(atiles + s * kATile, k * 32), umma_desc_k128(qb, k * 32), idesc, k > 0);
@@ -214,7 +219,7 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
           break;
         }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * 256;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * (a.tg * HEADS);
         for (int c = 0; c < p_cnt[p]; ++c) {
           const int g = p_first[p] + c;
           const float* w = wfs + g * HEADS;
@@ -236,7 +241,7 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
 }
 
 }  // namespace
@@ -270,9 +275,11 @@ DSV4_API int dsv4_indexer_logits_mma(const void* qc, const float* wf, const void
       return 476;
     set = true;
   }
-  IdxArgs a{wf, kscale, slots, pos, page_table, ld_pt, ps, logits, width, t, tg, box_rows};
+  const int stages = tg == 1 ? 4 : SA;
+  const int tmem_cols = tg == 1 ? 128 : tg == 2 ? 256 : 512;
+  IdxArgs a{wf, kscale, slots, pos, page_table, ld_pt, ps, logits, width, t, tg, box_rows, stages, tmem_cols};
   const int groups = (t + tg - 1) / tg;
   if (nsplit < 1) nsplit = 1;
-  dsv4_launch(indexer_logits_mma_kernel, dim3(nsplit, groups), 192, kSmemBytes, st, tmK, tmQ, a);
+  dsv4_launch(indexer_logits_mma_kernel, dim3(nsplit, groups), 192, idx_smem_bytes(tg, stages), st, tmK, tmQ, a);
   return (int)cudaGetLastError();
 }

@@ -257,7 +257,9 @@ def indexer_logits(qc, wf, vals, scales, slots, positions, pt, ps: int, width: i
         tg = 4 if (prefill and t >= 4) else 1
         groups = (t + tg - 1) // tg
         nblocks = (width + 127) // 128
-        nsplit = max(1, min(nblocks, -(-2 * num_sms(qc.device) // groups)))
+        # one-token groups fit three CTAs on an SM (smaller ring, 128 tensor-memory columns), wider groups one
+        ctas = (3 if tg == 1 else 2) * num_sms(qc.device)
+        nsplit = max(1, min(nblocks, -(-ctas // groups)))
         nv.call("indexer_logits_mma", nv.ptr(qc), nv.ptr(wf), nv.ptr(vals), nv.ptr(scales), L(vals.shape[0]),
                 _i32(slots), _i32(positions), _i32(pt), I(pt.stride(0)), I(ps), nv.ptr(logits), I(width), I(t), I(h),
                 I(d), I(tg), I(nsplit))
