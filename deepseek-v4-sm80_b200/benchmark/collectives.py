@@ -208,8 +208,12 @@ def main(argv=None):
             ag_s[rank * plan.rpr:(rank + 1) * plan.rpr] = ys_own
             full_q = torch.empty(mp, H, device=dev, dtype=torch.uint8)
             full_s = torch.empty(mp, H // 128, device=dev, dtype=torch.float32)
+            full_y = torch.empty(mp, H, device=dev, dtype=torch.bfloat16)
+            y_own = torch.randn(plan.rpr, H, device=dev, generator=g).to(torch.bfloat16)
 
             def ag_nccl():
+                # the same three tensors the fused form delivers: the block's other consumers read the bf16 rows
+                dist.all_gather_into_tensor(full_y, y_own)
                 dist.all_gather_into_tensor(full_q, yq_own.view(torch.uint8))
                 dist.all_gather_into_tensor(full_s, ys_own)
                 O.gemm_fp8(full_q.view(torch.float8_e4m3fn)[:m], full_s[:m], waq, was)

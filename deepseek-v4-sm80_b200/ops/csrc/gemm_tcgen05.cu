@@ -325,13 +325,30 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if constexpr (sizeof(OutT) == 2) {
         const int rpr = g.sp.rows_per_rank;
         const int owner = m0 / rpr;                 // a 128-row tile has one owner (rpr is a multiple of 128)
-        if (write_out && grow < M) {
-          OutT* dst0 = reinterpret_cast<OutT*>(g.sp.peer[owner] + g.sp.rs_off) +
-                       ((size_t)g.sp.rank * rpr + (grow - owner * rpr)) * N;
+        // Stage the bf16 tile in shared memory (the pipeline stages are idle by now) and store it row-contiguously:
+        // consecutive threads write consecutive 16-byte pieces of a row, so a warp's store is a few 64-128-byte
+        // segments instead of 32 pieces 8 KB apart -- over NVLink every separate piece is a packet of its own.
+        constexpr int LD = BN + 8;                                   // padded row (elements): conflict-free 16-byte access
+        __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(tiles);
+        if (write_out) {
 #pragma unroll
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col = n0 + c * 32;
-            if (col < N) store_row_chunk(dst0 + col, &acc[c * 32], N - col);
+          for (int j = 0; j < BN; j += 8) {
+            uint4 u;
+            __nv_bfloat162* pu = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) pu[e2] = __floats2bfloat162_rn(acc[j + 2 * e2], acc[j + 2 * e2 + 1]);
+            *reinterpret_cast<uint4*>(stg + (size_t)row * LD + j) = u;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (write_out) {
+          OutT* base = reinterpret_cast<OutT*>(g.sp.peer[owner] + g.sp.rs_off) + (size_t)g.sp.rank * rpr * N;
+          constexpr int CPR = BN / 8;                                // 16-byte pieces per tile row
+          for (int i = threadIdx.x - 64; i < kBM * CPR; i += 128) {
+            const int r = i / CPR, cc = i % CPR, gr = m0 + r, col = n0 + cc * 8;
+            if (gr < M && col < N)
+              st_peer16(base + (size_t)(gr - owner * rpr) * N + col,
+                        *reinterpret_cast<const uint4*>(stg + (size_t)r * LD + cc * 8));
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -36,7 +36,7 @@ def _counters(device) -> torch.Tensor:
 
 def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int = 0, splits: int = 0):
     """(tile width, K splits) that put roughly one CTA on every SM."""
-    mt = (m + 127) // 128 * batches
+    mt = max((m + 127) // 128 * batches, 1)      # m == 0 (nothing to do) must not divide by zero below
     if bn == 0:
         fill = NUM_SMS_HINT * 2 // 3
         if mt == 1:
@@ -123,7 +123,7 @@ def gemm_bf16_partials(x, w, splits: int = 0, gate=None):
     n = w.shape[0]
     k_tiles = (k + 63) // 64
     if splits <= 0:
-        ctas = ((m + 127) // 128) * ((n + 31) // 32)
+        ctas = max(((m + 127) // 128) * ((n + 31) // 32), 1)      # m may be 0 (a rank that owns no rows)
         splits = max(1, min(NUM_SMS_HINT // ctas, k_tiles // 4, 64))
     if not x.is_cuda:
         per = (k_tiles + splits - 1) // splits * 64

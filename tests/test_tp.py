@@ -14,7 +14,12 @@ def _run(nproc, extra, port, env_extra=None, timeout=900):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "tp_worker.py")] + extra
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    log_dir = os.environ.get("MINISGL_TEST_LOG_DIR")
+    if log_dir and os.path.isdir(log_dir):       # keep the workers' complete output (a traceback scrolls out of a tail)
+        with open(os.path.join(log_dir, f"tp_worker_n{nproc}.log"), "w") as f:
+            f.write(r.stdout + "\n---- stderr ----\n" + r.stderr)
+    first_tb = r.stderr.find("Traceback")
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[max(first_tb, 0):][:3000]
     assert r.stdout.count("OK") >= nproc, r.stdout[-2000:]
 
 
