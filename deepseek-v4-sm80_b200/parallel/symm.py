@@ -143,10 +143,13 @@ class SymmComm(Comm):
             self._enable_big(hidden, max_rows)
         from ..utils.logger import init_logger
 
+        if self.sp_min_rows > 0 and not _SKIP_EXCHANGE:
+            self._check_sp(hidden, min(max_rows, 1024))
         init_logger(__name__).info_rank0(
-            "NVLink communicator: %d ranks, multicast mapping %s, in-switch reductions %s, block-wise prefill path %s",
-            self.size, "yes" if self.has_multicast else "no", "on" if self.multimem else "off",
-            "on" if self.big else "off")
+            "NVLink communicator: %d ranks, multicast mapping %s, in-switch reductions %s, block-wise prefill path %s, "
+            "row-sharded prefill %s", self.size, "yes" if self.has_multicast else "no",
+            "on" if self.multimem else "off", "on" if self.big else "off",
+            f"from {self.sp_min_rows} rows" if self.sp_min_rows > 0 else "off")
 
     @property
     def mode(self) -> str:
@@ -156,6 +159,63 @@ class SymmComm(Comm):
         self.big = on
         for x in self.ctx:
             x.big = 1 if on else 0
+
+    def _check_sp(self, hidden: int, rows: int) -> None:
+        """Start-up check of the row-sharded exchange on this machine and world size: an all-gather push followed by
+        a gated GEMM must reproduce the plain GEMM over the full tensor bit for bit, and a reduce-scatter GEMM must
+        agree with GEMM + NCCL.  A failure (or a wait that ran out) switches the row-sharded prefill off on all ranks
+        together; prefill then keeps replicated activations and the all-reduce paths."""
+        from ..ops import api as O
+        from ..ops import quant
+        from ..ops.gemm import gemm_fp8_gated
+        from ..utils.logger import init_logger
+
+        rows = rows - rows % 8 + 5            # ragged: the last row block is partial, the last rank may own less
+        plan = SpPlan(rows, self.rank, self.size)
+        good = plan.tpad <= self.sp_tpad_max
+        status = [0]
+        if good:
+            g = torch.Generator(device="cpu").manual_seed(777)                 # the same tensor on every rank
+            xf = torch.randn(rows, hidden, generator=g).to(torch.bfloat16).to(self.device)
+            w = (torch.randn(256, hidden, generator=g) * 0.02).to(self.device)
+            wq, wc = quant.fp8_weight_quant(w)
+            ws = quant.e8m0_decode(wc)
+            xq, sx = O.fp8_quant(xf)
+            ag_y, ag_q, ag_s = self.sp_buffers(plan, self.CH_ATTN)
+            r0, n = plan.row0, plan.n_own
+            ag_y[r0:r0 + n] = xf[r0:r0 + n]
+            ag_q[r0:r0 + n] = xq[r0:r0 + n]
+            ag_s[r0:r0 + n] = sx[r0:r0 + n]
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+            gate = self.sp_all_gather(plan, self.CH_ATTN)
+            got = gemm_fp8_gated(ag_q[:rows], ag_s[:rows], wq, ws, gate)
+            want = O.gemm_fp8(xq, sx, wq, ws)
+            torch.cuda.synchronize(self.device)
+            good = bool(torch.equal(got, want)) and bool(torch.equal(ag_y[:rows], xf))
+            # reduce-scatter: every rank contributes a different K shard
+            g2 = torch.Generator(device="cpu").manual_seed(900 + self.rank)
+            xr = torch.randn(rows, 512, generator=g2).to(torch.bfloat16).to(self.device)
+            w2 = (torch.randn(hidden, 512, generator=g2) * 0.02).to(self.device)
+            w2q, w2c = quant.fp8_weight_quant(w2)
+            w2s = quant.e8m0_decode(w2c)
+            xq2, sx2 = O.fp8_quant(xr)
+            full = O.gemm_fp8(xq2, sx2, w2q, w2s, out_dtype=torch.float32)
+            dist.all_reduce(full, group=self.group)
+            own = self.sp_gemm_fp8_reduce_scatter(plan, self.CH_ATTN, xq2, sx2, w2q, w2s)
+            torch.cuda.synchronize(self.device)
+            status = nv.read_status(clear=True)
+            if n > 0:
+                ref = full[r0:r0 + n]
+                good = good and float((own.float() - ref).abs().max()) <= 0.02 * float(ref.abs().max()) + 1e-3
+            good = good and status[0] == 0
+        flag = torch.tensor([1 if good else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self.sp_min_rows = 0
+            init_logger(__name__).warning("row-sharded exchange failed its start-up check (status %s); prefill keeps "
+                                          "replicated activations", status[:4])
+        self.counters["sp_all_gather"] = self.counters["sp_reduce_scatter"] = 0
 
     def _set_multimem(self, on: bool) -> None:
         self.multimem = on
