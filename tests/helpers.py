@@ -30,6 +30,10 @@ class MiniRunner:
 
     def step(self, chunks):
         """chunks: list of (slot, token_ids list) appended at the slot's current length. Returns logits [B,V]."""
+        return self.model.forward(self.make_fb(chunks))
+
+    def make_fb(self, chunks):
+        """The ForwardBatch of ``step`` (pages allocated, lengths advanced) without running the model."""
         ids, pos, slots, last = [], [], [], []
         for slot, toks in chunks:
             n0 = self.lens.get(slot, 0)
@@ -43,7 +47,6 @@ class MiniRunner:
         pos_t = torch.tensor(pos, dtype=torch.int32, device=dev)
         slot_t = torch.tensor(slots, dtype=torch.int32, device=dev)
         out_loc = self.page_table[slot_t.long(), pos_t.long()]
-        fb = ForwardBatch(torch.tensor(ids, dtype=torch.int32, device=dev), pos_t, slot_t, out_loc,
-                          torch.tensor(last, dtype=torch.int64, device=dev), self.page_table,
-                          is_prefill=any(len(t) > 1 for _, t in chunks), max_context=max(self.lens.values()))
-        return self.model.forward(fb)
+        return ForwardBatch(torch.tensor(ids, dtype=torch.int32, device=dev), pos_t, slot_t, out_loc,
+                            torch.tensor(last, dtype=torch.int64, device=dev), self.page_table,
+                            is_prefill=any(len(t) > 1 for _, t in chunks), max_context=max(self.lens.values()))
