@@ -271,9 +271,14 @@ class DSV4Model:
         for blk, fn, norm, ch in (("hc_attn", self.attention, "attn_norm", c.CH_ATTN),
                                   ("hc_ffn", self.moe, "ffn_norm", c.CH_MOE)):
             ag_y, ag_q, ag_s = c.sp_buffers(plan, ch)
-            _, post, comb, _ = O.hc_pre(x_own, w[p + blk + ".fn"], w[p + blk + ".scale"], w[p + blk + ".base"],
-                                        cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps, w[p + norm + ".weight"],
-                                        want_q=True, out=(ag_y[r0:r0 + n], ag_q[r0:r0 + n], ag_s[r0:r0 + n]))
+            if n > 0:
+                _, post, comb, _ = O.hc_pre(x_own, w[p + blk + ".fn"], w[p + blk + ".scale"], w[p + blk + ".base"],
+                                            cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_norm_eps,
+                                            w[p + norm + ".weight"], want_q=True,
+                                            out=(ag_y[r0:r0 + n], ag_q[r0:r0 + n], ag_s[r0:r0 + n]))
+            else:   # a short prompt leaves the last ranks without rows: they still take part in both exchanges
+                post = torch.empty(0, cfg.hc_mult, dtype=torch.float32, device=x_own.device)
+                comb = torch.empty(0, cfg.hc_mult, cfg.hc_mult, dtype=torch.float32, device=x_own.device)
             gate = c.sp_all_gather(plan, ch)
             x_own = fn(l, ag_y[:t], fb, (ag_q[:t], ag_s[:t]), (x_own, post, comb), sp=(plan, gate))
         return x_own
@@ -281,7 +286,11 @@ class DSV4Model:
     def _forward_sp(self, fb: ForwardBatch, plan, greedy):
         cfg, w, c = self.cfg, self.w, self.comm
         r0, n = plan.row0, plan.n_own
-        x_own = O.embed(fb.input_ids[r0:r0 + n], w["embed.weight"], cfg.hc_mult)
+        if n > 0:
+            x_own = O.embed(fb.input_ids[r0:r0 + n], w["embed.weight"], cfg.hc_mult)
+        else:
+            x_own = torch.empty(0, cfg.hc_mult, cfg.hidden_size, dtype=w["embed.weight"].dtype,
+                                device=fb.input_ids.device)
         for l in range(cfg.num_layers):
             x_own = self.layer_sp(l, x_own, fb, plan)
         # the rows whose logits are wanted live on their owners: every rank contributes its own ones, zeros elsewhere

@@ -218,6 +218,17 @@ def _checks():
         assert comm.counters["sp_all_gather"] == 2 + 2 * cfg.num_layers, comm.counters
         assert rel(l_sp, l_tp) < 0.1, ("row-sharded vs replicated", rel(l_sp, l_tp))
         assert rel(l_sp, l_1) < 0.2, rel(l_sp, l_1)
+        # 3c) a prompt so short that the last rank owns no row at all (one 128-row block for the whole prompt)
+        comm.sp_min_rows = 64
+        short = toks[:100]
+        s_sp = MiniRunner(cfg, dev, comm=comm, moe_mode=args.moe_mode, rank=rank, size=world, seed=2, **kw)
+        l_short = s_sp.step([(0, short)])
+        comm.sp_min_rows = 0
+        s_tp = MiniRunner(cfg, dev, comm=comm, moe_mode=args.moe_mode, rank=rank, size=world, seed=2, **kw)
+        l_short_tp = s_tp.step([(0, short)])
+        torch.cuda.synchronize()
+        native.assert_device_ok()
+        assert rel(l_short, l_short_tp) < 0.1, ("short row-sharded prompt", rel(l_short, l_short_tp))
         comm.sp_min_rows = 1024
         print(f"OK cuda rank {rank} rel {rel(l_tp, l_1):.4f} counters {comm.counters}", flush=True)
 
