@@ -65,6 +65,10 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
   return v;
 }
 
+// Bulk data for a peer: a plain (weak) 16-byte store.  Unlike the volatile form it may be merged with its neighbours
+// on the way to the link; the writer's system-scope fence before it raises the flag makes the data visible.
+__device__ __forceinline__ void st_bulk16(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+
 __device__ __forceinline__ void st_peer16(void* p, const uint4& v) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");

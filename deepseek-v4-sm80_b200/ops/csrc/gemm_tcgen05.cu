@@ -347,7 +347,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int i = threadIdx.x - 64; i < kBM * CPR; i += 128) {
             const int r = i / CPR, cc = i % CPR, gr = m0 + r, col = n0 + cc * 8;
             if (gr < M && col < N)
-              st_peer16(base + (size_t)(gr - owner * rpr) * N + col,
+              st_bulk16(base + (size_t)(gr - owner * rpr) * N + col,
                         *reinterpret_cast<const uint4*>(stg + (size_t)r * LD + cc * 8));
           }
         }

@@ -770,7 +770,7 @@ __global__ void __launch_bounds__(256) moe_finalize_rs_kernel(const __nv_bfloat1
       const float2 s2 = __bfloat1622float2(spv[j]);
       po[j] = __floats2bfloat162_rn(r2.x + s2.x, r2.y + s2.y);
     }
-    st_peer16(dst + i, o);
+    st_bulk16(dst + i, o);
   }
   __syncthreads();
   if (threadIdx.x == 0) {

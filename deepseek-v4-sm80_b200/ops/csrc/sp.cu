@@ -14,7 +14,7 @@ __device__ __forceinline__ void sp_store16_all(const SpCtx& c, size_t off, const
   } else {
 #pragma unroll
     for (int p = 0; p < kMaxRanks; ++p)
-      if (p < c.world && p != c.rank) st_peer16(c.peer[p] + off, v);
+      if (p < c.world && p != c.rank) st_bulk16(c.peer[p] + off, v);
   }
 }
 

@@ -190,7 +190,7 @@ class SymmComm(Comm):
             dist.barrier(group=self.group)
             gate = self.sp_all_gather(plan, self.CH_ATTN)
             got = gemm_fp8_gated(ag_q[:rows], ag_s[:rows], wq, ws, gate)
-            want = O.gemm_fp8(xq, sx, wq, ws)
+            want = O.gemm_fp8(xq, sx, wq, ws, splits=1)       # the gated GEMM does not split K: same summation order
             torch.cuda.synchronize(self.device)
             good = bool(torch.equal(got, want)) and bool(torch.equal(ag_y[:rows], xf))
             # reduce-scatter: every rank contributes a different K shard

@@ -81,6 +81,7 @@ def _checks():
 
         assert isinstance(comm, SymmComm), type(comm)
         assert comm.big, "the block-wise two-shot path failed its start-up check"
+        assert comm.sp_min_rows > 0, "the row-sharded exchange failed its start-up check"
         if comm.has_multicast and os.environ.get("MINISGL_DISABLE_MULTIMEM", "0") != "1":
             assert comm.multimem, "the in-switch all-reduce failed its start-up check"
         print(f"rank {rank}: multicast {comm.has_multicast} multimem {comm.multimem} big {comm.big}", flush=True)
@@ -216,7 +217,7 @@ def _checks():
         torch.cuda.synchronize()
         native.assert_device_ok()
         assert comm.counters["sp_all_gather"] == 2 + 2 * cfg.num_layers, comm.counters
-        assert rel(l_sp, l_tp) < 0.1, ("row-sharded vs replicated", rel(l_sp, l_tp))
+        assert rel(l_sp, l_tp) < 0.2, ("row-sharded vs replicated", rel(l_sp, l_tp))   # same bound as sharded vs single
         assert rel(l_sp, l_1) < 0.2, rel(l_sp, l_1)
         # 3c) a prompt so short that the last rank owns no row at all (one 128-row block for the whole prompt)
         comm.sp_min_rows = 64
@@ -228,7 +229,7 @@ def _checks():
         l_short_tp = s_tp.step([(0, short)])
         torch.cuda.synchronize()
         native.assert_device_ok()
-        assert rel(l_short, l_short_tp) < 0.1, ("short row-sharded prompt", rel(l_short, l_short_tp))
+        assert rel(l_short, l_short_tp) < 0.2, ("short row-sharded prompt", rel(l_short, l_short_tp))
         comm.sp_min_rows = 1024
         print(f"OK cuda rank {rank} rel {rel(l_tp, l_1):.4f} counters {comm.counters}", flush=True)
 
