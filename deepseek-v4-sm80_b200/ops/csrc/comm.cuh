@@ -309,8 +309,10 @@ __device__ __forceinline__ bool comm_use_two_shot(const CommCtx& c, int rows, in
 // the exchange makes progress whenever the grid is co-resident (the launchers size it so); every wait is bounded.
 // Per rank this moves 2 * (world-1)/world of the tensor over NVLink; the one-shot form moves (world-1) times it.
 // emit(row, col, v) receives 8 reduced bf16 values.
-__device__ __forceinline__ int comm_big_block_rows(int rows) {
-  int r = 8;
+// Rows per block: every block costs two flag exchanges, so large tensors use larger blocks (about two passes per CTA
+// at 8 192 rows) and small ones keep 8-row blocks so that every SM has work.
+__host__ __device__ __forceinline__ int comm_big_block_rows(int rows) {
+  int r = rows > 4096 ? 32 : rows > 2048 ? 16 : 8;
   while ((rows + r - 1) / r > kTwoShotSlot) r *= 2;
   return r;
 }
@@ -341,18 +343,20 @@ __device__ __forceinline__ void comm_big_two_shot(const CommCtx& c, uint32_t epo
     __syncthreads();
     const int ok = *sh_ok;
     if (owner == c.rank && ok && use_mm) {
-      // the block's rows are contiguous: four independent switch reductions per thread and trip
+      // the block's rows are contiguous: eight independent switch reductions per thread and trip (a reduction is a
+      // round trip through the switch, so the bytes in flight per SM decide the rate)
+      constexpr int U = 8;
       const int c8 = cols / 8, n8 = (r1 - r0) * c8;
       __nv_bfloat16* mcb = comm_mc_data(c, parity) + (size_t)r0 * cols;
-      for (int i = threadIdx.x; i < n8; i += blockDim.x * 4) {
-        uint4 v[4];
+      for (int i = threadIdx.x; i < n8; i += blockDim.x * U) {
+        uint4 v[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
           const int j = i + u * (int)blockDim.x;
           if (j < n8) v[u] = mm_ld_reduce16(mcb + (size_t)j * 8);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
           const int j = i + u * (int)blockDim.x;
           if (j < n8) {
             mm_st16(mcb + (size_t)j * 8, v[u]);
@@ -428,8 +432,7 @@ __device__ __forceinline__ void comm_big_two_shot(const CommCtx& c, uint32_t epo
 }
 // Grid of a kernel on the block-wise path: one CTA of 256 threads per SM at most, so that all of them are co-resident.
 inline int comm_big_grid(int rows) {
-  int r = 8;
-  while ((rows + r - 1) / r > kTwoShotSlot) r *= 2;
+  const int r = comm_big_block_rows(rows);
   const int nblk = (rows + r - 1) / r;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
