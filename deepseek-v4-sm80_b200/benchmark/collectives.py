@@ -195,6 +195,8 @@ def main(argv=None):
             res["wo_b_rs_gemm_plus_nccl_us"] = _time_eager(rs_nccl, it)
             res["wo_b_rs_fused_us"] = _time_eager(
                 lambda: comm.sp_gemm_fp8_reduce_scatter(plan, comm.CH_ATTN, xq, sx, wq, ws), it)
+            res["wo_b_rs_push_us"] = _time_eager(
+                lambda: comm.sp_gemm_fp8_reduce_scatter(plan, comm.CH_ATTN, xq, sx, wq, ws, push=True), it)
             rs_link = (world - 1) / world * m * H * 2 / (NVLINK_GBS * 1e3)
             res["wo_b_rs_roofline_us"] = max(flops / (tflops * 1e6), rs_link)
             res["wo_b_rs_roofline_frac"] = res["wo_b_rs_roofline_us"] / res["wo_b_rs_fused_us"]

@@ -321,6 +321,33 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (warp == 2 && lane == 0) g.counters[tile] = 0;
       }
     }
+    if (g.sp_mode == 3) {
+      // reduce-scatter through the switch: leave the partial tile in this rank's own buffer (row-major [T, N] at the
+      // same offset on every rank) and tell the tile's owner; the owner's sp_rs_reduce_kernel then asks the switch
+      // for the sum of all ranks' copies of its rows (multimem.ld_reduce), so no partial row crosses NVLink twice
+      if constexpr (sizeof(OutT) == 2) {
+        const int rpr = g.sp.rows_per_rank;
+        const int owner = m0 / rpr;
+        if (write_out && grow < M) {
+          OutT* dst0 = reinterpret_cast<OutT*>(g.sp.peer[g.sp.rank] + g.sp.rs_off) + (size_t)grow * N;
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = n0 + c * 32;
+            if (col < N) store_row_chunk(dst0 + col, &acc[c * 32], N - col);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          __threadfence_system();
+          if (atomicAdd(&g.sp_counters[blockIdx.y], 1) == (int)gridDim.x - 1) {
+            g.sp_counters[blockIdx.y] = 0;
+            __threadfence_system();
+            st_relaxed_sys(sp_flag(g.sp, owner, kSpRS, g.sp.rank, (m0 - owner * rpr) >> 7), g.sp.seq);
+          }
+        }
+      }
+      write_out = false;
+    }
     if (g.sp_mode == 2) {
       if constexpr (sizeof(OutT) == 2) {
         const int rpr = g.sp.rows_per_rank;
@@ -496,7 +523,7 @@ int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, in
              o.out_col_pb, o.splits, o.ws, o.counters, o.deposit_only, g_weight_prefetch, o.cluster, o.partial_stride,
              o.sp_mode, o.sp_counters, o.sp ? *o.sp : SpCtx{}};
   if (o.sp_mode && (!o.sp || o.sp->rows_per_rank % kBM || o.batches != 1)) return 106;
-  if (o.sp_mode == 2 && (o.splits != 1 || !o.sp_counters)) return 107;
+  if (o.sp_mode >= 2 && (o.splits != 1 || !o.sp_counters)) return 107;
   if (o.cluster) {
     if (o.splits != 2 && o.splits != 4 && o.splits != 8) return 105;
     dsv4_launch_cluster(kern, grid, 192, Cfg::kSmemBytes, stream, o.splits, tmA, tmB, out, g, comm);
@@ -632,7 +659,7 @@ DSV4_API int dsv4_gemm_fp8_rs(const void* x, const void* w, const float* sa, con
   if (M <= 0 || N <= 0) return 0;
   if ((K % 128) || (ldx % 16) || (ldw % 16) || (N % 8) || N != sp->hidden) return 112;
   LaunchOpts o;
-  o.sp_mode = 2;
+  o.sp_mode = (sp->use_mc && sp->mc) ? 3 : 2;   // in-switch reduction where a multicast mapping exists
   o.sp = sp;
   o.sp_counters = counters;
   return dispatch_bn<true, __nv_bfloat16>(x, w, (__nv_bfloat16*)nullptr, M, N, K, ldx, ldw, N, sa, sb, 0, bn, stream, o);

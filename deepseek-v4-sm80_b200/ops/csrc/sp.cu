@@ -58,8 +58,10 @@ __global__ void __launch_bounds__(256) sp_ag_push_kernel(const SpCtx c, int tpad
 
 // Owner side of the reduce-scatter: CTA r adds the `world` partials of local row r in rank order (all of them sit in
 // this rank's own buffer) and writes the row, or -- with the hyper-connection arguments -- the new residual streams.
+// mc_mode: the producers left their partials in their own buffers ([T, cols] at the same offset on every rank) and the
+// switch adds them (multimem.ld_reduce on the multicast mapping), instead of the ranks' partials sitting here.
 __global__ void __launch_bounds__(256) sp_rs_reduce_kernel(const SpCtx c, int cols, __nv_bfloat16* __restrict__ out,
-                                                           const HcPostArgs hc) {
+                                                           const HcPostArgs hc, int mc_mode) {
   pdl_entry();
   __shared__ int ok;
   const int row = blockIdx.x, blk = row >> 7;
@@ -71,6 +73,24 @@ __global__ void __launch_bounds__(256) sp_rs_reduce_kernel(const SpCtx c, int co
   }
   __syncthreads();
   if (!ok) return;
+  if (mc_mode) {
+    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(c.mc + c.rs_off) +
+                               ((size_t)c.rank * c.rows_per_rank + row) * cols;
+    for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 16) {
+      const int i1 = i + blockDim.x * 8;
+      const uint4 v0 = mm_ld_reduce16(src + i);
+      uint4 v1 = make_uint4(0, 0, 0, 0);
+      if (i1 < cols) v1 = mm_ld_reduce16(src + i1);
+      if (hc.res) {
+        hc_post_store8(v0, hc, row, cols, i);
+        if (i1 < cols) hc_post_store8(v1, hc, row, cols, i1);
+      } else {
+        *reinterpret_cast<uint4*>(out + (size_t)row * cols + i) = v0;
+        if (i1 < cols) *reinterpret_cast<uint4*>(out + (size_t)row * cols + i1) = v1;
+      }
+    }
+    return;
+  }
   const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(c.peer[c.rank] + c.rs_off);
   for (int i = threadIdx.x * 8; i < cols; i += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -119,11 +139,12 @@ DSV4_API int dsv4_sp_ag_push(const SpCtx* c, int tpad, int* counters, cudaStream
 // Reduces the partial rows delivered to this rank: rows = valid local rows.  out bf16 [rows, cols], or with
 // res / post / comb / xout the hyper-connection post mix of the reduced rows ([rows, 4, cols]).
 DSV4_API int dsv4_sp_rs_reduce(const SpCtx* c, int rows, int cols, void* out, const void* res, const float* post,
-                               const float* comb, void* xout, cudaStream_t st) {
+                               const float* comb, void* xout, int mc_mode, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (cols % 8 || rows > c->rows_per_rank) return 522;
   if (xout && (!res || !post || !comb)) return 523;
   HcPostArgs hc{xout ? (const __nv_bfloat16*)res : nullptr, post, comb, (__nv_bfloat16*)xout};
-  dsv4_launch(sp_rs_reduce_kernel, rows, 256, 0, st, *c, cols, (__nv_bfloat16*)out, hc);
+  if (mc_mode && !(c->use_mc && c->mc)) return 524;
+  dsv4_launch(sp_rs_reduce_kernel, rows, 256, 0, st, *c, cols, (__nv_bfloat16*)out, hc, mc_mode);
   return (int)cudaGetLastError();
 }

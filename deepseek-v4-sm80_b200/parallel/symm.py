@@ -326,19 +326,27 @@ class SymmComm(Comm):
         nv.call("sp_ag_push", ctypes.byref(ctx), I(plan.tpad), nv.ptr(self.sp_counters))
         return ctx
 
-    def sp_gemm_fp8_reduce_scatter(self, plan: SpPlan, channel: int, xq, sx, w, ws, hc=None) -> torch.Tensor:
+    def sp_gemm_fp8_reduce_scatter(self, plan: SpPlan, channel: int, xq, sx, w, ws, hc=None,
+                                   push: bool = False) -> torch.Tensor:
         """Projection of all rows by this rank's K shard, reduce-scattered: the GEMM epilogue stores every partial row
         into its owner's buffer over NVLink, the owner adds the ranks' partials.  Returns this rank's rows
-        [n_own, n], or with hc = (residual, post, comb) of the own rows the new residual streams [n_own, 4, n]."""
+        [n_own, n], or with hc = (residual, post, comb) of the own rows the new residual streams [n_own, 4, n].
+        Two forms: with a multicast mapping the epilogue leaves the partial tile in the rank's own buffer and the
+        owner's reduction is a ``multimem.ld_reduce`` (the switch adds the ranks' copies); ``push=True`` or no multicast:
+        the epilogue stores every partial row straight into its owner's buffer and the owner adds them."""
         m, k = xq.shape
         n = w.shape[0]
         self.sp_seq += 1
         self.counters["sp_reduce_scatter"] += 1
         ctx = self._sp_ctx(plan, channel, self.sp_seq)
+        if push:
+            ctx.use_mc = 0      # the epilogue stores the partial rows into the owners' buffers (no multicast needed)
         cnt = self.sp_counters[self.sp_slots:]
         nv.call("gemm_fp8_rs", nv.ptr(xq), nv.ptr(w), nv.ptr(sx), nv.ptr(ws), I(m), I(n), I(k), I(xq.stride(0)),
                 I(w.stride(0)), I(0), ctypes.byref(ctx), nv.ptr(cnt))
-        return self._sp_reduce(ctx, plan, n, hc)
+        # with a multicast mapping the GEMM leaves its partial in its own buffer and the owner's reduction asks the
+        # switch for the sum; otherwise the epilogue stored the partial rows into the owners' buffers
+        return self._sp_reduce(ctx, plan, n, hc, mc_mode=1 if ctx.use_mc else 0)
 
     def sp_moe_finalize_reduce_scatter(self, plan: SpPlan, rows, moe_plan, max_tiles, shared, t, topk, h, hc=None):
         """Expert combine of all rows on this rank's experts (+ shared expert shard), reduce-scattered like above."""
@@ -350,16 +358,16 @@ class SymmComm(Comm):
                 I(topk), I(h), ctypes.byref(ctx), nv.ptr(cnt))
         return self._sp_reduce(ctx, plan, h, hc)
 
-    def _sp_reduce(self, ctx: SpCtx, plan: SpPlan, n: int, hc):
+    def _sp_reduce(self, ctx: SpCtx, plan: SpPlan, n: int, hc, mc_mode: int = 0):
         if hc is not None:
             res, post, comb = hc
             xout = torch.empty_like(res)
             nv.call("sp_rs_reduce", ctypes.byref(ctx), I(plan.n_own), I(n), nv.ptr(None), nv.ptr(res), nv.ptr(post),
-                    nv.ptr(comb), nv.ptr(xout))
+                    nv.ptr(comb), nv.ptr(xout), I(mc_mode))
             return xout
         out = torch.empty(plan.n_own, n, dtype=torch.bfloat16, device=self.device)
         nv.call("sp_rs_reduce", ctypes.byref(ctx), I(plan.n_own), I(n), nv.ptr(out), nv.ptr(None), nv.ptr(None),
-                nv.ptr(None), nv.ptr(None))
+                nv.ptr(None), nv.ptr(None), I(mc_mode))
         return out
 
     # ------------------------------------------------------------------ collectives

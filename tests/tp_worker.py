@@ -185,11 +185,13 @@ def _checks():
             w2s = quant.e8m0_decode(w2c)
             full = O.gemm_fp8(xq, sx, w2q, w2s, out_dtype=torch.float32)
             dist.all_reduce(full)
-            own = comm.sp_gemm_fp8_reduce_scatter(plan, comm.CH_ATTN, xq, sx, w2q, w2s)
-            torch.cuda.synchronize()
-            assert own.shape[0] == n
-            if n:
-                assert rel(own, full[r0:r0 + n]) < 1e-2, ("reduce-scatter", trows, rel(own, full[r0:r0 + n]))
+            for push in (False, True):          # in-switch form (where a multicast mapping exists) and peer-store form
+                own = comm.sp_gemm_fp8_reduce_scatter(plan, comm.CH_ATTN, xq, sx, w2q, w2s, push=push)
+                torch.cuda.synchronize()
+                assert own.shape[0] == n
+                if n:
+                    assert rel(own, full[r0:r0 + n]) < 1e-2, ("reduce-scatter", push, trows,
+                                                                rel(own, full[r0:r0 + n]))
             assert native.read_status(clear=False)[0] == 0
         # 3) whole model: tensor/expert parallel vs single rank
         # (600 prompt tokens: the prefill's collectives take the block-wise path, the decode steps the row-wise one)
