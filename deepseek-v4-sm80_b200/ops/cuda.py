@@ -13,6 +13,7 @@ import torch
 from . import native as nv
 from .native import F, I, L
 from .ref import RopeSpec
+from .tensorcheck import tensors
 
 
 class RopeParams(ctypes.Structure):
@@ -55,6 +56,7 @@ def check_index(idx, lo: int, hi: int, tag: int) -> None:
     nv.call("check_index", nv.ptr(idx), ctypes.c_longlong(idx.numel()), I(lo), I(hi), I(tag))
 
 
+@tensors(ids="i32[T]", weight="bf16[_,H]", feedback="?i32[_]", slots="?i32[T]")
 def embed(ids, weight, m: int, feedback=None, slots=None):
     """feedback / slots: row t embeds token feedback[slots[t]] and writes it to ids[t]."""
     t, h = ids.shape[0], weight.shape[1]
@@ -63,6 +65,7 @@ def embed(ids, weight, m: int, feedback=None, slots=None):
     return out
 
 
+@tensors(logits="f32[R,_]s", slots="i32[R]", num_valid="?i32[1]", token_feedback="i32[_]", out="?i32[R]")
 def greedy_tokens(logits, v_base: int, slots, num_valid, token_feedback, out=None, comm_ctx=None):
     """Argmax of fp32 logits rows (this rank's vocabulary shard starting at token v_base; with comm_ctx the shards'
     candidates are exchanged inside the kernel), written to out [rows] int32 and to token_feedback[slots[row]]."""
@@ -108,6 +111,7 @@ def fp8_quant(x, block: int = 128):
     return q, s
 
 
+@tensors(gate_up="bf16[_,_]")
 def silu_mul_clamp(gate_up, limit):
     rows, two_i = gate_up.shape
     out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
@@ -115,6 +119,7 @@ def silu_mul_clamp(gate_up, limit):
     return out
 
 
+@tensors(gate_up="bf16[_,_]")
 def silu_mul_clamp_quant(gate_up, limit):
     """SwiGLU with clamp straight to (e4m3, scales); the bf16 activation is not materialised."""
     rows, two_i = gate_up.shape
@@ -127,6 +132,7 @@ def silu_mul_clamp_quant(gate_up, limit):
     return q, s
 
 
+@tensors(routed="bf16[R,H]", shared="bf16[R,H]", num_valid="?i32[1]")
 def add_cast(routed, shared, num_valid=None):
     out = torch.empty_like(routed)
     nv.call("add_cast", nv.ptr(routed), nv.ptr(shared), nv.ptr(out), I(routed.shape[0]), I(routed.shape[1]),
@@ -144,6 +150,8 @@ def rope_tail(x, positions, spec, inverse: bool = False, pos_offset: int = 0):
     return x
 
 
+@tensors(q="bf16[T,_,D]", kv="bf16[T,D]s", positions="i32[T]", kv_w="bf16[D]", swa_cache="bf16[_,D]", out_loc="i32[T]",
+         swa_map="i32[_]")
 def q_kv_norm_rope_store(q, kv, positions, kv_w, eps, spec, swa_cache, out_loc, swa_map, ps: int, qat: bool):
     t, h, d = q.shape
     assert q.is_contiguous() and kv.stride(-1) == 1
@@ -163,6 +171,7 @@ def _hc_mixes(x, fn):
     return gemm_bf16_partials(x.reshape(t, -1), fn)
 
 
+@tensors(x="bf16[T,4,H]", fn="bf16[_,_]", scale="f32[_]", base="f32[_]", norm_w="?bf16[H]")
 def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None, want_q: bool = False, out=None):
     """out = (y, q, s): preallocated result rows (the row-sharded layer passes its rows of the gathered buffer)."""
     t, m, h = x.shape
@@ -185,6 +194,7 @@ def hc_pre(x, fn, scale, base, iters, eps, norm_eps, norm_w=None, want_q: bool =
     return y, post, comb
 
 
+@tensors(y="bf16[T,H]", residual="bf16[T,4,H]", post="f32[T,4]", comb="f32[T,4,4]")
 def hc_post(y, residual, post, comb):
     t, m, h = residual.shape
     out = torch.empty_like(residual)
@@ -223,6 +233,7 @@ def compress_store(pooled, fb, norm_w, eps, spec, cache, ps: int, ratio: int):
             rope_params(spec), nv.ptr(cache), I(t), I(d), I(ps), I(ratio))
 
 
+@tensors(q="bf16[T,HI,DI]", weights="bf16[T,HI]", positions="i32[T]")
 def indexer_q_encode(q, weights, positions, spec, softmax_scale, head_scale):
     t, h, d = q.shape
     assert q.is_contiguous() and weights.is_contiguous() and weights.dtype == torch.bfloat16
@@ -247,6 +258,8 @@ def _mma_indexer_ok(h: int, d: int, ps: int) -> bool:
     return h == 64 and d == 128 and ps % 4 == 0 and rpp >= 8 and (64 % rpp == 0 or rpp % 64 == 0)
 
 
+@tensors(qc="u8[T,HI,DI]", wf="f32[T,HI]", vals="u8[_,DI]", scales="f32[_]", slots="i32[T]", positions="i32[T]",
+         pt="i32[_,_]s", out="?f32[T,_]s")
 def indexer_logits(qc, wf, vals, scales, slots, positions, pt, ps: int, width: int, prefill: bool, out=None,
                    force_scalar: bool = False):
     """fp32 logits [t, width] of the rows' compressed history (-inf past each row's length).  64 x 128 indexers run
@@ -313,6 +326,8 @@ def attention_splits(t: int, heads: int, mode: int, ratio: int, topk_width: int,
     return int(max(1, min(sms // t, -(-ntiles // 2), 32)))
 
 
+@tensors(q="bf16[T,H,512]", swa_cache="bf16[_,512]", swa_map="i32[_]", comp_cache="?bf16[_,512]", topk_idx="?i32[T,_]",
+         topk_len="?i32[T]", sink="f32[H]")
 def attention(q, fb, swa_cache, swa_map, comp_cache, ratio: int, topk_idx, topk_len, sink, scale, ps: int,
               window: int, out_rope=None, nsplit: int = 0):
     """out_rope: RopeSpec whose inverse rotation the kernel applies to the tail of every output row.
@@ -367,6 +382,7 @@ def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_va
     return idx, wts
 
 
+@tensors(y="bf16[T,H]", idx="i32[T,K]", w="f32[T,K]", w13="i8|u8[E,_,_]", s13="u8[E,_,_]", w2="i8|u8[E,H,_]", s2="u8[E,H,_]")
 def moe_routed(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
     """Returns (route_rows bf16 [T*topk, H], plan int32) for :func:`moe_finalize`."""
     t, h = y.shape
@@ -411,6 +427,7 @@ def moe_experts(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
 
 
 # --------------------------------------------------------------------------- sampling
+@tensors(logits="f32[_,_]")
 def argmax(logits):
     b, v = logits.shape
     out = torch.empty(b, dtype=torch.int64, device=logits.device)
@@ -418,6 +435,7 @@ def argmax(logits):
     return out
 
 
+@tensors(logits="f32[B,_]", temperature="f32[B]", top_k="i32[B]", top_p="f32[B]", uniform="f32[B]", mask_ids="?i32[B,_]")
 def sample(logits, temperature, top_k, top_p, uniform, mask_ids=None):
     b, v = logits.shape
     out = torch.empty(b, dtype=torch.int64, device=logits.device)
