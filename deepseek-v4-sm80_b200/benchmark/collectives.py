@@ -108,6 +108,8 @@ def main(argv=None):
     ap.add_argument("--rows", type=int, nargs="+", default=[1, 8, 32, 128, 256, 8192])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default="")
+    ap.add_argument("--allreduce-only", action="store_true",
+                    help="time the all-reduce forms only (plain, behind wo_b, behind the MoE combine)")
     a = ap.parse_args(argv)
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -143,7 +145,8 @@ def main(argv=None):
         nccl_buf = x.clone()
         link_bytes = (world - 1) * m * H * 2
         t_link = link_bytes / (NVLINK_GBS * 1e3)  # us
-        res = {"rows": m, "world": world, "block_two_shot": bool(getattr(comm, "big", False) and m > 256)}
+        big_min = int(comm.ctx[0].big) if getattr(comm, "ctx", None) else 0
+        res = {"rows": m, "world": world, "block_two_shot": bool(big_min and m > big_min)}
         res["allreduce_nccl_us"] = _time(lambda: dist.all_reduce(nccl_buf), a.iters, True)
         res["allreduce_ours_us"] = _time(lambda: comm.all_reduce(x), a.iters, True)
 
@@ -180,7 +183,7 @@ def main(argv=None):
         from minisgl.parallel.symm import SpPlan
 
         plan = SpPlan(m, rank, world)
-        if plan.tpad <= comm.sp_tpad_max:
+        if plan.tpad <= comm.sp_tpad_max and not a.allreduce_only:
             it = a.iters
             mp = plan.tpad
             pad_x = torch.zeros(mp, KO, device=dev, dtype=torch.bfloat16)

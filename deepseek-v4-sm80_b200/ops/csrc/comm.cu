@@ -7,7 +7,7 @@
 
 namespace {
 
-// BIG: the block-wise two-shot path for tensors of more than 256 rows (own instantiation: the row-wise paths of a
+// BIG: the block-wise two-shot path for tensors of more than comm.big rows (own instantiation: the row-wise paths of a
 // decode step keep their register allocation).
 template <bool BIG>
 __global__ void __launch_bounds__(256) allreduce_kernel(const __nv_bfloat16* __restrict__ x,

@@ -23,7 +23,7 @@ struct CommCtx {
   uint8_t* peer[kMaxRanks];   // symmetric base of every rank (peer[rank] is local)
   int rank, world;
   int channel;
-  int big;                    // 1: tensors of more than 256 rows use the block-wise two-shot path
+  int big;                    // > 0: tensors of more than `big` rows use the block-wise two-shot path (0: never)
   long long data_bytes;       // bytes of one parity buffer of one channel
   long long small_bytes;      // bytes of one result buffer of the two-shot path (0: none)
   int* epoch;                 // local [kCommChannels] device ints
@@ -310,13 +310,13 @@ __device__ __forceinline__ bool comm_use_two_shot(const CommCtx& c, int rows, in
 // Per rank this moves 2 * (world-1)/world of the tensor over NVLink; the one-shot form moves (world-1) times it.
 // emit(row, col, v) receives 8 reduced bf16 values.
 // Rows per block: every block costs two flag exchanges, so large tensors use larger blocks (about two passes per CTA
-// at 8 192 rows) and small ones keep 8-row blocks so that every SM has work.
+// at 8 192 rows) and small ones use 8-, 4- or 2-row blocks so that a hundred or more CTAs have work.
 __host__ __device__ __forceinline__ int comm_big_block_rows(int rows) {
-  int r = rows > 4096 ? 32 : rows > 2048 ? 16 : 8;
+  int r = rows > 4096 ? 32 : rows > 2048 ? 16 : rows > 512 ? 8 : rows > 256 ? 4 : 2;
   while ((rows + r - 1) / r > kTwoShotSlot) r *= 2;
   return r;
 }
-inline bool comm_host_use_big(const CommCtx& c, int rows) { return c.world > 1 && c.big && rows > 256; }
+inline bool comm_host_use_big(const CommCtx& c, int rows) { return c.world > 1 && c.big > 0 && rows > c.big; }
 // With c.mm set, the owner's reduction is one multimem.ld_reduce per 16 bytes (the switch adds the ranks' partials)
 // and its result goes to all ranks with one multimem.st; the second flag is one multicast store as well.  Per rank
 // that is (world-1)/world of the tensor in each NVLink direction, half of what the peer-to-peer form moves.

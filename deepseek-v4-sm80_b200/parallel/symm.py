@@ -29,8 +29,11 @@ from .info import DistributedInfo
 import os as _os
 
 _SKIP_EXCHANGE = _os.environ.get("MINISGL_SKIP_EXCHANGE", "0") == "1"
-# MINISGL_BIG_ALLREDUCE=0 keeps tensors of more than 256 rows (prefill) on the one-shot exchange.
+# MINISGL_BIG_ALLREDUCE=0 keeps large tensors (prefill) on the one-shot exchange; with it on, tensors of more than
+# MINISGL_BIG_MIN_ROWS rows take the block-wise two-shot path (the one-shot form moves world-1 times the tensor out of
+# every GPU, the two-shot form (world-1)/world of it, at the price of a second flag round trip).
 _BIG = _os.environ.get("MINISGL_BIG_ALLREDUCE", "1") == "1"
+_BIG_MIN_ROWS = max(int(_os.environ.get("MINISGL_BIG_MIN_ROWS", "128")), 1)
 
 MAX_RANKS = 8
 
@@ -158,7 +161,7 @@ class SymmComm(Comm):
     def _set_big(self, on: bool) -> None:
         self.big = on
         for x in self.ctx:
-            x.big = 1 if on else 0
+            x.big = _BIG_MIN_ROWS if on else 0
 
     def _check_sp(self, hidden: int, rows: int) -> None:
         """Start-up check of the row-sharded exchange on this machine and world size: an all-gather push followed by
@@ -260,14 +263,14 @@ class SymmComm(Comm):
     def _enable_big(self, hidden: int, max_rows: int) -> None:
         """Switch the block-wise two-shot path on, reduce tensors with it and with NCCL, and keep it only if every
         rank saw the same sums and no wait ran out (otherwise all ranks fall back to the one-shot exchange together).
-        Two sizes are checked: ``max_rows`` rows -- the largest prefill forward, with more 8-row blocks than CTAs, so
-        that every CTA runs several passes and the owner of its blocks rotates through all ranks -- and a ragged
-        row count that ends in a partial block."""
+        Checked sizes: ``max_rows`` rows -- the largest prefill forward, with more 8-row blocks than CTAs, so
+        that every CTA runs several passes and the owner of its blocks rotates through all ranks --, a ragged
+        row count that ends in a partial block, and the smallest tensor that takes this path."""
         from ..utils.logger import init_logger
 
         good, status = True, [0]
         self._set_big(True)
-        for rows in (max_rows, max(max_rows // 2 - 3, 257)):
+        for rows in (max_rows, max(max_rows // 2 - 3, 257), _BIG_MIN_ROWS + 1):
             g = torch.Generator(device="cpu").manual_seed(1234 + self.rank)
             x = torch.randn(rows, hidden, generator=g).to(self.device, torch.bfloat16)
             want = x.float()
@@ -381,7 +384,7 @@ class SymmComm(Comm):
 
     def gemm_fp8_allreduce(self, xq, sx, w, ws, bn: int = 0, hc=None) -> torch.Tensor:
         """out = all_reduce(xq @ w^T).  The GEMM deposits its partial product in the channel's symmetric buffer and the
-        all-reduce kernel follows as its programmatic dependent: row-wise up to 256 rows (decode; its peer reads are
+        all-reduce kernel follows as its programmatic dependent: row-wise for small tensors (decode; its peer reads are
         whole rows, the GEMM epilogue's would be 64-byte pieces of 128 x 32 tiles), block-wise two-shot above
         (prefill; 2 * (world-1)/world of the tensor crosses NVLink per rank instead of world-1 times the tensor).
         With the block-wise path off, large tensors are reduced in the GEMM's epilogue.
