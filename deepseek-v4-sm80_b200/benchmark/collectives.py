@@ -162,7 +162,7 @@ def main(argv=None):
         base = rank * e_local
 
         def moe(fused):
-            rows, plan, mt = C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, base)
+            rows, plan, mt = C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, base, 256)
             if fused:
                 return comm.moe_finalize_allreduce(rows, plan, mt, shared, None, m, topk, H)
             y = C.moe_finalize(rows, plan, mt, shared, None, m, topk, H)
@@ -234,7 +234,7 @@ def main(argv=None):
             res["ag_wqkv_a_roofline_frac"] = res["ag_wqkv_a_roofline_us"] / res["ag_wqkv_a_fused_us"]
 
             def moe_rs():
-                rows, mplan, mt = C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, base)
+                rows, mplan, mt = C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, base, 256)
                 return comm.sp_moe_finalize_reduce_scatter(plan, rows, mplan, mt, shared, m, topk, H)
 
             res["moe_rs_fused_us"] = _time_eager(moe_rs, max(it // 2, 3))

@@ -1,4 +1,4 @@
-"""Microbenchmark of the routed-expert path (plan, permute, FP4 grouped GEMM 1 and 2) with uniform-random routing.
+"""Microbenchmark of the routed-expert path (plan, permute / split, FP4 grouped GEMM 1 and 2) with uniform-random routing.
 
     python -m minisgl.benchmark.moe_gemm --experts 32 --rows 128 [--iters 5]
 
@@ -51,19 +51,21 @@ def main(argv=None):
     wt = torch.rand(m, topk, device=dev)
     touched = int(torch.unique(idx[idx < e_local]).numel())
     for _ in range(2):
-        C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, 0)
+        C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, 0, 256)
     torch.cuda.synchronize()
     native.enable_profile(True)
     for _ in range(a.iters):
         flush_l2()
-        C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, 0)
+        C.moe_routed(x, idx, wt, w13, s13, w2, s2, 7.0, 0, 256)
     # events in launch order: plan, permute, gemm(1), gemm(2)
+    # (MINISGL_MOE_KERNEL=f16: moe_permute / moe_gemm; default: moe_mx_permute / moe_mx_gemm)
     ev = {"moe_plan": [], "moe_permute": [], "moe_gemm1": [], "moe_gemm2": []}
     seen = 0
     from minisgl.ops.native import _PROFILE  # per-launch events, in order
 
     torch.cuda.synchronize()
     for name, e0, e1 in _PROFILE["events"]:
+        name = name.replace("moe_mx_", "moe_")
         if name == "moe_gemm":
             seen += 1
             name = "moe_gemm1" if seen % 2 == 1 else "moe_gemm2"
@@ -73,7 +75,7 @@ def main(argv=None):
     us = {k: sorted(v)[len(v) // 2] for k, v in ev.items() if v}
     b1 = touched * (2 * inter * H // 2 + 2 * inter * H // 32)
     b2 = touched * (H * inter // 2 + H * inter // 32)
-    out = {"experts_resident": e_local, "experts_touched": touched, "rows": m, "median_us": us,
+    out = {"kernel": C.MOE_KERNEL, "experts_resident": e_local, "experts_touched": touched, "rows": m, "median_us": us,
            "gemm1_gbs": b1 / us["moe_gemm1"] / 1e3, "gemm2_gbs": b2 / us["moe_gemm2"] / 1e3,
            "gemm1_frac_of_%s_hbm" % src: b1 / us["moe_gemm1"] / 1e3 / hbm,
            "gemm2_frac_of_%s_hbm" % src: b2 / us["moe_gemm2"] / 1e3 / hbm}

@@ -96,6 +96,14 @@ class DSV4Model:
             # the weights of this model are never written after loading: let the GEMMs fetch them ahead of the
             # dependent-launch wait
             native.check(native.cuda_lib().dsv4_gemm_set_weight_prefetch(1), "dsv4_gemm_set_weight_prefetch")
+            from ..ops import cuda as C
+
+            if C.MOE_KERNEL == "mx":
+                # one-time re-tiling of the expert weights and scales for the block-scaled grouped GEMM (same bytes,
+                # stage-contiguous order); the reference repacks its experts for Marlin at the same point
+                # (python/minisgl/models/deepseek_v4.py:1718-1787)
+                for l in range(cfg.num_layers):
+                    C.prepare_experts(weights, f"L{l}.moe.")
         from ..env import ENV
 
         self._debug_bounds = bool(ENV.DEBUG_BOUNDS)  # audit every gathered index tensor before use
@@ -230,7 +238,7 @@ class DSV4Model:
             from ..ops import cuda as C
 
             rows, plan, mt = C.moe_routed(y, idx, wt, w[p + "w13"], w[p + "s13"], w[p + "w2"], w[p + "s2"],
-                                          cfg.swiglu_limit, self.expert_base)
+                                          cfg.swiglu_limit, self.expert_base, cfg.n_routed_experts)
             t, k, h = y.shape[0], idx.shape[1], y.shape[1]
             self._join(y)
             if sp is not None:
@@ -333,7 +341,7 @@ class DSV4Model:
                 "experts_local": int(self.w["L0.moe.w13"].shape[0]), "expert_base": self.expert_base,
                 "heads_local": self.h_local, "o_groups_local": self.g_local,
                 "bytes_by_format": by_fmt, "bytes_total": sum(by_fmt.values()),
-                "derived_bytes": derived, "repack": "none (FP4 experts and FP8 projections are read in place)",
+                "derived_bytes": derived, "repack": "experts re-tiled in place for the block-scaled GEMM (same bytes); FP8 projections read in place",
                 "weight_prefetch_before_dependency_wait": bool(self.w["embed.weight"].is_cuda)}
 
     def audit_inputs(self, fb: ForwardBatch) -> None:

@@ -159,9 +159,16 @@ def build_layer(cfg: ModelConfig, l: int, raw: Dict[str, torch.Tensor], rank: in
     out[p + "moe.s13"] = torch.stack(s13, 0).contiguous()
     out[p + "moe.w2"] = torch.stack([g(f"ffn.experts.{e}.w2.weight") for e in experts], 0).contiguous()
     out[p + "moe.s2"] = torch.stack([_u8(g(f"ffn.experts.{e}.w2.scale")) for e in experts], 0).contiguous()
+    from ..ops.cuda import MOE_KERNEL
+
     for key in ("moe.s13", "moe.s2"):
         sc = out[p + key]
-        # the grouped GEMM applies a group scale as an fp16 power of two: exact for e8m0 bytes 103..142 (2^-24..2^15)
+        if MOE_KERNEL == "mx":
+            # the block-scaled MMA takes every e8m0 byte as it is; 255 encodes NaN
+            if sc.numel() and int(sc.max()) == 255:
+                raise ValueError(f"{p + key}: expert scale byte 255 (NaN)")
+            continue
+        # the fp16 grouped GEMM applies a group scale as an fp16 power of two: exact for e8m0 bytes 103..142
         if sc.numel() and (int(sc.min()) < 103 or int(sc.max()) > 142):
             raise ValueError(f"{p + key}: expert scale bytes outside [103, 142] are not representable on the fp16 "
                              f"operand path (found {int(sc.min())}..{int(sc.max())})")

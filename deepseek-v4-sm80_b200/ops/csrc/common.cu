@@ -31,6 +31,7 @@ int dsv4_make_tmap_2d(CUtensorMap* out, const void* base, int elem, uint64_t inn
   if (!fn) return 1;
   CUtensorMapDataType dt = elem == 0   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                            : elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : elem == 3 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B
                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_bytes};

@@ -104,14 +104,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 
 // ---------------------------------------------------------------- programmatic dependent launch
 // Every kernel of this library is launched with the programmatic-stream-serialization attribute: it may start while
-// the kernel before it in the stream is still draining, which hides launch latency and the prologue (barrier
-// init, tensor-memory allocation).  pdl_wait() blocks until every earlier kernel has completed and its memory is
-// visible; no kernel touches global memory before it.  pdl_launch_dependents() lets the next kernel start early.
+// the kernel before it in the stream is still running, which hides launch latency and the prologue (barrier init,
+// tensor-memory allocation, weight prefetch).  pdl_wait() blocks until every earlier kernel has completed and its
+// memory is visible; no kernel touches data of an earlier kernel before it.  pdl_launch_dependents() lets the next
+// kernel start.
+//
+// A kernel lets its successor start only AFTER its own wait, never before.  With the trigger first, a chain of
+// kernels runs ahead several deep: a kernel's CTAs can already sit on an SM while kernels two and three places
+// earlier still run there.  Loads through the read-only path (what `const __restrict__` compiles to) then hit lines
+// that an earlier kernel's CTA brought into that SM's L1 after the late kernel's start, and when the allocator has
+// meanwhile handed the address to a new tensor, the late kernel reads the old tensor's bytes: seen as a route plan
+// header that held the router's scores, in a captured graph where launches follow each other without host gaps.
+// With the wait first, a kernel starts only once everything before its predecessor has completed.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_entry() {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
 }
 
 // ---------------------------------------------------------------- thread-block clusters
@@ -228,6 +237,42 @@ __device__ __forceinline__ uint64_t umma_desc_k128(const void* smem_tile, uint32
 __host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int a_fmt, int b_fmt) {
   return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) |
          ((uint32_t)(M >> 4) << 24);
+}
+
+// ---- block-scaled MMA (kind::mxf8f6f4): D (+)= (A * SFA) (B * SFB), one ue8m0 scale per row and 32 K elements.
+// Instruction descriptor: a_fmt / b_fmt as for kind::f8f6f4, scale format e8m0, fp32 accumulate, both operands K-major.
+// The instruction covers K = 32; its scales are byte `sf_id` (0..3) of the 32-bit tensor-memory cells at sfa / sfb.
+__host__ __device__ constexpr uint32_t umma_idesc_mx(int M, int N, int a_fmt, int b_fmt) {
+  return ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) | (1u << 23) |
+         ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_mx(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sf_id,
+                                        uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  const uint32_t id = idesc | (sf_id << 4) | (sf_id << 29);
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(id), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// Scale factors of 128 rows x 4 K blocks: 512 contiguous bytes of shared memory, byte (row % 32) * 16 + (row / 32) * 4
+// + block.  The copy puts them into 4 tensor-memory columns (lane = row % 32 in each of the four 32-lane groups,
+// column = row / 32, byte = block), the arrangement the block-scaled MMA reads.  It is ordered after the MMAs this
+// thread issued before it and before those it issues afterwards.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, const void* smem_sf) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(smem_sf) & 0x3FFFF) >> 4);  // 32 rows of 16 bytes, no swizzle
+  d |= (uint64_t)1 << 16;                               // LBO (one 16-byte column: unused)
+  d |= (uint64_t)(128 >> 4) << 32;                      // SBO: 8-row groups are 128 B apart
+  d |= (uint64_t)1 << 46;
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(d) : "memory");
+}
+// untiled bulk copy global -> shared, completion counted on an mbarrier (both addresses and the size multiples of 16)
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp gets row (lane base + t)
@@ -347,6 +392,9 @@ inline cudaError_t dsv4_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3
 }
 
 // Encodes a 2-D row-major tensor map (inner = contiguous dimension) with the given box and swizzle.
-// Returns 0 on success.  elem: 0 = uint8, 1 = bf16, 2 = fp32.  swizzle: 0 = none, 3 = 128 B.
+// Returns 0 on success.  elem: 0 = uint8, 1 = bf16, 2 = fp32, 3 = packed 4-bit values that land in shared memory
+// as 16 values per 16 bytes (8 bytes of nibbles, 8 bytes of gap: the operand form of the f8f6f4 MMA kinds; inner,
+// box_inner count 4-bit elements, box_inner must be 128, base and row stride multiples of 32 bytes).
+// swizzle: 0 = none, 3 = 128 B.
 int dsv4_make_tmap_2d(CUtensorMap* out, const void* base, int elem, uint64_t inner, uint64_t outer,
                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle);

@@ -98,7 +98,6 @@ template <int BN, bool FP8, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ out,
                const GemmArgs g, const CommCtx comm) {
-  pdl_launch_dependents();
   using Cfg = GemmCfg<BN>;
   constexpr int S = Cfg::kStages;
   constexpr int BK = FP8 ? 128 : 64;  // elements per k-tile (= 128 bytes)
@@ -167,6 +166,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
   pdl_wait();
+  pdl_launch_dependents();  // only after the own wait (common.cuh: programmatic dependent launch)
 
   if (warp == 0) {
     if (lane == 0) {

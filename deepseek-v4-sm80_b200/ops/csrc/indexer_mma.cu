@@ -52,7 +52,6 @@ constexpr int kSmemBytes = SA * kATile + TGMAX * kQTile + TGMAX * HEADS * 4 + 25
 __global__ void __launch_bounds__(192, 1)
 indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ,
                           const IdxArgs a) {
-  pdl_launch_dependents();
   extern __shared__ uint8_t ix_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ix_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* atiles = smem;                                   // [SA][128 keys][128 B], 128B-swizzled by TMA
@@ -91,6 +90,7 @@ indexer_logits_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   pdl_wait();
+  pdl_launch_dependents();  // only after the own wait (common.cuh: programmatic dependent launch)
 
   // passes: maximal runs of consecutive tokens of the group that share a request slot (at most 4 runs)
   int p_first[TGMAX], p_cnt[TGMAX], p_blocks[TGMAX], p_slot[TGMAX], npass = 0;

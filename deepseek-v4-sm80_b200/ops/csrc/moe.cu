@@ -317,7 +317,6 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 const int* __restrict__ sorted_route, const float* __restrict__ sorted_w,
                 __nv_bfloat16* __restrict__ out, int K, int rows_per_expert /*I (mode1) or H (mode2)*/,
                 int ld_out, float limit) {
-  pdl_launch_dependents();
   using S = MoeSmem<MODE, NT>;
   constexpr int kOBufs = S::kOBufs, kPStages = S::kPStages, kAccBufs = S::kAccBufs;
   constexpr uint32_t kIdesc = umma_idesc(128, NT, 0, 0);  // fp16 x fp16 -> fp32
@@ -364,6 +363,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   pdl_wait();  // barriers and tensor memory are set up; from here on the kernel touches global memory
+  pdl_launch_dependents();  // only after the own wait (common.cuh: programmatic dependent launch)
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t a_base = tmem_base + S::kAccCols;  // operand buffer b starts at column a_base + b * kACols
   const int total_work = hdr->num_tiles * row_tiles;

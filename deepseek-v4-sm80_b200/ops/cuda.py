@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os as _os
 
 import torch
 
@@ -382,26 +383,119 @@ def moe_gate(y, gate_w, bias, topk, scaling, scoring, tid2eid, token_ids, num_va
     return idx, wts
 
 
-@tensors(y="bf16[T,H]", idx="i32[T,K]", w="f32[T,K]", w13="i8|u8[E,_,_]", s13="u8[E,_,_]", w2="i8|u8[E,H,_]", s2="u8[E,H,_]")
-def moe_routed(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0):
-    """Returns (route_rows bf16 [T*topk, H], plan int32) for :func:`moe_finalize`."""
+# MINISGL_MOE_KERNEL=f16 selects the W4A16 kernel that dequantises the experts to fp16 inside the SM (csrc/moe.cu);
+# the default feeds the packed FP4 weights and their scales to the block-scaled MMA as they are (csrc/moe_mx.cu).
+MOE_KERNEL = _os.environ.get("MINISGL_MOE_KERNEL", "mx")
+
+
+def block_expert_scales(s: torch.Tensor, gate_up: bool) -> torch.Tensor:
+    """e8m0 scale bytes [E, rows, K/32] -> [E, row tiles, K/128, 512]: one 512-byte block per (128 weight rows of a
+    work item, 128 K elements), byte (m % 32) * 16 + (m // 32) * 4 + k_block for tile row m -- the arrangement that one
+    tcgen05.cp moves into tensor memory for the block-scaled MMA.  gate_up: rows are [gate; up] of 2I rows and tile rt
+    holds gate rows [64 rt, 64 rt + 64) on m < 64 and the matching up rows on m >= 64 (csrc/moe_mx.cu)."""
+    e, rows, kb = s.shape
+    assert s.dtype == torch.uint8 and kb % 4 == 0, (s.dtype, s.shape)
+    ch = kb // 4
+    if gate_up:
+        i = rows // 2
+        assert i % 64 == 0
+        t = s.view(e, 2, i // 64, 64, ch, 4).permute(0, 2, 4, 1, 3, 5).reshape(e, i // 64, ch, 128, 4)
+    else:
+        assert rows % 128 == 0
+        t = s.view(e, rows // 128, 128, ch, 4).permute(0, 1, 3, 2, 4)
+    rt = t.shape[1]
+    t = t.reshape(e, rt, ch, 4, 32, 4).permute(0, 1, 2, 4, 3, 5)
+    return t.contiguous().view(e, rt, ch, 512)
+
+
+def pack_expert_weights(w: torch.Tensor, gate_up: bool) -> torch.Tensor:
+    """Packed FP4 bytes [E, rows, K/2] -> tiles [E, row tiles, K/128, 128, 64]: the 128 rows x 128 K elements of one
+    pipeline stage of the grouped GEMM become 8 KiB of consecutive bytes (csrc/moe_mx.cu explains why).  Row order
+    inside a tile as in :func:`block_expert_scales`."""
+    e, rows, kb2 = w.shape
+    assert w.dtype in (torch.int8, torch.uint8) and kb2 % 64 == 0, (w.dtype, w.shape)
+    ch = kb2 // 64
+    if gate_up:
+        i = rows // 2
+        assert i % 64 == 0
+        return w.view(e, 2, i // 64, 64, ch, 64).permute(0, 2, 4, 1, 3, 5).reshape(e, i // 64, ch, 128, 64)
+    assert rows % 128 == 0
+    return w.view(e, rows // 128, 128, ch, 64).permute(0, 1, 3, 2, 4).contiguous()
+
+
+def prepare_experts(weights: dict, prefix: str) -> None:
+    """Load-time step of the block-scaled expert kernel: replaces ``prefix + w13 / s13 / w2 / s2`` in ``weights`` by
+    their tiled forms (same bytes, other order), one tensor at a time so that at most one extra copy exists.  Tensors
+    that are tiled already are left alone."""
+    for name, gate_up in (("w13", True), ("w2", False)):
+        if weights[prefix + name].dim() == 3:
+            weights[prefix + name] = pack_expert_weights(weights[prefix + name], gate_up)
+    for name, gate_up in (("s13", True), ("s2", False)):
+        if weights[prefix + name].dim() == 3:
+            weights[prefix + name] = block_expert_scales(weights[prefix + name], gate_up)
+
+
+def _tiled(t: torch.Tensor, fn, gate_up: bool, ndim: int) -> torch.Tensor:
+    """Tiled form of an expert tensor: given as such (built at load time), or built once and kept on the tensor object
+    itself (a cache keyed by address would outlive the tensor and hit a later one)."""
+    if t.dim() == ndim:
+        return t
+    b = getattr(t, "_dsv4_tiled", None)
+    if b is None:
+        b = fn(t, gate_up)
+        t._dsv4_tiled = b
+    return b
+
+
+def route_tile(routes: int, n_experts: int, kernel: str) -> int:
+    """Routes per tile of the grouped GEMM (its N dimension): wide enough that an expert's routes rarely need a second
+    tile (which would stream the expert's weights again), no wider (the route rows of a tile are loaded per stage)."""
+    avg = routes / max(n_experts, 1)
+    if kernel != "mx":
+        return 32 if avg <= 32 else 64
+    return 8 if avg <= 3.5 else 16 if avg <= 7 else 32 if avg <= 16 else 64
+
+
+@tensors(y="bf16[T,H]", idx="i32[T,K]", w="f32[T,K]")
+def moe_routed(y, idx, w, w13, s13, w2, s2, limit, expert_base: int = 0, n_experts: int = 0):
+    """Returns (route_rows bf16 [T*topk, H], plan int32, max_tiles) for :func:`moe_finalize`.  Expert tensors in the
+    checkpoint layout (w [E, rows, K/2] packed FP4, s [E, rows, K/32] e8m0 bytes) or, for the block-scaled kernel,
+    already tiled (:func:`prepare_experts`).  n_experts: experts of the whole layer (default: the resident ones)."""
     t, h = y.shape
     topk = idx.shape[1]
     routes = t * topk
-    e_local, two_i = w13.shape[0], w13.shape[1]
-    inter = two_i // 2
-    nt = 32 if routes <= 32 * e_local else 64
+    e_local = w13.shape[0]
+    inter = w13.shape[1] * 64 if w13.dim() == 5 else w13.shape[1] // 2
+    for a in (w13, s13, w2, s2):
+        assert a.is_cuda and a.is_contiguous() and a.dtype in (torch.int8, torch.uint8) and a.shape[0] == e_local
+    nt = route_tile(routes, n_experts or e_local, MOE_KERNEL)
     max_tiles = min(e_local, routes) + routes // nt + 1
     plan = torch.empty(4 + 3 * max_tiles + 3 * routes, dtype=torch.int32, device=y.device)
     nv.call("moe_plan", nv.ptr(idx), nv.ptr(w), I(routes), I(e_local), I(expert_base), I(nt), nv.ptr(plan),
             I(max_tiles))
+    sms = num_sms(y.device)
+    rows = torch.empty(routes, h, dtype=y.dtype, device=y.device)
+    if MOE_KERNEL == "mx":
+        w13, w2 = _tiled(w13, pack_expert_weights, True, 5), _tiled(w2, pack_expert_weights, False, 5)
+        b13, b2 = _tiled(s13, block_expert_scales, True, 4), _tiled(s2, block_expert_scales, False, 4)
+        u8 = dict(dtype=torch.uint8, device=y.device)
+        # rows 2 pos / 2 pos + 1: hi / lo of a route; one 512-byte scale block per (route tile, 128 K elements)
+        xq, sfx = torch.empty(2 * routes, h, **u8), torch.empty(max_tiles, h // 128, 512, **u8)
+        nv.call("moe_mx_permute", nv.ptr(y), nv.ptr(xq), nv.ptr(sfx), nv.ptr(plan), I(routes), I(max_tiles), I(topk),
+                I(h), I(nt))
+        act, sfa = torch.empty(2 * routes, inter, **u8), torch.empty(max_tiles, inter // 128, 512, **u8)
+        nv.call("moe_mx_gemm", I(1), I(nt), nv.ptr(w13), nv.ptr(b13), nv.ptr(xq), nv.ptr(sfx), nv.ptr(plan),
+                I(routes), I(max_tiles), nv.ptr(act), nv.ptr(sfa), I(e_local), I(h), I(inter), I(inter),
+                F(limit or 0.0), I(sms))
+        nv.call("moe_mx_gemm", I(2), I(nt), nv.ptr(w2), nv.ptr(b2), nv.ptr(act), nv.ptr(sfa), nv.ptr(plan),
+                I(routes), I(max_tiles), nv.ptr(rows), nv.ptr(None), I(e_local), I(inter), I(h), I(h), F(0.0), I(sms))
+        return rows, plan, max_tiles
+    assert w13.dim() == 3 and s13.dim() == 3, "the fp16 expert kernel reads the checkpoint layout"
     xs = torch.empty(routes, h, dtype=torch.float16, device=y.device)
     nv.call("moe_permute", nv.ptr(y), nv.ptr(xs), nv.ptr(plan), I(routes), I(max_tiles), I(topk), I(h))
     act = torch.empty(routes, inter, dtype=torch.float16, device=y.device)
-    sms = num_sms(y.device)
     nv.call("moe_gemm", I(1), I(nt), nv.ptr(w13), nv.ptr(s13), nv.ptr(xs), I(routes), nv.ptr(plan), I(routes),
             I(max_tiles), nv.ptr(act), I(e_local), I(h), I(inter), I(inter), F(limit or 0.0), I(sms))
-    rows = torch.empty(routes, h, dtype=y.dtype, device=y.device)
     nv.call("moe_gemm", I(2), I(nt), nv.ptr(w2), nv.ptr(s2), nv.ptr(act), I(routes), nv.ptr(plan), I(routes),
             I(max_tiles), nv.ptr(rows), I(e_local), I(inter), I(h), I(h), F(0.0), I(sms))
     return rows, plan, max_tiles

@@ -92,7 +92,10 @@ def test_extra_tensors_are_ignored_and_bad_expert_scales_are_refused(ckpt, tmp_p
     save_file({"mtp.0.emb.weight": torch.zeros(4, 4), f"layers.{cfg.num_layers}.attn_norm.weight": torch.ones(8)},
               os.path.join(work, "model-extra.safetensors"))
     _same(W.load_checkpoint(work, cfg, "cpu"), W.load_checkpoint(folder, cfg, "cpu"))
-    # a group scale the fp16 operand path cannot represent must stop the load, not corrupt the expert
+    # the block-scaled expert kernel takes every e8m0 byte but 255 (NaN); the fp16 operand kernel only 103..142:
+    # a scale the selected kernel cannot represent must stop the load, not corrupt the expert
+    from minisgl.ops import cuda as C
+
     f = os.path.join(work, "model-layer000.safetensors")
     t = load_file(f)
     k = "layers.0.ffn.experts.0.w2.scale"
@@ -100,7 +103,18 @@ def test_extra_tensors_are_ignored_and_bad_expert_scales_are_refused(ckpt, tmp_p
     s.view(-1)[0] = 150
     t[k] = s.view(t[k].dtype)
     save_file(t, f)
-    with pytest.raises(ValueError, match="outside"):
+    assert C.MOE_KERNEL == "mx"
+    W.load_checkpoint(work, cfg, "cpu")
+    C.MOE_KERNEL = "f16"
+    try:
+        with pytest.raises(ValueError, match="outside"):
+            W.load_checkpoint(work, cfg, "cpu")
+    finally:
+        C.MOE_KERNEL = "mx"
+    s.view(-1)[0] = 255
+    t[k] = s.view(t[k].dtype)
+    save_file(t, f)
+    with pytest.raises(ValueError, match="NaN"):
         W.load_checkpoint(work, cfg, "cpu")
 
 
