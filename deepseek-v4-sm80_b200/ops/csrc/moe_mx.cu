@@ -22,16 +22,34 @@
 // With a handful of routes per expert an instruction does little arithmetic, so what bounds the kernel is how fast
 // instructions are issued, not the tensor pipe.  Measured on one CTA (M = 128, K = 32, this MMA kind): one thread
 // issues an MMA every 68 cycles whatever N <= 128 is, two threads together every 39 (N = 16) to 64 cycles (N = 128,
-// the pipe's own rate), a TMA or bulk copy costs its issuing thread about 70 cycles.  Hence:
-// Hence a pipeline stage is 256 K elements (16 KiB of packed weights, one TMA box; two boxes of route rows; two
-// 1 KiB scale copies): five copies and one barrier round trip per 8 MMAs.  One thread issues all MMAs of a CTA.  (A
-// second issuing thread with its own accumulator, stages alternating between the two, gave wrong sums and then a
-// launch failure with 16-column accumulators side by side in tensor memory; the cause was not found, so the kernel
-// has one issuer for every tile width.)
+// the pipe's own rate), a TMA or bulk copy costs its issuing thread about 70 cycles.  Inside this kernel, with one
+// CTA per SM and 256-element stages, the issuer spent 785 cycles on a stage (8 MMAs, 4 scale copies) plus 165 on the
+// barrier wait and the commit: more than the 735 cycles in which HBM delivers the stage's 17 KiB to one SM.
+// Hence TWO CTAs PER SM, each with half the shared memory and one K chunk (128 elements, 8 KiB of packed weights) per
+// stage: two independent issuers share the tensor pipe and together outrun HBM for narrow route tiles; for wide
+// tiles (NT = 64, prefill: N = 128, where an MMA takes the pipe 64 cycles) they keep the pipe busy, and one CTA's
+// epilogue runs under the other's MMAs (a wide tile has one accumulator set per CTA, a narrow one two).
+// One thread issues all MMAs of a CTA.  (A second issuing thread in the same CTA, with its own accumulator and scale
+// columns, stages alternating between the two, was tried twice, the second time with the accumulators on 32-column
+// boundaries: right sums while the weights came from a warm L2, wrong sums and then a launch failure as soon as the
+// issuers had to wait for HBM.  The cause was not found by reading, so a CTA has one issuer.)
 // Warp roles per CTA (192 threads): warp 0 TMA producer (weights through a 4-bit "unpack" tensor map: 16 nibbles
 // land in 16 bytes of shared memory, the operand form of this MMA kind), warp 1 tcgen05.cp of the scales into tensor
 // memory + tcgen05.mma, warps 2-5 epilogue.
 #include "common.cuh"
+
+#ifdef DSV4_MOE_MX_TIMING
+// development aid (scratch builds only): cycles that the producer and the MMA issuer spend waiting and issuing,
+// kept in registers and added to a global table once per CTA
+__device__ unsigned long long g_mx_timing[8];
+#define MX_CLK(v) const long long v = clock64()
+#define MX_ACC(sum, a, b) sum += (b) - (a)
+#define MX_FLUSH(slot, sum) atomicAdd(&g_mx_timing[slot], (unsigned long long)(sum))
+#else
+#define MX_CLK(v)
+#define MX_ACC(sum, a, b)
+#define MX_FLUSH(slot, sum)
+#endif
 
 namespace {
 
@@ -127,22 +145,25 @@ __global__ void __launch_bounds__(128) moe_mx_permute_kernel(const __nv_bfloat16
 
 template <int MODE, int NT>
 struct MxSmem {
-  static constexpr int kChunks = 2;                        // 128-element K chunks per pipeline stage
+  static constexpr int kCtasPerSm = 2;
+  static constexpr int kChunks = 1;                        // 128-element K chunks per pipeline stage
   static constexpr int kABytes = kChunks * 128 * 128;      // per chunk: 128 weight rows x 128 K elements, one byte each
   static constexpr int kBBytes = kChunks * 2 * NT * 128;   // per chunk: rows (hi, lo) x routes, 128 K elements (e4m3)
   static constexpr int kSfBytes = kChunks * 512;           // per chunk: scales of 128 rows x 4 K blocks
   static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
   // what the stage's copies report to the mbarrier: the unpacking weight copy counts the packed bytes it read
   static constexpr int kStageTxBytes = kABytes / 2 + kBBytes + 2 * kSfBytes;
-  // 16 KiB of packed weights per stage come from HBM: >= 64 KiB per SM in flight for the narrow tiles
-  static constexpr int kStages = NT <= 16 ? 5 : NT == 32 ? 4 : 3;
+  // 8 KiB of packed weights per stage: 2 CTAs x 5 or 4 stages keep >= 64 KiB per SM in flight (HBM latency)
+  static constexpr int kStages = NT <= 8 ? 5 : NT <= 32 ? 4 : 3;
+  static constexpr int kAccSets = NT <= 32 ? 2 : 1;  // accumulator sets of a CTA (two: its epilogue overlaps its next MMAs)
   static constexpr int kIssuers = 1;  // see the note on a second issuer at the top of the file
-  static constexpr int kXchBytes = MODE == 1 ? 2 * 64 * NT * 2 : 0;  // GEMM1 epilogue: up sums (bf16) for the gate warps
+  static constexpr int kPass = NT < 32 ? NT : 32;                   // GEMM1 epilogue: routes per pass
+  static constexpr int kXchBytes = MODE == 1 ? 128 * kPass * 2 : 0;  // its exchange buffer, bf16 [128 rows][kPass]
   static constexpr int kTotal = kStages * kStageBytes + kXchBytes + 1024 + 512;
-  static_assert(kTotal <= 227 * 1024, "shared memory budget");
+  static_assert(kCtasPerSm * (kTotal + 1024) <= 228 * 1024, "shared memory budget (1 KiB per CTA is reserved)");
   static_assert(NT == 8 || NT == 16 || NT == 32 || NT == 64, "route tile");
   static constexpr int kAccStride = kIssuers * 2 * NT;  // columns of one accumulator set: [issuer][128 x 2 NT]
-  static constexpr int kAccCols = 2 * kAccStride;        // two sets, so an epilogue overlaps the next item's MMAs
+  static constexpr int kAccCols = kAccSets * kAccStride;
   static constexpr int kSfColsIssuer = 2 * kChunks * 8;  // per issuer: two buffers of kChunks x (SFA 4 + SFB 4) columns
   static constexpr int kUsedCols = kAccCols + kIssuers * kSfColsIssuer;
   static constexpr uint32_t kTmemCols = kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128 : kUsedCols <= 256 ? 256 : 512;
@@ -155,7 +176,7 @@ struct MxSmem {
 //         w13 tiles [E, I/64, K/128, 128, 64 B] (rows 0..63 gate, 64..127 up), sfa [E, I/64, K/128, 512].
 // MODE 2: D -> out[route, h] = bf16(bf16(acc) * bf16(w_route)); w2 tiles [E, H/128, K/128, 128, 64 B], sfa alike.
 template <int MODE, int NT>
-__global__ void __launch_bounds__(kMxThreads, 1)
+__global__ void __launch_bounds__(kMxThreads, 2)
 moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb,
                    const MxPlanHeader* __restrict__ hdr, const int* __restrict__ tiles,
@@ -163,7 +184,7 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                    uint8_t* __restrict__ sf_out, int K, int rows_per_expert /*I (mode 1) or H (mode 2)*/, int ld_out,
                    float limit, int e_local, int routes, int max_tiles) {
   using S = MxSmem<MODE, NT>;
-  constexpr int kStages = S::kStages, kChunks = S::kChunks, kIssuers = S::kIssuers;
+  constexpr int kStages = S::kStages, kChunks = S::kChunks, kIssuers = S::kIssuers, kAccSets = S::kAccSets;
   constexpr uint32_t kIdesc = umma_idesc_mx(128, 2 * NT, 5, 0);  // e2m1 x e4m3, ue8m0 scales
   constexpr int kIssuerWarp1 = 6;  // unused while kIssuers == 1 (the CTA has warps 0..5)
   extern __shared__ uint8_t mx_smem_raw[];
@@ -174,7 +195,7 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint64_t* empty = full + kStages;  // [kStages] the stage's MMAs and scale copies retired
   uint64_t* tfull = empty + kStages;  // [2] accumulator set complete (one commit per issuer)
   uint64_t* tempty = tfull + 2;       // [2] accumulator set drained by the four epilogue warps
-  uint64_t* xfull = tempty + 2;       // [2] GEMM1: the up warps' sums are in the exchange buffer
+  uint64_t* xfull = tempty + 2;       // [2] GEMM1 epilogue: [0] a pass' sums are in the exchange buffer, [1] they were read
   uint64_t* drain = xfull + 2;        // [2] only after a wait ran out: the issuers' MMAs in flight have retired
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(drain + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -187,7 +208,7 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) mbar_init(&full[i], 1), mbar_init(&empty[i], 1);
     for (int i = 0; i < 2; ++i)
-      mbar_init(&tfull[i], kIssuers), mbar_init(&tempty[i], 4), mbar_init(&xfull[i], 2), mbar_init(&drain[i], 1);
+      mbar_init(&tfull[i], kIssuers), mbar_init(&tempty[i], 4), mbar_init(&xfull[i], 4), mbar_init(&drain[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
@@ -217,6 +238,7 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (lane == 0) {
       long long ps = 0;
       bool ok = true;
+      [[maybe_unused]] long long t_wait = 0, t_issue = 0;
       for (int wk = blockIdx.x; wk < total_work && ok; wk += gridDim.x) {
         const int ct = wk / row_tiles, rt = wk % row_tiles;
         if (!tile_ok(ct)) {
@@ -230,7 +252,9 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint8_t* sb = sfb + (size_t)ct * nchunks * 512;
         for (int sg = 0; sg < nstages; ++sg, ++ps) {
           const int s = (int)(ps % kStages);
+          MX_CLK(c0);
           if (!mbar_wait(&empty[s], ((uint32_t)(ps / kStages) & 1) ^ 1, abort_flag, 21)) { ok = false; break; }
+          MX_CLK(c1);
           uint8_t* st = smem + s * S::kStageBytes;
           mbar_expect_tx(&full[s], S::kStageTxBytes);
           tma_load_2d(st, &tmW, &full[s], 0, (int)(wrow + sg * (kChunks * 128)));  // 16 KiB of consecutive bytes
@@ -239,8 +263,13 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             tma_load_2d(st + S::kABytes + c * (2 * NT * 128), &tmX, &full[s], (sg * kChunks + c) * 128, 2 * tok0);
           bulk_load(st + S::kABytes + S::kBBytes, sa + (size_t)sg * S::kSfBytes, S::kSfBytes, &full[s]);
           bulk_load(st + S::kABytes + S::kBBytes + S::kSfBytes, sb + (size_t)sg * S::kSfBytes, S::kSfBytes, &full[s]);
+          MX_CLK(c2);
+          MX_ACC(t_wait, c0, c1);
+          MX_ACC(t_issue, c1, c2);
         }
       }
+      MX_FLUSH(0, t_wait);
+      MX_FLUSH(1, t_issue);
     }
   } else if (warp == 1 || (kIssuers == 2 && warp == kIssuerWarp1)) {
     if (lane == 0) {
@@ -250,17 +279,23 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       int it = 0;
       long long mine = 0;  // stages this issuer has handled (selects its scale buffer in tensor memory)
       bool ok = true;
+      [[maybe_unused]] long long t_acc = 0, t_full = 0, t_mma = 0, t_commit = 0;
       const uint32_t sf_base = tmem_base + S::kAccCols + iss * S::kSfColsIssuer;
       for (int wk = blockIdx.x; wk < total_work && ok; wk += gridDim.x, ++it, ps0 += nstages) {
-        const int acc = it & 1;
-        if (!mbar_wait(&tempty[acc], ((uint32_t)(it >> 1) & 1) ^ 1, abort_flag, 22)) break;
+        const int acc = it % kAccSets;
+        MX_CLK(a0);
+        if (!mbar_wait(&tempty[acc], ((uint32_t)(it / kAccSets) & 1) ^ 1, abort_flag, 22)) break;
+        MX_CLK(a1);
+        MX_ACC(t_acc, a0, a1);
         tc_fence_after();
         const uint32_t d = tmem_base + acc * S::kAccStride + iss * 2 * NT;
         bool first = true;
         for (int sg = iss; sg < nstages; sg += kIssuers, ++mine) {
           const long long ps = ps0 + sg;
           const int s = (int)(ps % kStages);
+          MX_CLK(f0);
           if (!mbar_wait(&full[s], (uint32_t)(ps / kStages) & 1, abort_flag, 23)) { ok = false; break; }
+          MX_CLK(f1);
           tc_fence_after();
           const uint8_t* st = smem + s * S::kStageBytes;
           const uint32_t sft = sf_base + (uint32_t)(mine & 1) * (kChunks * 8);
@@ -278,16 +313,26 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                       kIdesc, k, sft + c * 8, sft + c * 8 + 4, !(first && c == 0 && k == 0));
           }
           first = false;
+          MX_CLK(f2);
           umma_commit(&empty[s]);
+          MX_CLK(f3);
+          MX_ACC(t_full, f0, f1);
+          MX_ACC(t_mma, f1, f2);
+          MX_ACC(t_commit, f2, f3);
         }
         if (ok) umma_commit(&tfull[acc]);
       }
+      MX_FLUSH(2, t_acc);
+      MX_FLUSH(3, t_full);
+      MX_FLUSH(4, t_mma);
+      MX_FLUSH(5, t_commit);
     }
   } else if (warp < 6) {  // epilogue: warp w reads the TMEM lanes of quarter w % 4
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     int it = 0;
+    [[maybe_unused]] int xph = 0;  // GEMM1: passes through the exchange buffer so far
     // sum over issuers of (hi + lo) of 8 routes: 16 accumulator columns per issuer
     const bool two = kIssuers == 2 && nstages >= 2;  // a one-stage item leaves the second issuer's accumulator unwritten
     auto load8 = [&](uint32_t d0, int r0, float (&y)[8]) {
@@ -302,11 +347,11 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     };
     for (int wk = blockIdx.x; wk < total_work; wk += gridDim.x, ++it) {
-      const int acc = it & 1;
+      const int acc = it % kAccSets;
       const int ct = wk / row_tiles, rt = wk % row_tiles;
       if (!tile_ok(ct)) break;  // the producer reports it and stops the CTA
       const int tok0 = tiles[ct * 3 + 1], ntok = tiles[ct * 3 + 2];
-      if (!mbar_wait<256>(&tfull[acc], (uint32_t)(it >> 1) & 1, abort_flag, 24)) break;
+      if (!mbar_wait<256>(&tfull[acc], (uint32_t)(it / kAccSets) & 1, abort_flag, 24)) break;
       tc_fence_after();
       const uint32_t d0 = lane_addr + acc * S::kAccStride;
       if (MODE == 2) {
@@ -330,61 +375,71 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
         }
       } else {
-        __nv_bfloat16* xq = xch + (size_t)acc * 64 * NT;  // [64 rows][NT], one buffer per accumulator set
-        const bool is_up = r >= 64;
-        if (is_up) {
+        // SwiGLU and the hi / lo split, kPass routes at a time.  Step 1, all four warps: the bf16-rounded sums of
+        // the pass go to shared memory, xs[row][route] (gate rows 0..63, up rows 64..127; a row's entries are rotated
+        // by the row number, which spreads the lanes' column-wise stores over the banks).  Step 2, warps 0 and 1 of the
+        // group: thread (block b, route) reads its 32 gate and 32 up values, applies the clamped SwiGLU, takes the
+        // block's largest magnitude in registers and stores 32 hi and 32 lo bytes as two 16-byte pieces each.
+        constexpr int kPass = S::kPass;
+        bool dead = false;
 #pragma unroll 1
-          for (int r0 = 0; r0 < NT; r0 += 8) {
+        for (int p0 = 0; p0 < NT && !dead; p0 += kPass) {
+          if (p0 >= ntok) break;
+          // the readers of the pass before (of this or the previous work item) are done with xs
+          if (xph > 0 && !mbar_wait(&xfull[1], (uint32_t)(xph - 1) & 1, abort_flag, 26)) { dead = true; break; }
+#pragma unroll 1
+          for (int r0 = p0; r0 < p0 + kPass; r0 += 8) {
             if (r0 >= ntok) break;
             float y[8];
             load8(d0, r0, y);
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-              xq[(size_t)(r - 64) * NT + ((r0 + c + (r & 7)) & (NT - 1))] = f2bf(y[c]);
+            for (int c = 0; c < 8; ++c) xch[r * kPass + ((r0 - p0 + c + r) & (kPass - 1))] = f2bf(y[c]);
           }
           __syncwarp();
-          if (lane == 0) mbar_arrive(&xfull[acc]);
-        } else if (!mbar_wait(&xfull[acc], (uint32_t)(it >> 1) & 1, abort_flag, 25)) {
-          break;
-        }
-        if (!is_up) {
-          // this warp holds 32 consecutive intermediate indices: one scale block per route column
-          const int orow = rt * 64 + r;
-          uint8_t* act = reinterpret_cast<uint8_t*>(out);
-          uint8_t* sblk = sf_out + ((size_t)ct * (rows_per_expert / 128) + (rt * 64 + q * 32) / 128) * 512;
-          const int kb = ((rt * 64 + q * 32) >> 5) & 3;
-#pragma unroll 1
-          for (int r0 = 0; r0 < NT; r0 += 8) {
-            if (r0 >= ntok) break;
-            float y[8];
-            load8(d0, r0, y);
+          if (lane == 0) mbar_arrive(&xfull[0]);
+          if (!mbar_wait(&xfull[0], (uint32_t)xph & 1, abort_flag, 25)) { dead = true; break; }
+          const int n = p0 + lane;  // route of the tile
+          if (q < 2 && lane < kPass && n < ntok) {
+            const int b = q;
+            float a[32], amax = 0.f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              float gv = bf2f(f2bf(y[c]));
-              float uv = bf2f(xq[(size_t)r * NT + ((r0 + c + (r & 7)) & (NT - 1))]);
+            for (int i = 0; i < 32; ++i) {
+              const int rg = b * 32 + i, ru = 64 + rg;
+              float gv = bf2f(xch[rg * kPass + ((lane + rg) & (kPass - 1))]);
+              float uv = bf2f(xch[ru * kPass + ((lane + ru) & (kPass - 1))]);
               if (limit > 0.f) {
                 gv = fminf(gv, limit);
                 uv = fminf(fmaxf(uv, -limit), limit);
               }
-              float a = bf2f(f2bf(gv / (1.f + expf(-gv)) * uv));
-              if (r0 + c >= ntok) a = 0.f;  // columns past the tile hold another tile's routes
-              const float amax = warp_max(fabsf(a));
-              int eh, el;
-              mx_block_exps(amax, eh, el);
-              uint32_t hb, lb;
-              mx_split(a, eh, el, hb, lb);
-              if (r0 + c < ntok) {
-                const int n = r0 + c;
-                act[(size_t)(2 * (tok0 + n)) * ld_out + orow] = (uint8_t)hb;
-                act[(size_t)(2 * (tok0 + n) + 1) * ld_out + orow] = (uint8_t)lb;
-                if (lane == (c & 31)) {
-                  sblk[sf_offset(2 * n, kb)] = (uint8_t)eh;
-                  sblk[sf_offset(2 * n + 1, kb)] = (uint8_t)el;
-                }
-              }
+              a[i] = bf2f(f2bf(gv / (1.f + expf(-gv)) * uv));
+              amax = fmaxf(amax, fabsf(a[i]));
             }
+            int eh, el;
+            mx_block_exps(amax, eh, el);
+            uint32_t wh[8] = {0, 0, 0, 0, 0, 0, 0, 0}, wl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              uint32_t hb, lb;
+              mx_split(a[i], eh, el, hb, lb);
+              wh[i >> 2] |= hb << (8 * (i & 3));
+              wl[i >> 2] |= lb << (8 * (i & 3));
+            }
+            const int col0 = rt * 64 + b * 32;  // first intermediate index of the block
+            uint8_t* act = reinterpret_cast<uint8_t*>(out);
+            uint4* dh = reinterpret_cast<uint4*>(act + (size_t)(2 * (tok0 + n)) * ld_out + col0);
+            uint4* dl = reinterpret_cast<uint4*>(act + (size_t)(2 * (tok0 + n) + 1) * ld_out + col0);
+            dh[0] = make_uint4(wh[0], wh[1], wh[2], wh[3]), dh[1] = make_uint4(wh[4], wh[5], wh[6], wh[7]);
+            dl[0] = make_uint4(wl[0], wl[1], wl[2], wl[3]), dl[1] = make_uint4(wl[4], wl[5], wl[6], wl[7]);
+            uint8_t* sblk = sf_out + ((size_t)ct * (rows_per_expert / 128) + col0 / 128) * 512;
+            const int kb = (col0 >> 5) & 3;
+            sblk[sf_offset(2 * n, kb)] = (uint8_t)eh;
+            sblk[sf_offset(2 * n + 1, kb)] = (uint8_t)el;
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&xfull[1]);
+          ++xph;
         }
+        if (dead) break;
       }
       tc_fence_before();
       __syncwarp();
@@ -424,9 +479,11 @@ int launch_mx_gemm(const void* w, const uint8_t* sfa, const void* xq, const uint
   static bool set = false;
   if (!set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) return 243;
+    // two CTAs per SM need the SM's whole shared-memory carveout
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
     set = true;
   }
-  dsv4_launch(kern, num_sms, kMxThreads, S::kTotal, st, tmW, tmX, sfa, sfb, hdr, tiles, sorted_route, sorted_w, out,
+  dsv4_launch(kern, num_sms * S::kCtasPerSm, kMxThreads, S::kTotal, st, tmW, tmX, sfa, sfb, hdr, tiles, sorted_route, sorted_w, out,
               sf_out, K, rows_per_expert, ld_out, limit, e_local, x_rows, max_tiles);
   return (int)cudaGetLastError();
 }
@@ -455,7 +512,7 @@ DSV4_API int dsv4_moe_mx_gemm(int mode, int nt, const void* w, const void* sfa, 
                               const int* plan, int routes, int max_tiles, void* out, void* sf_out, int e_local, int K,
                               int rows_per_expert, int ld_out, float limit, int num_sms, cudaStream_t st) {
   if (routes <= 0) return 0;
-  if (K % 256 || rows_per_expert % 128 || (reinterpret_cast<uintptr_t>(w) & 31)) return 244;
+  if (K % 256 || rows_per_expert % 128 || (reinterpret_cast<uintptr_t>(w) & 31)) return 244;  // K: whole stages
   const MxPlanHeader* hdr = reinterpret_cast<const MxPlanHeader*>(plan);
   const int* tiles = plan + 4;
   const int* sorted_route = tiles + 3 * max_tiles;
@@ -475,3 +532,14 @@ DSV4_API int dsv4_moe_mx_gemm(int mode, int nt, const void* w, const void* sfa, 
 #undef MX_LAUNCH
   return 245;
 }
+
+#ifdef DSV4_MOE_MX_TIMING
+DSV4_API int dsv4_moe_mx_timing(long long* host_out, int clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_mx_timing, sizeof(long long) * 8);
+  if (clear) {
+    long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_mx_timing, z, sizeof(z));
+  }
+  return (int)e;
+}
+#endif
