@@ -6,11 +6,19 @@
 //
 // Two operand formats:
 //   * bf16 x bf16 (kind::f16), fp32 accumulate over the CTA's K range in one TMEM buffer.
-//   * e4m3 x e4m3 (kind::f8f6f4) with power-of-two block scales: activations carry one fp32 scale per (row, 128-wide
-//     K block), weights one per (128 x 128) block.  Each 128-wide K block is accumulated on the tensor cores into one
-//     of two TMEM buffers and promoted into fp32 registers by the epilogue warps as
-//     acc += sa[row,kb] * sw[nb,kb] * partial  -- the exact arithmetic of the reference's "fake-quant activations x
-//     dequantised weights" path (python/minisgl/models/deepseek_v4.py:145-149, :483) up to summation order.
+//   * e4m3 x e4m3 with power-of-two block scales: activations carry one fp32 scale per (row, 128-wide K block),
+//     weights one per (128 x 128) block.  The scales go to the tensor core as they are: the block-scaled MMA
+//     (kind::mxf8f6f4.block_scale) multiplies every 32-element K group by 2^(ea + eb) from ue8m0 bytes in tensor memory
+//     and accumulates the whole K range in ONE fp32 accumulator, i.e.  out = sum_kb sa[row,kb] * sw[nb,kb] * partial_kb
+//     -- the arithmetic of the reference's "fake-quant activations x dequantised weights" path
+//     (python/minisgl/models/deepseek_v4.py:145-149, :483) up to summation order -- without reading a partial product
+//     back per K block (an earlier version promoted every 128-wide block through the epilogue warps, which bounded
+//     the kernel at 0.33 us per k-tile and kept tiles at 32 columns: 0.16-0.2 of the HBM rate at 128 rows).  Before
+//     the main loop the four epilogue warps turn this CTA's scales into 512-byte blocks in shared memory, one per
+//     k-tile, holding byte(sa[row,kb]) + byte(sw[nb,kb]) - 127 for the tile's 128 rows (the weight scale is uniform
+//     over a tile's columns, so it is folded into the row scale and the column-side scale is the constant 1).
+//     Scales must be exact powers of two (they are: e8m0 weights, power-of-two activation quantisation); a scale with
+//     mantissa bits is reported in the status word.
 //
 // Three launch extensions, all through blockIdx.z = batch * splits + split:
 //   * batched: batch b reads A columns [b*a_col_pb, +K), B rows [b*b_row_pb, +N) and writes output columns
@@ -26,13 +34,17 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kRowBytes = 128;  // one swizzle span per tile row
 
-template <int BN>
+constexpr int kMaxKt = 64;  // fp8: k-tiles (128 elements each) of one CTA's K range whose scale blocks fit shared memory
+
+template <int BN, bool FP8 = false>
 struct GemmCfg {
   static constexpr int kStages = (BN >= 128) ? 5 : 6;
   static constexpr int kABytes = kBM * kRowBytes;
   static constexpr int kBBytes = BN * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  // fp8: one 512-byte scale block per k-tile + the constant block of ones
+  static constexpr int kSfBytes = FP8 ? (kMaxKt + 1) * 512 : 0;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kSfBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct GemmArgs {
@@ -98,21 +110,19 @@ template <int BN, bool FP8, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ out,
                const GemmArgs g, const CommCtx comm) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, FP8>;
   constexpr int S = Cfg::kStages;
   constexpr int BK = FP8 ? 128 : 64;  // elements per k-tile (= 128 bytes)
-  // FP8: every 128-wide k-tile gets an accumulator of its own, promoted by the epilogue warps with the tile's scales.
-  // kAcc of them rotate (256 tensor-memory columns, 512 for the widest tile), so that the MMA issuer runs several
-  // tiles ahead of the promotion instead of waiting for a round trip through two buffers.
-  constexpr uint32_t kTmemCols = FP8 ? (BN <= 128 ? 256 : 2 * BN) : (BN < 32 ? 32 : BN);
-  constexpr int kAcc = FP8 ? (int)kTmemCols / BN : 1;
-  static_assert((kAcc & (kAcc - 1)) == 0 && kAcc <= 8, "accumulator ring");
-  constexpr uint32_t kIdesc = FP8 ? umma_idesc(kBM, BN, 0, 0) : umma_idesc(kBM, BN, 1, 1);
+  // one accumulator [128 x BN]; fp8 adds the scale columns: 4 for the constant column-side block, 2 x 4 for the row
+  // scales of the k-tile in flight and the next one
+  constexpr uint32_t kTmemCols = FP8 ? (BN <= 32 ? 64 : BN <= 64 ? 128 : 256) : (BN < 32 ? 32 : BN);
+  constexpr uint32_t kIdesc = FP8 ? umma_idesc_mx(kBM, BN, 0, 0) : umma_idesc(kBM, BN, 1, 1);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint8_t* sf_all = smem + S * Cfg::kStageBytes;  // fp8: [nkt] row-scale blocks, then the block of ones
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + Cfg::kSfBytes);
   uint64_t* empty = full + S;
   uint64_t* tfull = empty + S;   // [8]
   uint64_t* tempty = tfull + 8;  // [8]
@@ -138,7 +148,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int i = 0; i < 8; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 128);
+      mbar_init(&tempty[i], 128);  // [0]: fp8, the 128 epilogue threads have written the scale blocks
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -197,33 +207,37 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      for (int i = 0; i < nkt; ++i) {
+      const uint32_t d = tmem_base;
+      const uint32_t sfb_t = tmem_base + BN, sfa_t = tmem_base + BN + 4;  // scale columns behind the accumulator
+      bool ok = true;
+      if (FP8 && nkt > 0) {
+        // the scale blocks of this CTA's K range are in shared memory once the epilogue warps have arrived
+        ok = mbar_wait(&tempty[0], 0, abort_flag, 2);
+        tc_fence_after();
+        if (ok) tmem_cp_sf(sfb_t, sf_all + (size_t)nkt * 512);
+      }
+      for (int i = 0; i < nkt && ok; ++i) {
         const int s = i % S;
         const uint32_t ph = (i / S) & 1;
-        uint32_t d = tmem_base;
-        if (FP8) {
-          const int b = i & (kAcc - 1);
-          if (!mbar_wait(&tempty[b], ((i / kAcc) & 1) ^ 1, abort_flag, 2)) break;
-          d = tmem_base + b * BN;
-        }
         if (!mbar_wait(&full[s], ph, abort_flag, 3)) break;
         tc_fence_after();
         const uint8_t* a = tiles + s * Cfg::kStageBytes;
         const uint8_t* bt = a + Cfg::kABytes;
+        const uint32_t sfa_i = sfa_t + (uint32_t)(i & 1) * 4;
+        if (FP8) tmem_cp_sf(sfa_i, sf_all + (size_t)i * 512);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const uint64_t ad = umma_desc_k128(a, k * 32);
           const uint64_t bd = umma_desc_k128(bt, k * 32);
-          const uint32_t acc = FP8 ? (k > 0) : (i > 0 || k > 0);
+          const uint32_t acc = (i > 0 || k > 0);
           if (FP8)
-            umma_f8(d, ad, bd, kIdesc, acc);
+            umma_mx(d, ad, bd, kIdesc, k, sfa_i, sfb_t, acc);
           else
             umma_f16(d, ad, bd, kIdesc, acc);
         }
         umma_commit(&empty[s]);
-        if (FP8) umma_commit(&tfull[i & (kAcc - 1)]);
       }
-      if (!FP8 && nkt > 0) umma_commit(&tfull[0]);
+      if (nkt > 0) umma_commit(&tfull[0]);
     }
   } else {
     // epilogue warps 2..5 ; TMEM lane quarter = warp % 4
@@ -244,43 +258,50 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
     for (int j = 0; j < BN; ++j) acc[j] = 0.f;
     bool ok = true;
-    if (!FP8) {
-      if (nkt > 0) {
-        ok = mbar_wait<64>(&tfull[0], 0, abort_flag, 4);
-        tc_fence_after();
-        if (ok) {
+    if (FP8 && nkt > 0) {
+      // scale blocks: block i, word (row % 32) * 4 + row / 32 = the byte ea(row, k-tile i) + eb(k-tile i) - 127 four
+      // times (one per 32-element group of the tile); the block behind them is all 127 (2^0)
+      const size_t sb_row = (size_t)((batch * g.b_row_pb + n0) >> 7) * g.sb_ld;
+      const float* sa_row = g.sa + (size_t)(grow < M ? grow : 0) * k_tiles + kt0;
+      uint32_t* blk = reinterpret_cast<uint32_t*>(sf_all) + (row & 31) * 4 + (row >> 5);
+      bool pow2 = true;
+      // sixteen k-tiles at a time: all their scale loads are in flight together (a dependent loop would pay the
+      // global-memory latency once per k-tile, before the first MMA can be issued)
+#pragma unroll 1
+      for (int i0 = 0; i0 < nkt; i0 += 16) {
+        uint32_t ba[16], bb[16];
 #pragma unroll
-          for (int c = 0; c < BN / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(lane_addr + c * 32, r);
-            tmem_ld_wait();
+        for (int j = 0; j < 16; ++j) {
+          const bool in = i0 + j < nkt;
+          ba[j] = (in && grow < M) ? __float_as_uint(sa_row[i0 + j]) : 0u;
+          bb[j] = in ? __float_as_uint(g.sb[sb_row + kt0 + i0 + j]) : 0x3f800000u;
+        }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 16; ++j) {
+          if (i0 + j < nkt) {
+            pow2 = pow2 && !((ba[j] | bb[j]) & 0x807fffffu);
+            const int e = grow < M ? (int)(ba[j] >> 23) + (int)(bb[j] >> 23) - 127 : 0;
+            blk[(i0 + j) * 128] = (uint32_t)min(max(e, 0), 254) * 0x01010101u;
           }
         }
       }
-    } else {
-      const size_t sb_row = (size_t)((batch * g.b_row_pb + n0) >> 7) * g.sb_ld;
-      const int kblocks = k_tiles;
-      for (int i = 0; i < nkt; ++i) {
-        const int b = i & (kAcc - 1);
-        if (!mbar_wait(&tfull[b], (i / kAcc) & 1, abort_flag, 5)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const float s_a = (grow < M) ? g.sa[(size_t)grow * kblocks + kt0 + i] : 0.f;
-        const float sc = s_a * g.sb[sb_row + kt0 + i];
+      reinterpret_cast<uint32_t*>(sf_all)[nkt * 128 + row] = 0x7f7f7f7fu;
+      if (!pow2) dsv4_set_error(DSV4_ERR_BAD_INDEX, 41, grow);  // a scale that is not a power of two
+      fence_proxy_async_smem();
+      mbar_arrive(&tempty[0]);
+    }
+    if (nkt > 0) {
+      ok = mbar_wait<64>(&tfull[0], 0, abort_flag, 4);
+      tc_fence_after();
+      if (ok) {
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32(lane_addr + b * BN + c * 32, r);
+          tmem_ld_32x32(lane_addr + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(sc, __uint_as_float(r[j]), acc[c * 32 + j]);
+          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(r[j]);
         }
-        tc_fence_before();
-        mbar_arrive(&tempty[b]);
       }
     }
     bool write_out = ok;
@@ -497,9 +518,10 @@ int g_weight_prefetch = 0;  // set by dsv4_gemm_set_weight_prefetch
 template <int BN, bool FP8, typename OutT>
 int launch_gemm(const void* x, const void* w, OutT* out, int M, int N, int K, int ldx, int ldw, int ldo, const float* sa,
                 const float* sb, int accumulate_out, cudaStream_t stream, const LaunchOpts& o) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, FP8>;
   constexpr int BK = FP8 ? 128 : 64;
   const int esz = FP8 ? 1 : 2;
+  if (FP8 && ((K + BK - 1) / BK + o.splits - 1) / o.splits > kMaxKt) return 108;  // scale blocks of one CTA's K range
   CUtensorMap tmA, tmB;
   const uint64_t a_cols = o.a_cols ? o.a_cols : K, b_rows = o.b_rows ? o.b_rows : N;
   if (dsv4_make_tmap_2d(&tmA, x, FP8 ? 0 : 1, a_cols, (uint64_t)M, (uint64_t)ldx * esz, BK, kBM, 3)) return 101;
@@ -538,21 +560,20 @@ int dispatch_bn(const void* x, const void* w, OutT* out, int M, int N, int K, in
                 const float* sb, int acc, int bn, cudaStream_t st, const LaunchOpts& o = LaunchOpts{}) {
   if (bn == 0) {
     const int mt = (M + kBM - 1) / kBM * o.batches;
-    if (mt * ((N + 127) / 128) >= 98 && !FP8)
+    if (mt * ((N + 127) / 128) >= 98)
       bn = 128;
     else if (mt * ((N + 63) / 64) >= 98)
       bn = 64;
     else
       bn = 32;
   }
-  if (FP8 && bn > 64) bn = 64;
   // fused all-reduce epilogue: one flag slot per tile, so a tile count beyond the slots needs the wider tile
   if (o.comm && !o.deposit_only && bn < 64 &&
       (long long)((N + bn - 1) / bn) * ((M + kBM - 1) / kBM) > kCommSlots)
     bn = 64;
   switch (bn) {
     case 128:
-      if constexpr (!FP8) return launch_gemm<128, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, o);
+      return launch_gemm<128, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, o);
     case 64:
       return launch_gemm<64, FP8, OutT>(x, w, out, M, N, K, ldx, ldw, ldo, sa, sb, acc, st, o);
     default:

@@ -37,6 +37,8 @@ def _counters(device) -> torch.Tensor:
 def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int = 0, splits: int = 0):
     """(tile width, K splits) that put roughly one CTA on every SM."""
     mt = max((m + 127) // 128 * batches, 1)      # m == 0 (nothing to do) must not divide by zero below
+    if fp8 and mt == 1 and bn == 0 and splits == 0:
+        return _pick_decode_fp8(n, k_tiles)
     if bn == 0:
         fill = NUM_SMS_HINT * 2 // 3
         if mt == 1:
@@ -44,11 +46,8 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
             # cheaper per byte; but a split costs a cluster launch and two cluster barriers (about 4 us measured, 8 us
             # for 8-way), so: no split when 32-wide tiles alone fill the GPU, else the widest tile that fills it with
             # at most 4 splits.
-            # FP8 stays at 32 columns: its epilogue warps promote every 128-wide K block out of tensor memory, work
-            # that grows with the tile width and is the per-k-tile bottleneck (0.33 us at 32 columns, 0.8 at 64).
-            if fp8:
-                bn = 32
-            elif (n + 31) // 32 >= fill:
+            # (FP8 follows the same rule since its block scales are applied by the MMA itself.)
+            if (n + 31) // 32 >= fill:
                 bn = 128 if (n + 127) // 128 >= fill else 64 if (n + 63) // 64 >= fill else 32
             else:
                 smax = max(min(4, k_tiles // 4), 1)
@@ -56,14 +55,12 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
                     bn = cand
                     if ((n + cand - 1) // cand) * smax >= fill:
                         break
-        elif mt * ((n + 127) // 128) >= fill and not fp8:
+        elif mt * ((n + 127) // 128) >= fill:
             bn = 128  # the widest tile that still gives about one CTA per SM
         elif mt * ((n + 63) // 64) >= fill:
             bn = 64
         else:
             bn = 32
-    if fp8 and bn > 64:
-        bn = 64
     if splits == 0:
         ctas = mt * ((n + bn - 1) // bn)
         splits = 1
@@ -74,6 +71,31 @@ def pick_tiling(m: int, n: int, k_tiles: int, batches: int, fp8: bool, bn: int =
     if mt * ((n + bn - 1) // bn) > (1 << 16):
         splits = 1
     return bn, splits
+
+
+# One row tile of FP8 activations (decode): what a k-tile costs is its bytes from L2 -- every CTA re-reads the 16 KiB
+# activation tile next to its bn x 128 bytes of weights -- at the rate one CTA's TMA ring pulls (about 57 GB/s:
+# 32 CTAs x 12 k-tiles x 32 KiB took 6.9 us, 32 x 32 x 32 KiB 18.2 us) or at the L2's aggregate rate when all SMs
+# pull (about 5.3 TB/s: 164 MB in 31 us), whichever is slower; a K split adds the cluster launch and its two
+# barriers (4 us up to four ways).  The widest tile moves the fewest bytes (a weight row costs 16384 / bn + 128
+# bytes per k-tile) but needs K splits to put enough CTAs on the GPU.
+_SM_GBS, _L2_GBS, _SPLIT_US = 57.0, 5300.0, {1: 0.0, 2: 4.0, 4: 4.0}
+
+
+def _pick_decode_fp8(n: int, k_tiles: int):
+    best = None
+    for bn in (32, 64, 128):
+        tiles = (n + bn - 1) // bn
+        for splits in (1, 2, 4):
+            if splits > 1 and (k_tiles // splits < 2 or tiles * splits > 2 * NUM_SMS_HINT):
+                continue
+            ctas = tiles * splits
+            per_cta = -(-k_tiles // splits) * (16384 + bn * 128)
+            waves = -(-ctas // NUM_SMS_HINT)
+            t = max(waves * per_cta / (_SM_GBS * 1e3), ctas * per_cta / (_L2_GBS * 1e3)) + _SPLIT_US[splits]
+            if best is None or t < best[0] - 1e-9:
+                best = (t, bn, splits)
+    return best[1], best[2]
 
 
 def _ws(m, n, bn, batches, splits, device):

@@ -406,6 +406,99 @@ def test_moe_full_size_repeatable(e_local, m):
     close(got, exp, atol=0.13, rtol=3e-2)
 
 
+def test_moe_mx_split_is_exact_for_bf16():
+    """The block-scaled expert kernel writes every bf16 activation as hi + lo (two e4m3 values under one power-of-two
+    scale per 32 elements each).  For every element within 2^13 of its block's largest magnitude the pair must give the
+    bf16 value back bit for bit; smaller ones may be off by at most 2^-21 of that magnitude."""
+    from minisgl.ops import cuda as C
+    from minisgl.ops import native as nv
+    from minisgl.ops.native import I
+
+    t, h, e, k, nt = 45, 4096, 16, 6, 8
+    g = torch.Generator().manual_seed(1)
+    y = (torch.randn(t, h, generator=g) * torch.exp(torch.randn(t, h, generator=g) * 2)).to(torch.bfloat16).to(DEV)
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).to(torch.int32).to(DEV)
+    wt = torch.rand(t, k, generator=g).to(DEV)
+    routes = t * k
+    max_tiles = min(e, routes) + routes // nt + 1
+    plan = torch.empty(4 + 3 * max_tiles + 3 * routes, dtype=torch.int32, device=DEV)
+    nv.call("moe_plan", nv.ptr(idx), nv.ptr(wt), I(routes), I(e), I(0), I(nt), nv.ptr(plan), I(max_tiles))
+    xq = torch.zeros(2 * routes, h, dtype=torch.uint8, device=DEV)
+    sfx = torch.zeros(max_tiles, h // 128, 512, dtype=torch.uint8, device=DEV)
+    nv.call("moe_mx_permute", nv.ptr(y), nv.ptr(xq), nv.ptr(sfx), nv.ptr(plan), I(routes), I(max_tiles), I(k), I(h),
+            I(nt))
+    torch.cuda.synchronize()
+    p = plan.cpu()
+    ntiles = int(p[0])
+    tiles = p[4:4 + 3 * max_tiles].view(max_tiles, 3)
+    sroute = p[4 + 3 * max_tiles: 4 + 3 * max_tiles + routes]
+    xqc, sfc, yc = xq.cpu(), sfx.cpu(), y.cpu().float()
+    blk = torch.arange(h) // 32
+    seen = 0
+    for ti in range(ntiles):
+        _, tok0, ntok = [int(v) for v in tiles[ti]]
+        assert 1 <= ntok <= nt
+        for n in range(ntok):
+            pos = tok0 + n
+            x = yc[int(sroute[pos]) // k]
+            hi = xqc[2 * pos].view(torch.float8_e4m3fn).float()
+            lo = xqc[2 * pos + 1].view(torch.float8_e4m3fn).float()
+            off = lambda row: (row % 32) * 16 + (row // 32) * 4 + (blk % 4)
+            eh = sfc[ti, blk // 4, off(2 * n)].float()
+            el = sfc[ti, blk // 4, off(2 * n + 1)].float()
+            rec = hi * torch.exp2(eh - 127) + lo * torch.exp2(el - 127)
+            bmax = x.abs().view(-1, 32).max(-1).values.repeat_interleave(32)
+            big = x.abs() >= bmax * 2.0 ** -13
+            assert torch.equal(rec[big], x[big])
+            assert bool(((rec - x).abs() <= bmax * 2.0 ** -21).all())
+            seen += 1
+    assert seen == routes  # every expert is resident: every route has a position
+
+
+def _flush_l2():
+    if not hasattr(_flush_l2, "buf"):
+        _flush_l2.buf = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    _flush_l2.buf.zero_()
+
+
+@pytest.mark.parametrize("m,expect_nt", [(128, 8), (256, 16), (600, 32), (2048, 64)])
+def test_moe_mx_every_tile_width_cold_and_warm(m, expect_nt):
+    """One rank of an 8-way expert-parallel layer (32 of 256 experts resident), full-size experts: the block-scaled
+    kernel at each route-tile width against the fp16-operand kernel (both compute the exact bf16 x FP4 products with
+    fp32 accumulation; they differ in summation order only), bit-identical from call to call, also when every call
+    starts from a flushed L2 (weights, plan and route rows then arrive from HBM and every pipeline wait is taken)."""
+    from minisgl.ops import cuda as C
+
+    h, inter, topk, e_local = 4096, 2048, 6, 32
+    assert C.route_tile(m * topk, 256, "mx") == expect_nt
+    g = torch.Generator().manual_seed(11)
+    w13 = torch.randint(0, 256, (e_local, 2 * inter, h // 2), generator=g, dtype=torch.uint8).view(torch.int8)
+    s13 = torch.randint(119, 122, (e_local, 2 * inter, h // 32), generator=g, dtype=torch.uint8)
+    w2 = torch.randint(0, 256, (e_local, h, inter // 2), generator=g, dtype=torch.uint8).view(torch.int8)
+    s2 = torch.randint(119, 122, (e_local, h, inter // 32), generator=g, dtype=torch.uint8)
+    y = bf(m, h, seed=3)
+    idx = torch.stack([torch.randperm(256, generator=g)[:topk] for _ in range(m)]).to(torch.int32)
+    wt = torch.rand(m, topk, generator=g)
+    dev = [a.to(DEV) for a in (y, idx, wt, w13, s13, w2, s2)]
+
+    def run():
+        rows, plan, mt = C.moe_routed(*dev, 7.0, 0, 256)
+        return C.moe_finalize(rows, plan, mt, None, None, m, topk, h)
+
+    assert C.MOE_KERNEL == "mx"
+    C.MOE_KERNEL = "f16"
+    try:
+        want = run().float()
+    finally:
+        C.MOE_KERNEL = "mx"
+    first = run()
+    assert float((first.float() - want).norm() / want.norm()) < 1e-3
+    for i in range(5):
+        if i >= 2:
+            _flush_l2()
+        assert torch.equal(run(), first), f"call {i} differs"
+
+
 def test_fused_quant_matches_separate_quant():
     """The producers that also write FP8 (rms_norm, hc_pre, SwiGLU) give exactly what fp8_quant gives on their
     bf16 result."""

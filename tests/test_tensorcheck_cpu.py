@@ -63,3 +63,44 @@ def test_kernel_wrappers_declare_their_tensor_arguments():
     with pytest.raises(TensorSpecError, match="dtype"):
         cuda.hc_post(torch.zeros(2, 8), torch.zeros(2, 4, 8, dtype=torch.bfloat16), torch.zeros(2, 4),
                      torch.zeros(2, 4, 4))
+
+
+def test_expert_tiling_keeps_every_byte_and_is_indexed_as_the_kernel_reads_it():
+    """Load-time re-tiling for the block-scaled expert kernel: scale byte (tile row m, K block kb) of a 512-byte block
+    sits at (m % 32) * 16 + (m // 32) * 4 + kb; a weight tile is 128 rows x 64 bytes; gate / up tiles interleave 64
+    gate rows with the 64 matching up rows."""
+    import torch
+
+    from minisgl.ops.cuda import block_expert_scales, pack_expert_weights, prepare_experts, route_tile
+
+    e, inter, k = 2, 128, 256
+    s13 = torch.randint(0, 255, (e, 2 * inter, k // 32), dtype=torch.uint8)
+    w13 = torch.randint(-128, 127, (e, 2 * inter, k // 2), dtype=torch.int8)
+    s2 = torch.randint(0, 255, (e, 256, k // 32), dtype=torch.uint8)
+    w2 = torch.randint(-128, 127, (e, 256, k // 2), dtype=torch.int8)
+    b13, t13, b2, t2 = block_expert_scales(s13, True), pack_expert_weights(w13, True), block_expert_scales(s2, False), \
+        pack_expert_weights(w2, False)
+    assert b13.shape == (e, inter // 64, k // 128, 512) and t13.shape == (e, inter // 64, k // 128, 128, 64)
+    assert b2.shape == (e, 2, k // 128, 512) and t2.shape == (e, 2, k // 128, 128, 64)
+    for ee in range(e):
+        for rt in range(inter // 64):
+            for ch in range(k // 128):
+                for m in (0, 31, 32, 63, 64, 100, 127):
+                    row = rt * 64 + m if m < 64 else inter + rt * 64 + m - 64
+                    assert torch.equal(t13[ee, rt, ch, m], w13[ee, row, ch * 64:(ch + 1) * 64])
+                    for kb in range(4):
+                        assert b13[ee, rt, ch, (m % 32) * 16 + (m // 32) * 4 + kb] == s13[ee, row, ch * 4 + kb]
+        for rt in range(2):
+            for ch in range(k // 128):
+                for m in (0, 33, 127):
+                    assert torch.equal(t2[ee, rt, ch, m], w2[ee, rt * 128 + m, ch * 64:(ch + 1) * 64])
+                    for kb in range(4):
+                        assert b2[ee, rt, ch, (m % 32) * 16 + (m // 32) * 4 + kb] == s2[ee, rt * 128 + m, ch * 4 + kb]
+    w = {"L0.moe.w13": w13, "L0.moe.s13": s13, "L0.moe.w2": w2, "L0.moe.s2": s2}
+    prepare_experts(w, "L0.moe.")
+    assert torch.equal(w["L0.moe.w13"], t13) and torch.equal(w["L0.moe.s2"], b2)
+    before = {k_: v.data_ptr() for k_, v in w.items()}
+    prepare_experts(w, "L0.moe.")  # tiled tensors are left alone
+    assert before == {k_: v.data_ptr() for k_, v in w.items()}
+    assert [route_tile(r * 6, 256, "mx") for r in (64, 128, 256, 512, 1024)] == [8, 8, 16, 32, 64]
+    assert route_tile(768, 256, "f16") == 32
