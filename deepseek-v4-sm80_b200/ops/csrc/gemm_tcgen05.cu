@@ -258,6 +258,22 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
     for (int j = 0; j < BN; ++j) acc[j] = 0.f;
     bool ok = true;
+    if (FP8 && g.sp_mode == 1) {
+      // the activation scales are part of the gathered buffer: like the TMA producer, wait for the owner's flag of this
+      // row block before reading them (one thread polls, the group's barrier hands the result to the others)
+      if (warp == 2 && lane == 0) {
+        const int owner = m0 / g.sp.rows_per_rank;
+        bool gate_ok = true;
+        if (owner != g.sp.rank)
+          gate_ok = sp_wait_flag(sp_flag(g.sp, g.sp.rank, kSpAG, owner, m0 >> 7), g.sp.seq, owner, m0 >> 7);
+        __threadfence();
+        *sh_flag = gate_ok ? 1 : 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      __threadfence();
+      ok = *sh_flag != 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // sh_flag is reused by the split-K reduction below
+    }
     if (FP8 && nkt > 0) {
       // scale blocks: block i, word (row % 32) * 4 + row / 32 = the byte ea(row, k-tile i) + eb(k-tile i) - 127 four
       // times (one per 32-element group of the tile); the block behind them is all 127 (2^0)
