@@ -38,19 +38,6 @@
 // memory + tcgen05.mma, warps 2-5 epilogue.
 #include "common.cuh"
 
-#ifdef DSV4_MOE_MX_TIMING
-// development aid (scratch builds only): cycles that the producer and the MMA issuer spend waiting and issuing,
-// kept in registers and added to a global table once per CTA
-__device__ unsigned long long g_mx_timing[8];
-#define MX_CLK(v) const long long v = clock64()
-#define MX_ACC(sum, a, b) sum += (b) - (a)
-#define MX_FLUSH(slot, sum) atomicAdd(&g_mx_timing[slot], (unsigned long long)(sum))
-#else
-#define MX_CLK(v)
-#define MX_ACC(sum, a, b)
-#define MX_FLUSH(slot, sum)
-#endif
-
 namespace {
 
 constexpr int kMxThreads = 192;
@@ -238,7 +225,6 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (lane == 0) {
       long long ps = 0;
       bool ok = true;
-      [[maybe_unused]] long long t_wait = 0, t_issue = 0;
       for (int wk = blockIdx.x; wk < total_work && ok; wk += gridDim.x) {
         const int ct = wk / row_tiles, rt = wk % row_tiles;
         if (!tile_ok(ct)) {
@@ -252,9 +238,7 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint8_t* sb = sfb + (size_t)ct * nchunks * 512;
         for (int sg = 0; sg < nstages; ++sg, ++ps) {
           const int s = (int)(ps % kStages);
-          MX_CLK(c0);
           if (!mbar_wait(&empty[s], ((uint32_t)(ps / kStages) & 1) ^ 1, abort_flag, 21)) { ok = false; break; }
-          MX_CLK(c1);
           uint8_t* st = smem + s * S::kStageBytes;
           mbar_expect_tx(&full[s], S::kStageTxBytes);
           tma_load_2d(st, &tmW, &full[s], 0, (int)(wrow + sg * (kChunks * 128)));  // 16 KiB of consecutive bytes
@@ -263,13 +247,8 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             tma_load_2d(st + S::kABytes + c * (2 * NT * 128), &tmX, &full[s], (sg * kChunks + c) * 128, 2 * tok0);
           bulk_load(st + S::kABytes + S::kBBytes, sa + (size_t)sg * S::kSfBytes, S::kSfBytes, &full[s]);
           bulk_load(st + S::kABytes + S::kBBytes + S::kSfBytes, sb + (size_t)sg * S::kSfBytes, S::kSfBytes, &full[s]);
-          MX_CLK(c2);
-          MX_ACC(t_wait, c0, c1);
-          MX_ACC(t_issue, c1, c2);
         }
       }
-      MX_FLUSH(0, t_wait);
-      MX_FLUSH(1, t_issue);
     }
   } else if (warp == 1 || (kIssuers == 2 && warp == kIssuerWarp1)) {
     if (lane == 0) {
@@ -279,23 +258,17 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       int it = 0;
       long long mine = 0;  // stages this issuer has handled (selects its scale buffer in tensor memory)
       bool ok = true;
-      [[maybe_unused]] long long t_acc = 0, t_full = 0, t_mma = 0, t_commit = 0;
       const uint32_t sf_base = tmem_base + S::kAccCols + iss * S::kSfColsIssuer;
       for (int wk = blockIdx.x; wk < total_work && ok; wk += gridDim.x, ++it, ps0 += nstages) {
         const int acc = it % kAccSets;
-        MX_CLK(a0);
         if (!mbar_wait(&tempty[acc], ((uint32_t)(it / kAccSets) & 1) ^ 1, abort_flag, 22)) break;
-        MX_CLK(a1);
-        MX_ACC(t_acc, a0, a1);
         tc_fence_after();
         const uint32_t d = tmem_base + acc * S::kAccStride + iss * 2 * NT;
         bool first = true;
         for (int sg = iss; sg < nstages; sg += kIssuers, ++mine) {
           const long long ps = ps0 + sg;
           const int s = (int)(ps % kStages);
-          MX_CLK(f0);
           if (!mbar_wait(&full[s], (uint32_t)(ps / kStages) & 1, abort_flag, 23)) { ok = false; break; }
-          MX_CLK(f1);
           tc_fence_after();
           const uint8_t* st = smem + s * S::kStageBytes;
           const uint32_t sft = sf_base + (uint32_t)(mine & 1) * (kChunks * 8);
@@ -313,19 +286,10 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                       kIdesc, k, sft + c * 8, sft + c * 8 + 4, !(first && c == 0 && k == 0));
           }
           first = false;
-          MX_CLK(f2);
           umma_commit(&empty[s]);
-          MX_CLK(f3);
-          MX_ACC(t_full, f0, f1);
-          MX_ACC(t_mma, f1, f2);
-          MX_ACC(t_commit, f2, f3);
         }
         if (ok) umma_commit(&tfull[acc]);
       }
-      MX_FLUSH(2, t_acc);
-      MX_FLUSH(3, t_full);
-      MX_FLUSH(4, t_mma);
-      MX_FLUSH(5, t_commit);
     }
   } else if (warp < 6) {  // epilogue: warp w reads the TMEM lanes of quarter w % 4
     const int q = warp & 3;
@@ -532,14 +496,3 @@ DSV4_API int dsv4_moe_mx_gemm(int mode, int nt, const void* w, const void* sfa, 
 #undef MX_LAUNCH
   return 245;
 }
-
-#ifdef DSV4_MOE_MX_TIMING
-DSV4_API int dsv4_moe_mx_timing(long long* host_out, int clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(host_out, g_mx_timing, sizeof(long long) * 8);
-  if (clear) {
-    long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    cudaMemcpyToSymbol(g_mx_timing, z, sizeof(z));
-  }
-  return (int)e;
-}
-#endif
