@@ -7,8 +7,9 @@ Rules checked over the package sources (Python and CUDA):
   * no compatibility layers on the compute path: no ``import triton`` / ``tilelang`` / ``torch.compile`` /
     ``flashinfer`` / ``flash_attn`` / ``vllm`` imports;
   * no CUDA batched-memcpy entry points; no TMA or bulk load with cluster multicast; no ``wgmma``;
-  * every ``__global__`` kernel begins with the programmatic-dependent-launch prologue (``pdl_entry`` or
-    ``pdl_launch_dependents`` + ``pdl_wait``), and no launch uses the ``<<< >>>`` syntax (launches go through
+  * every ``__global__`` kernel has the programmatic-dependent-launch prologue (``pdl_entry``, or after a set-up
+    phase ``pdl_wait`` followed by ``pdl_launch_dependents``: never the trigger before the own wait), and no launch
+    uses the ``<<< >>>`` syntax (launches go through
     ``dsv4_launch`` so that they all carry the same attributes);
   * every spin loop in device code is bounded: a ``for (;;)`` / ``while (true)`` body must contain a clock read;
   * ``tests/``: a test that touches CUDA carries the ``gpu`` marker (file-level ``pytestmark`` or per-test marks).
@@ -99,8 +100,12 @@ def audit() -> Dict:
         for name, body in _kernel_bodies(src):
             n += 1
             head = body[:400]
-            if "pdl_entry()" not in head and not ("pdl_launch_dependents()" in head and "pdl_wait()" in body):
+            w, t = body.find("pdl_wait()"), body.find("pdl_launch_dependents()")
+            # pdl_entry() first thing, or (kernels with a set-up phase) an explicit wait followed by the trigger
+            if "pdl_entry()" not in head and not (0 <= w < t):
                 violations.append(f"{rel}: kernel {name} lacks the dependent-launch prologue")
+            elif 0 <= t < w:
+                violations.append(f"{rel}: kernel {name} lets its successor start before its own wait")
             for loop in re.finditer(r"for \(;;\)|while \(true\)|while \(1\)", body):
                 depth, e = 0, body.find("{", loop.end())
                 s0 = e
