@@ -104,3 +104,22 @@ def test_expert_tiling_keeps_every_byte_and_is_indexed_as_the_kernel_reads_it():
     assert before == {k_: v.data_ptr() for k_, v in w.items()}
     assert [route_tile(r * 6, 256, "mx") for r in (64, 128, 256, 512, 1024)] == [8, 8, 16, 32, 64]
     assert route_tile(768, 256, "f16") == 32
+
+
+def test_decode_tile_choice_is_launchable_and_prefers_fewer_bytes():
+    """The FP8 decode tile model returns only configurations the kernel accepts (tile widths 32 / 64 / 128, splits
+    1 / 2 / 4 with at least two k-tiles per split, at most 64 k-tiles per CTA) and moves to wide tiles with K splits
+    where narrow tiles would re-read the activation tile most often."""
+    from minisgl.ops.gemm import _pick_decode_fp8, pick_tiling
+
+    for n in (256, 512, 1536, 2112, 4096, 8192, 32768, 129280):
+        for k in (256, 1024, 1536, 2048, 4096, 8192):
+            bn, splits = _pick_decode_fp8(n, k // 128)
+            assert bn in (32, 64, 128) and splits in (1, 2, 4)
+            assert splits == 1 or (k // 128) // splits >= 2
+            assert -(-(k // 128) // splits) <= 64
+            assert pick_tiling(128, n, k // 128, 1, True) == (bn, splits)
+    assert _pick_decode_fp8(32768, 12) == (128, 1)          # enough column tiles: the widest tile, no split
+    assert _pick_decode_fp8(4096, 64)[0] == 128 and _pick_decode_fp8(4096, 64)[1] > 1   # long K, few columns
+    # explicit arguments are respected
+    assert pick_tiling(128, 4096, 32, 1, True, bn=32, splits=1) == (32, 1)
