@@ -143,16 +143,15 @@ struct MxSmem {
   // 8 KiB of packed weights per stage: 2 CTAs x 5 or 4 stages keep >= 64 KiB per SM in flight (HBM latency)
   static constexpr int kStages = NT <= 8 ? 5 : NT <= 32 ? 4 : 3;
   static constexpr int kAccSets = NT <= 32 ? 2 : 1;  // accumulator sets of a CTA (two: its epilogue overlaps its next MMAs)
-  static constexpr int kIssuers = 1;  // see the note on a second issuer at the top of the file
   static constexpr int kPass = NT < 32 ? NT : 32;                   // GEMM1 epilogue: routes per pass
   static constexpr int kXchBytes = MODE == 1 ? 128 * kPass * 2 : 0;  // its exchange buffer, bf16 [128 rows][kPass]
   static constexpr int kTotal = kStages * kStageBytes + kXchBytes + 1024 + 512;
   static_assert(kCtasPerSm * (kTotal + 1024) <= 228 * 1024, "shared memory budget (1 KiB per CTA is reserved)");
   static_assert(NT == 8 || NT == 16 || NT == 32 || NT == 64, "route tile");
-  static constexpr int kAccStride = kIssuers * 2 * NT;  // columns of one accumulator set: [issuer][128 x 2 NT]
+  static constexpr int kAccStride = 2 * NT;  // columns of one accumulator set: [128 x (hi, lo) x NT]
   static constexpr int kAccCols = kAccSets * kAccStride;
-  static constexpr int kSfColsIssuer = 2 * kChunks * 8;  // per issuer: two buffers of kChunks x (SFA 4 + SFB 4) columns
-  static constexpr int kUsedCols = kAccCols + kIssuers * kSfColsIssuer;
+  static constexpr int kSfCols = 2 * kChunks * 8;  // two buffers of kChunks x (SFA 4 + SFB 4) columns
+  static constexpr int kUsedCols = kAccCols + kSfCols;
   static constexpr uint32_t kTmemCols = kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128 : kUsedCols <= 256 ? 256 : 512;
   static_assert(kUsedCols <= 512, "tensor memory budget");
 };
@@ -171,9 +170,8 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                    uint8_t* __restrict__ sf_out, int K, int rows_per_expert /*I (mode 1) or H (mode 2)*/, int ld_out,
                    float limit, int e_local, int routes, int max_tiles) {
   using S = MxSmem<MODE, NT>;
-  constexpr int kStages = S::kStages, kChunks = S::kChunks, kIssuers = S::kIssuers, kAccSets = S::kAccSets;
+  constexpr int kStages = S::kStages, kChunks = S::kChunks, kAccSets = S::kAccSets;
   constexpr uint32_t kIdesc = umma_idesc_mx(128, 2 * NT, 5, 0);  // e2m1 x e4m3, ue8m0 scales
-  constexpr int kIssuerWarp1 = 6;  // unused while kIssuers == 1 (the CTA has warps 0..5)
   extern __shared__ uint8_t mx_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mx_smem_raw) + 1023) & ~uintptr_t(1023));
   __nv_bfloat16* xch = reinterpret_cast<__nv_bfloat16*>(smem + kStages * S::kStageBytes);
@@ -183,8 +181,8 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint64_t* tfull = empty + kStages;  // [2] accumulator set complete (one commit per issuer)
   uint64_t* tempty = tfull + 2;       // [2] accumulator set drained by the four epilogue warps
   uint64_t* xfull = tempty + 2;       // [2] GEMM1 epilogue: [0] a pass' sums are in the exchange buffer, [1] they were read
-  uint64_t* drain = xfull + 2;        // [2] only after a wait ran out: the issuers' MMAs in flight have retired
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(drain + 2);
+  uint64_t* drain = xfull + 2;        // [1] only after a wait ran out: the MMAs in flight have retired
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(drain + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -195,7 +193,8 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) mbar_init(&full[i], 1), mbar_init(&empty[i], 1);
     for (int i = 0; i < 2; ++i)
-      mbar_init(&tfull[i], kIssuers), mbar_init(&tempty[i], 4), mbar_init(&xfull[i], 4), mbar_init(&drain[i], 1);
+      mbar_init(&tfull[i], 1), mbar_init(&tempty[i], 4), mbar_init(&xfull[i], 4);
+    mbar_init(drain, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
@@ -250,28 +249,25 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       }
     }
-  } else if (warp == 1 || (kIssuers == 2 && warp == kIssuerWarp1)) {
+  } else if (warp == 1) {
     if (lane == 0) {
-      // MMA issuer `iss`: the stages of its parity, into its own accumulator
-      const int iss = warp == 1 ? 0 : 1;
       long long ps0 = 0;  // ring index of the work item's first stage
       int it = 0;
-      long long mine = 0;  // stages this issuer has handled (selects its scale buffer in tensor memory)
       bool ok = true;
-      const uint32_t sf_base = tmem_base + S::kAccCols + iss * S::kSfColsIssuer;
+      const uint32_t sf_base = tmem_base + S::kAccCols;
       for (int wk = blockIdx.x; wk < total_work && ok; wk += gridDim.x, ++it, ps0 += nstages) {
         const int acc = it % kAccSets;
         if (!mbar_wait(&tempty[acc], ((uint32_t)(it / kAccSets) & 1) ^ 1, abort_flag, 22)) break;
         tc_fence_after();
-        const uint32_t d = tmem_base + acc * S::kAccStride + iss * 2 * NT;
+        const uint32_t d = tmem_base + acc * S::kAccStride;
         bool first = true;
-        for (int sg = iss; sg < nstages; sg += kIssuers, ++mine) {
+        for (int sg = 0; sg < nstages; ++sg) {
           const long long ps = ps0 + sg;
           const int s = (int)(ps % kStages);
           if (!mbar_wait(&full[s], (uint32_t)(ps / kStages) & 1, abort_flag, 23)) { ok = false; break; }
           tc_fence_after();
           const uint8_t* st = smem + s * S::kStageBytes;
-          const uint32_t sft = sf_base + (uint32_t)(mine & 1) * (kChunks * 8);
+          const uint32_t sft = sf_base + (uint32_t)(ps & 1) * (kChunks * 8);  // the scale columns alternate per stage
           const uint64_t a0 = umma_desc_k128(st, 0), b0 = umma_desc_k128(st + S::kABytes, 0);
 #pragma unroll
           for (int c = 0; c < kChunks; ++c) {
@@ -297,18 +293,13 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     int it = 0;
     [[maybe_unused]] int xph = 0;  // GEMM1: passes through the exchange buffer so far
-    // sum over issuers of (hi + lo) of 8 routes: 16 accumulator columns per issuer
-    const bool two = kIssuers == 2 && nstages >= 2;  // a one-stage item leaves the second issuer's accumulator unwritten
+    // hi + lo of 8 routes: 16 accumulator columns
     auto load8 = [&](uint32_t d0, int r0, float (&y)[8]) {
-      uint32_t a[16], b[16];
+      uint32_t a[16];
       tmem_ld_32x16(d0 + 2 * r0, a);
-      if (two) tmem_ld_32x16(d0 + 2 * NT + 2 * r0, b);
       tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        y[c] = __uint_as_float(a[2 * c]) + __uint_as_float(a[2 * c + 1]);
-        if (two) y[c] += __uint_as_float(b[2 * c]) + __uint_as_float(b[2 * c + 1]);
-      }
+      for (int c = 0; c < 8; ++c) y[c] = __uint_as_float(a[2 * c]) + __uint_as_float(a[2 * c + 1]);
     };
     for (int wk = blockIdx.x; wk < total_work; wk += gridDim.x, ++it) {
       const int acc = it % kAccSets;
@@ -415,10 +406,9 @@ moe_mx_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (*abort_flag) {
     // a wait ran out (the status word says where): before the tensor memory is freed and the CTA leaves, let the
     // MMAs already issued retire and the copies in flight land, each with a limit of its own
-    if ((warp == 1 || warp == kIssuerWarp1) && lane == 0) {
-      uint64_t* b = &drain[warp == 1 ? 0 : 1];
-      umma_commit(b);
-      for (int i = 0; i < 20000 && !mbar_try_wait(b, 0); ++i) __nanosleep(100);
+    if (warp == 1 && lane == 0) {
+      umma_commit(drain);
+      for (int i = 0; i < 20000 && !mbar_try_wait(drain, 0); ++i) __nanosleep(100);
     }
     if (threadIdx.x == 0)
       for (int i = 0; i < 100; ++i) __nanosleep(1000);
