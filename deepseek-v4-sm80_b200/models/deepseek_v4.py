@@ -320,9 +320,9 @@ class DSV4Model:
     def prepare_report(self) -> dict:
         """What the loaded weights occupy on this rank, by storage format, and which derived tensors were built at
         load time.  The reference rebuilds BF16 caches and a Marlin repack at every start and reports them in
-        ``model_prepare_report`` (python/minisgl/models/deepseek_v4.py:1718-1787); here FP8 / FP4 weights are consumed
-        in place, so the derived part is small: the dequantised ``wo_a``, the bf16 router weight and the stacked
-        compressor projection."""
+        ``model_prepare_report`` (python/minisgl/models/deepseek_v4.py:1718-1787); here the FP8 projections are
+        consumed in place and the FP4 experts are only re-ordered (same bytes), so the derived part is small: the
+        dequantised ``wo_a``, the bf16 router weight and the stacked compressor projection."""
         by_fmt, derived = {}, {}
         for k, v in self.w.items():
             if not isinstance(v, torch.Tensor):
