@@ -104,3 +104,36 @@ def fp4_dequant(packed: torch.Tensor, scale_code: torch.Tensor, group: int = 32,
     v = torch.stack((lo, hi), dim=-1).flatten(-2)
     s = e8m0_decode(scale_code).repeat_interleave(group, dim=-1)[..., : v.shape[-1]]
     return (v * s).to(dtype)
+
+
+# --------------------------------------------------------------------------- hi / lo split of bf16 activations
+def mx_split(x: torch.Tensor, group: int = 32):
+    """bf16 activations [..., K] -> (hi e4m3, lo e4m3, hi exponent bytes, lo exponent bytes) with one power-of-two
+    scale per ``group`` K elements each, so that ``x == hi * 2^(eh - 127) + lo * 2^(el - 127)``.  This is the operand
+    form of the block-scaled expert kernel (ops/csrc/moe_mx.cu: ``mx_block_exps`` / ``mx_split``), restated in torch:
+    eh = biased exponent of the group's largest magnitude - 7 (clamped to [5, 253]), el = eh - 5; hi is x / 2^(eh-127)
+    rounded to e4m3 (round to nearest even), lo is the remainder / 2^(el-127) rounded to e4m3.  A bf16 value has 8
+    significant bits, hi keeps the upper 4, and the remainder is a multiple of the value's last place of at most half
+    a place of hi, so lo is exact for every element within 2^14 of its group's largest magnitude."""
+    xf = x.float()
+    k = xf.shape[-1]
+    assert k % group == 0
+    g = xf.reshape(*xf.shape[:-1], k // group, group)
+    amax = g.abs().amax(-1)
+    ef = (amax.view(torch.int32) >> 23) & 0xFF
+    eh = (ef - 7).clamp(5, 253)
+    el = eh - 5
+    sh = torch.pow(2.0, (eh - 127).float()).unsqueeze(-1)
+    sl = torch.pow(2.0, (el - 127).float()).unsqueeze(-1)
+    hi = (g / sh).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    lo = ((g - hi.float() * sh) / sl).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    return hi.reshape(xf.shape), lo.reshape(xf.shape), eh.to(torch.uint8), el.to(torch.uint8)
+
+
+def mx_join(hi: torch.Tensor, lo: torch.Tensor, eh: torch.Tensor, el: torch.Tensor, group: int = 32) -> torch.Tensor:
+    """Inverse of :func:`mx_split` (fp32)."""
+    k = hi.shape[-1]
+    sh = torch.pow(2.0, eh.to(torch.int32).float() - 127.0).repeat_interleave(group, -1)
+    sl = torch.pow(2.0, el.to(torch.int32).float() - 127.0).repeat_interleave(group, -1)
+    return hi.float() * sh[..., :k] + lo.float() * sl[..., :k]
+
